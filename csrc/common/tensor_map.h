@@ -1,0 +1,73 @@
+// Host-side construction of TMA tensor maps without linking libcuda directly:
+// the encoder is looked up through the runtime's driver entry point query.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace b200 {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) {
+      throw std::runtime_error("cuTensorMapEncodeTiled is not available from the installed driver");
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D tensor map over a row-major matrix of 16-bit elements.
+//   inner      : number of contiguous elements per row
+//   outer      : number of rows
+//   row_stride : elements between consecutive rows (multiple of 8)
+//   box_inner / box_outer : tile fetched per copy (box_inner * 2 bytes <= 128 when swizzled)
+inline CUtensorMap make_tensor_map_2d_b16(const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride,
+                                          uint32_t box_inner, uint32_t box_outer, bool swizzle128 = true) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) throw std::runtime_error("TMA base must be 16-byte aligned");
+  if ((row_stride * 2) % 16 != 0) throw std::runtime_error("TMA row stride must be a multiple of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+  return m;
+}
+
+// 3-D variant: [outer2][outer][inner] with explicit strides (elements) for the two outer dims.
+inline CUtensorMap make_tensor_map_3d_b16(const void* base, uint64_t inner, uint64_t outer, uint64_t outer2,
+                                          uint64_t stride_outer, uint64_t stride_outer2, uint32_t box_inner,
+                                          uint32_t box_outer, uint32_t box_outer2, bool swizzle128 = true) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) throw std::runtime_error("TMA base must be 16-byte aligned");
+  if ((stride_outer * 2) % 16 != 0 || (stride_outer2 * 2) % 16 != 0)
+    throw std::runtime_error("TMA strides must be multiples of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {inner, outer, outer2};
+  cuuint64_t strides[2] = {stride_outer * 2, stride_outer2 * 2};
+  cuuint32_t box[3] = {box_inner, box_outer, box_outer2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+  return m;
+}
+
+}  // namespace b200

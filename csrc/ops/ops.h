@@ -1,0 +1,57 @@
+// Plain C++ launch interface of every kernel in this library (raw pointers and a
+// stream; no tensor library types) so that the Python binding layer and C callers
+// share one set of entry points.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// ---- gemm/gemm_bf16.cu
+void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+               bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream);
+
+// ---- gemm/grouped_gemm.cu
+void grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offsets, const int* gather_idx,
+                       const int* scatter_idx, const float* row_scale, int num_groups, int total_rows, int N, int K,
+                       long long lda, long long ldb_group, long long ldb, long long ldc, bool b_mn, int epi,
+                       int* status, cudaStream_t stream);
+
+// ---- ops/norm.cu
+int rmsnorm_bwd_partial_rows(int T);
+void rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd, int T, int H,
+                 float eps, cudaStream_t stream);
+void rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres, void* dh,
+                 float* partial, float* dw, bool accumulate_dw, int T, int H, cudaStream_t stream);
+
+// ---- ops/elementwise.cu
+void swiglu_fwd(const void* x, void* y, long long T, int I, cudaStream_t stream);
+void swiglu_bwd(const void* dy, const void* x, void* dx, void* y_recompute, long long T, int I, cudaStream_t stream);
+void rope_inplace(void* qkv, const float* cos_t, const float* sin_t, const int* position_ids, int T, long long row_stride,
+                  int num_kv_groups, int q_per_group, int head_dim, int rope_dim, bool inverse, cudaStream_t stream);
+void embedding_fwd(const void* weight, const long long* ids, void* out, int T, int H, float scale, cudaStream_t stream);
+void embedding_bwd(const void* dy, const long long* ids, float* dweight, int T, int H, float scale,
+                   cudaStream_t stream);
+void cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
+void cast_bf16_to_f32(const void* src, float* dst, long long n, bool accumulate, float scale, cudaStream_t stream);
+void add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+int sumsq_partial_count(long long n);
+void sumsq_f32(const float* x, long long n, float* partials, float* out, bool accumulate, cudaStream_t stream);
+void clip_coef(const float* total_sq, float max_norm, float* coef, float* norm, cudaStream_t stream);
+void adamw_step(float* p, float* m, float* v, float* g, void* p_bf16, long long n, float lr, float beta1, float beta2,
+                float eps, float weight_decay, float bias_c1, float bias_c2, const float* grad_scale, float grad_mul,
+                bool zero_grad, cudaStream_t stream);
+
+// ---- ops/cross_entropy.cu
+void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss, float* lse, int T, int V,
+                           long long row_stride, float logit_scale, float grad_scale, long long ignore_index,
+                           bool write_grad, cudaStream_t stream);
+
+// ---- ops/attention_fwd.cu / attention_bwd.cu
+void attn_varlen_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
+                     const int* tile_table, int num_tiles, int T, int num_q_heads, int num_kv_heads, int head_dim,
+                     long long q_stride, long long kv_stride, long long o_stride, int q_group_stride_cols,
+                     float softmax_scale, bool causal, int* status, cudaStream_t stream);
+
+}  // namespace b200

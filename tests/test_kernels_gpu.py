@@ -1,0 +1,212 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from lm_engine.ops.build import load_extension
+
+    return load_extension()
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1000, 72, 328), (513, 1032, 2048)])
+def test_gemm_layouts(C, a_mn, b_mn, shape):
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    st = _status()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm(a_in, b_in, out, a_mn, b_mn, False, 1.0, st, 0)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert _rel_err(out, ref) < 6e-3
+    out32 = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    C.gemm(a_in, b_in, out32, a_mn, b_mn, False, 0.5, st, 0)
+    assert _rel_err(out32, 0.5 * ref) < 1e-5
+    base = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    acc = base.clone()
+    C.gemm(a_in, b_in, acc, a_mn, b_mn, True, 1.0, st, 0)
+    assert _rel_err(acc, base + ref) < 1e-5
+    assert st.item() == 0
+
+
+def test_gemm_persistent_many_tiles(C):
+    torch.manual_seed(1)
+    M, N, K = 4096, 4096, 1024
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    C.gemm(a, b, out, False, False, False, 1.0, st, 0)
+    ref = (a.float() @ b.float().t())
+    assert st.item() == 0
+    assert _rel_err(out, ref) < 6e-3
+    out2 = torch.empty_like(out)
+    C.gemm(a, b, out2, False, False, False, 1.0, st, 0)
+    assert torch.equal(out, out2)  # run-to-run determinism
+
+
+def test_gemm_strided_views(C):
+    torch.manual_seed(2)
+    big = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16)
+    a = big[:, 256:768]  # row stride 1024, 512 wide
+    w = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16)
+    outbuf = torch.zeros(300, 1024, device="cuda", dtype=torch.bfloat16)
+    out = outbuf[:, 128:512]
+    st = _status()
+    C.gemm(a, w, out, False, False, False, 1.0, st, 0)
+    assert st.item() == 0
+    assert _rel_err(out, a.float() @ w.float().t()) < 6e-3
+    assert outbuf[:, :128].abs().sum().item() == 0 and outbuf[:, 512:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("T,H", [(7, 64), (33, 4096), (5, 2560), (3, 8192), (2, 16384)])
+def test_rmsnorm(C, T, H):
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    y, rstd, h = C.rmsnorm_fwd(x, r, w, 1e-5, True)
+    hf = (x.float() + r.float()).to(torch.bfloat16).float()
+    assert torch.equal(h.float(), hf)
+    ref = torch.nn.functional.rms_norm(hf, (H,), w.float(), 1e-5)
+    assert _rel_err(y, ref) < 5e-3
+    y2, rstd2 = C.rmsnorm_fwd(x, None, w, 1e-5, True)
+    assert _rel_err(y2, torch.nn.functional.rms_norm(x.float(), (H,), w.float(), 1e-5)) < 5e-3
+    # backward
+    dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    dres = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    hh = hf.clone().requires_grad_(True)
+    ww = w.float().clone().requires_grad_(True)
+    torch.nn.functional.rms_norm(hh, (H,), ww, 1e-5).backward(dy.float())
+    dw = torch.zeros(H, device="cuda")
+    dh = C.rmsnorm_bwd(dy, h, w, rstd, dres, dw, False)
+    assert _rel_err(dh, hh.grad + dres.float()) < 6e-3
+    assert _rel_err(dw, ww.grad) < 2e-3
+    C.rmsnorm_bwd(dy, h, w, rstd, None, dw, True)
+    assert _rel_err(dw, 2 * ww.grad) < 2e-3
+
+
+def test_swiglu(C):
+    torch.manual_seed(0)
+    x = torch.randn(37, 2 * 264, device="cuda", dtype=torch.bfloat16)
+    xf = x.float().requires_grad_(True)
+    up, gate = xf.chunk(2, dim=-1)
+    ref = up * torch.nn.functional.silu(gate)
+    y = C.swiglu_fwd(x)
+    assert _rel_err(y, ref) < 5e-3
+    dy = torch.randn_like(y)
+    ref.backward(dy.float())
+    dx, y2 = C.swiglu_bwd(dy, x, True)
+    assert _rel_err(dx, xf.grad) < 6e-3
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("groups,qpg,d,rd", [(2, 4, 128, 128), (4, 1, 64, 64), (1, 8, 64, 32), (2, 1, 80, 80)])
+def test_rope(C, groups, qpg, d, rd):
+    torch.manual_seed(0)
+    T = 19
+    width = groups * (qpg + 2) * d
+    qkv = torch.randn(T, width, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 50, (T,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (10000 ** (torch.arange(0, rd, 2, device="cuda").float() / rd))
+    ang = torch.arange(64, device="cuda").float()[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().contiguous(), ang.sin().contiguous()
+    ref = qkv.float().view(T, groups, qpg + 2, d).clone()
+    c = torch.cat([cos_t, cos_t], -1)[pos.long()][:, None, None, :]
+    s = torch.cat([sin_t, sin_t], -1)[pos.long()][:, None, None, :]
+    xr = ref[:, :, : qpg + 1, d - rd :]
+    x1, x2 = xr.chunk(2, -1)
+    ref[:, :, : qpg + 1, d - rd :] = xr * c + torch.cat([-x2, x1], -1) * s
+    out = qkv.clone()
+    C.rope_(out, cos_t, sin_t, pos, groups, qpg, d, rd, False)
+    assert _rel_err(out, ref.view(T, width)) < 5e-3
+    # the inverse rotation undoes it (up to bf16 rounding)
+    C.rope_(out, cos_t, sin_t, pos, groups, qpg, d, rd, True)
+    assert _rel_err(out, qkv) < 8e-3
+
+
+def test_embedding(C):
+    torch.manual_seed(0)
+    w = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 1000, (4, 33), device="cuda")
+    out = C.embedding_fwd(w, ids, 1.0)
+    assert torch.equal(out, w[ids])
+    dy = torch.randn(4, 33, 256, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(1000, 256, device="cuda")
+    C.embedding_bwd(dy, ids, dw, 1.0)
+    ref = torch.zeros_like(dw).index_add_(0, ids.flatten(), dy.float().view(-1, 256))
+    assert _rel_err(dw, ref) < 1e-5
+
+
+@pytest.mark.parametrize("V", [1000, 50264, 128256])
+def test_cross_entropy(C, V):
+    torch.manual_seed(0)
+    T = 9
+    logits = (3 * torch.randn(T, V, device="cuda")).to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[3] = -100
+    lf = logits.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, labels, reduction="sum", ignore_index=-100)
+    ref.backward()
+    work = logits.clone()
+    loss = C.cross_entropy_(work, labels, 1.0, 1.0, -100, True)
+    assert abs(loss.sum().item() - ref.item()) / abs(ref.item()) < 2e-3
+    assert _rel_err(work, lf.grad) < 8e-3
+    assert work[3].abs().sum().item() == 0
+
+
+def test_adamw_and_norm(C):
+    torch.manual_seed(0)
+    n = 4096 * 3 + 8
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1)
+    m = torch.zeros_like(p)
+    v = torch.zeros_like(p)
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    total = torch.zeros(1, device="cuda")
+    coef = torch.zeros(1, device="cuda")
+    norm = torch.zeros(1, device="cuda")
+    for step in range(1, 4):
+        gg = g * step
+        ref_p.grad = gg.clone()
+        gn = torch.nn.utils.clip_grad_norm_([ref_p], 1.0)
+        opt.step()
+        mine_g = gg.clone()
+        C.sumsq(mine_g, total, False)
+        C.clip_coef(total, 1.0, coef, norm)
+        assert abs(norm.item() - gn.item()) / gn.item() < 1e-5
+        C.adamw_step(p, m, v, mine_g, pb, 1e-2, 0.9, 0.95, 1e-10, 0.1, step, coef, 1.0, True)
+        assert mine_g.abs().sum().item() == 0
+        assert _rel_err(p, ref_p.data) < 1e-5
+        assert torch.equal(pb, p.to(torch.bfloat16))
+
+
+def test_casts(C):
+    x = torch.randn(1003, device="cuda")
+    y = torch.empty(1003, device="cuda", dtype=torch.bfloat16)
+    C.cast_f32_to_bf16(x, y)
+    assert torch.equal(y, x.to(torch.bfloat16))
+    acc = torch.ones(1003, device="cuda")
+    C.cast_bf16_to_f32(y, acc, True, 0.5)
+    assert torch.allclose(acc, 1 + 0.5 * y.float())
