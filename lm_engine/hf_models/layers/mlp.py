@@ -1,0 +1,198 @@
+"""Feed-forward blocks: dense MLP and sparse mixture of experts.
+
+Parity: lm_engine/hf_models/modeling_utils/mlp_blocks/{mlp.py:15-73, moe.py:47-384}. MoE routing: logits ->
+top-k (max for k = 1) -> softmax over the k selected logits in fp32; no capacity limit, no token dropping.
+Expert weights are ``c_fc.weight [E, I or 2I, H]`` and ``c_proj.weight [E, H, I]``. The auxiliary loss is
+``E * sum(normalize(sum probs) * normalize(freq)) + 0.1 * mean(logsumexp(logits)^2)`` with ``freq`` summed over the
+data parallel group, accumulated into a per-forward global (see :mod:`lm_engine.hf_models.loss`).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ... import ops
+from ...enums import Kernel
+from ...kernels import is_kernel_allowed
+from ...utils import ProcessGroupManager
+from ..loss import add_aux_loss
+from ..parameter import mark_parameter_as_mup_learning_rate, mark_parameter_as_no_weight_decay
+from .activations import get_activation_function, is_glu
+from .basic import ParameterizedLinear
+
+
+def _std(initializer_range: float, init_method: str, m_width: float | None, depth_scale: int | None = None) -> float:
+    std = initializer_range
+    if depth_scale is not None:
+        std /= math.sqrt(2 * depth_scale)
+    if init_method == "mup":
+        std /= math.sqrt(m_width)
+    return std
+
+
+class MLP(nn.Module):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation_function: str, add_bias: bool,
+                 dropout: float, init_method: str, initializer_range: float, m_width: float | None,
+                 num_layers: int) -> None:
+        super().__init__()
+        self.is_glu = is_glu(activation_function)
+        self.c_fc = ParameterizedLinear(hidden_size, 2 * intermediate_size if self.is_glu else intermediate_size,
+                                        bias=add_bias, std=_std(initializer_range, init_method, m_width))
+        self.act = get_activation_function(activation_function)
+        self.c_proj = ParameterizedLinear(intermediate_size, hidden_size, bias=add_bias,
+                                          std=_std(initializer_range, init_method, m_width, num_layers))
+        self.dropout = nn.Identity() if dropout == 0 else nn.Dropout(dropout)
+        mark_parameter_as_mup_learning_rate(self.c_fc.weight)
+        mark_parameter_as_mup_learning_rate(self.c_proj.weight)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.dropout(self.c_proj(self.act(self.c_fc(x))))
+
+
+class ParameterizedExperts(nn.Module):
+    """A bank of ``num_experts`` linear maps stored as one ``[E, out, in]`` tensor."""
+
+    def __init__(self, num_experts: int, in_features: int, out_features: int, add_bias: bool = False,
+                 std: float | None = None) -> None:
+        super().__init__()
+        self.num_experts = num_experts
+        self.in_features = in_features
+        self.out_features = out_features
+        self.std = std
+        self.weight = nn.Parameter(torch.empty(num_experts, out_features, in_features))
+        self.bias = nn.Parameter(torch.empty(num_experts, out_features)) if add_bias else None
+        mark_parameter_as_no_weight_decay(self.bias)
+        self.reset_parameters()
+
+    @torch.no_grad()
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, mean=0.0, std=self.std if self.std is not None else 0.02)
+        if self.bias is not None:
+            self.bias.zero_()
+
+    def forward_grouped(self, x: torch.Tensor, tokens_per_expert: list[int]) -> torch.Tensor:
+        """``x`` holds the rows of expert 0, then expert 1, ...; one dense product per non-empty expert."""
+        outs = []
+        start = 0
+        for e, n in enumerate(tokens_per_expert):
+            if n == 0:
+                continue
+            b = None if self.bias is None else self.bias[e]
+            outs.append(F.linear(x[start : start + n], self.weight[e], b))
+            start += n
+        if not outs:
+            return x.new_zeros(0, self.out_features)
+        return torch.cat(outs, dim=0)
+
+    def extra_repr(self) -> str:
+        return f"num_experts={self.num_experts}, in_features={self.in_features}, out_features={self.out_features}"
+
+
+class MoE(nn.Module):
+    linear_class = ParameterizedExperts
+
+    def __init__(self, hidden_size: int, intermediate_size: int, shared_intermediate_size: int | None,
+                 num_experts: int, num_experts_per_tok: int, activation_function: str, add_bias: bool,
+                 dropout: float, init_method: str, initializer_range: float, m_width: float | None,
+                 num_layers: int, use_padding_free_transformer: bool) -> None:
+        super().__init__()
+        self.num_experts = num_experts
+        self.top_k = num_experts_per_tok
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.shared_intermediate_size = shared_intermediate_size
+        self.use_padding_free_transformer = use_padding_free_transformer
+        self.is_glu = is_glu(activation_function)
+        self.activation_function = activation_function
+        width = 2 if self.is_glu else 1
+
+        self.gate = ParameterizedLinear(hidden_size, num_experts, bias=False, std=_std(initializer_range, init_method, m_width))
+        self.c_fc = ParameterizedExperts(num_experts, hidden_size, width * intermediate_size, add_bias=add_bias,
+                                         std=_std(initializer_range, init_method, m_width))
+        if shared_intermediate_size is not None:
+            self.c_fc_shared = ParameterizedLinear(hidden_size, width * shared_intermediate_size, bias=add_bias,
+                                                   std=_std(initializer_range, init_method, m_width))
+        self.act = get_activation_function(activation_function)
+        self.c_proj = ParameterizedExperts(num_experts, intermediate_size, hidden_size, add_bias=add_bias,
+                                           std=_std(initializer_range, init_method, m_width, num_layers))
+        if shared_intermediate_size is not None:
+            self.c_proj_shared = ParameterizedLinear(shared_intermediate_size, hidden_size, bias=add_bias,
+                                                     std=_std(initializer_range, init_method, m_width, num_layers))
+        self.dropout = nn.Identity() if dropout == 0 else nn.Dropout(dropout)
+
+        for module in (self.gate, self.c_fc, self.c_proj):
+            mark_parameter_as_mup_learning_rate(module.weight)
+        if shared_intermediate_size is not None:
+            mark_parameter_as_mup_learning_rate(self.c_fc_shared.weight)
+            mark_parameter_as_mup_learning_rate(self.c_proj_shared.weight)
+
+    # ------------------------------------------------------------------ routing
+    def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        logits = self.gate(x)
+        if self.top_k == 1:
+            top_logits, experts = logits.max(dim=-1, keepdim=True)
+        else:
+            top_logits, experts = logits.topk(self.top_k, dim=-1)
+        weights = F.softmax(top_logits.float(), dim=-1).type_as(x)
+        return logits, weights, experts
+
+    # ------------------------------------------------------------------ experts
+    def _experts_torch(self, x: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor) -> torch.Tensor:
+        flat = experts.flatten()
+        counts = torch.bincount(flat, minlength=self.num_experts).tolist()
+        order = flat.argsort(stable=True)
+        token_of_row = order // self.top_k
+        h = self.c_fc.forward_grouped(x[token_of_row], counts)
+        h = self.act(h)
+        h = self.c_proj.forward_grouped(h, counts)
+        h = h * weights.flatten()[order].unsqueeze(-1)
+        return torch.zeros_like(x).index_add(0, token_of_row, h)
+
+    def _experts_native(self, x: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor) -> torch.Tensor:
+        from ...ops.moe import scattered_experts_mlp
+
+        return scattered_experts_mlp(x, self.c_fc.weight, self.c_proj.weight, weights, experts, self.num_experts,
+                                     self.top_k, self.activation_function)
+
+    def experts(self, x: torch.Tensor, weights: torch.Tensor, selected: torch.Tensor) -> torch.Tensor:
+        if is_kernel_allowed(Kernel.scattermoe) and self.c_fc.bias is None:
+            from ...ops.moe import native_moe_ok
+
+            if native_moe_ok(x, self.activation_function):
+                return self._experts_native(x, weights, selected)
+        return self._experts_torch(x, weights, selected)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_size)
+        logits, weights, selected = self.route(x)
+        out = self.experts(x, weights, selected)
+        if self.shared_intermediate_size is not None:
+            out = out + self.c_proj_shared(self.act(self.c_fc_shared(x)))
+        out = self.dropout(out.reshape(shape))
+        add_aux_loss(self._aux_loss(logits, selected) if self.training else 0)
+        return out
+
+    def _aux_loss(self, logits: torch.Tensor, selected: torch.Tensor) -> torch.Tensor:
+        logits = logits.reshape(-1, logits.shape[-1])
+        probs = torch.softmax(logits, dim=-1)
+        freq = torch.bincount(selected.flatten(), minlength=self.num_experts).float()
+        if ProcessGroupManager.is_initialized() and ProcessGroupManager.get_data_parallel_world_size() > 1:
+            freq = freq.clone()
+            dist.all_reduce(freq, group=ProcessGroupManager.get_data_parallel_group())
+        balance = self.num_experts * (F.normalize(probs.sum(0), p=1, dim=0) * F.normalize(freq, p=1, dim=0)).sum()
+        z = (torch.logsumexp(logits, dim=-1) ** 2).mean()
+        return (balance + 0.1 * z).type_as(logits)
+
+    def get_num_active_parameters(self) -> int:
+        total = sum(p.numel() for p in self.parameters())
+        for bank in (self.c_fc, self.c_proj):
+            for p in bank.parameters():
+                total -= p.numel()
+                total += (p.numel() * self.top_k) // self.num_experts
+        return total

@@ -1,0 +1,83 @@
+"""Language-modelling loss and the per-forward auxiliary-loss accumulator.
+
+Parity: lm_engine/hf_models/loss.py:23-116. ``get_autoregressive_language_modeling_loss`` optionally shifts
+logits/labels, masks the last token of every packed document when shifting, and picks between the fused
+linear+cross-entropy kernel (no ``[T, V]`` logits are kept), a cross-entropy on given logits, and a vocab-parallel
+variant under tensor parallelism.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..enums import Kernel
+from ..kernels import is_kernel_allowed
+
+_AUX_LOSS: torch.Tensor | float = 0
+
+
+def clear_aux_loss() -> None:
+    global _AUX_LOSS
+    _AUX_LOSS = 0
+
+
+def add_aux_loss(aux_loss: torch.Tensor | float) -> None:
+    global _AUX_LOSS
+    _AUX_LOSS = _AUX_LOSS + aux_loss
+
+
+def get_aux_loss() -> torch.Tensor | float:
+    return _AUX_LOSS
+
+
+def is_aux_loss_zero(aux_loss: torch.Tensor | float) -> bool:
+    return isinstance(aux_loss, (int, float)) and aux_loss == 0
+
+
+def get_autoregressive_language_modeling_loss(
+    lm_logits: torch.Tensor | None,
+    labels: torch.Tensor,
+    hidden_states: torch.Tensor | None = None,
+    vocab_weight: torch.Tensor | None = None,
+    cu_seqlens: torch.Tensor | None = None,
+    use_padding_free_transformer: bool = False,
+    reduction: str = "mean",
+    shift_logits_and_labels: bool = True,
+    tensor_parallel_enabled: bool = False,
+    logit_scale: float = 1.0,
+    grad_scale_hint: float | None = None,
+) -> torch.Tensor:
+    """Next-token cross entropy (ignored label = -100).
+
+    Either ``lm_logits`` or (``hidden_states``, ``vocab_weight``) must be given; the latter selects the fused
+    linear + cross-entropy path, where ``logit_scale`` (``1 / m_width``) is applied inside the kernel.
+    """
+    if reduction not in ("sum", "mean"):
+        raise ValueError(f"unexpected reduction ({reduction})")
+    fused = lm_logits is None
+    x = hidden_states if fused else lm_logits
+
+    if use_padding_free_transformer:
+        if shift_logits_and_labels:
+            if cu_seqlens is None:
+                raise ValueError("cu_seqlens is needed to shift labels of packed documents")
+            # token t predicts t + 1; the last token of every document predicts nothing
+            labels = torch.cat([labels[1:], labels.new_full((1,), -100)])
+            labels[cu_seqlens[1:] - 1] = -100
+    elif shift_logits_and_labels:
+        x = x[..., :-1, :]
+        labels = labels[..., 1:]
+
+    if tensor_parallel_enabled and not fused:
+        from ..parallel.tensor_parallel import vocab_parallel_cross_entropy
+
+        return vocab_parallel_cross_entropy(x, labels, reduction=reduction)
+
+    if fused:
+        return ops.fused_linear_cross_entropy(x, vocab_weight, labels, logit_scale=logit_scale, reduction=reduction,
+                                              grad_scale_hint=grad_scale_hint)
+    if logit_scale != 1.0:
+        x = x * logit_scale
+    return ops.cross_entropy(x, labels, reduction=reduction)

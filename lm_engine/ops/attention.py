@@ -1,0 +1,79 @@
+"""Causal softmax attention over packed (padding-free) sequences.
+
+Native path: tcgen05 forward/backward kernels that read q, k and v straight out of the fused projection buffer
+(layout ``[T, groups, (q_per_group + 2), head_dim]``) through strided TMA maps, so no head split/copy is made.
+Oracle / CPU path: per-document ``scaled_dot_product_attention`` in the input dtype.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import native, native_available, status_word
+
+
+def split_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int):
+    """Views of q ``[T, groups*qpg, d]``, k and v ``[T, groups, d]`` inside a fused projection."""
+    T = qkv.shape[0]
+    v4 = qkv.view(T, groups, qpg + 2, d)
+    q = v4[:, :, :qpg].reshape(T, groups * qpg, d)
+    k = v4[:, :, qpg]
+    v = v4[:, :, qpg + 1]
+    return q, k, v
+
+
+def attention_varlen_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                               scale: float | None, causal: bool = True, dropout_p: float = 0.0) -> torch.Tensor:
+    """q ``[T, hq, d]``, k/v ``[T, hkv, d]`` -> ``[T, hq, d]``; documents delimited by ``cu_seqlens``."""
+    bounds = cu_seqlens.tolist()
+    outs = []
+    hq, hkv = q.shape[1], k.shape[1]
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        if e == s:
+            continue
+        qi = q[s:e].transpose(0, 1).unsqueeze(0)
+        ki = k[s:e].transpose(0, 1).unsqueeze(0)
+        vi = v[s:e].transpose(0, 1).unsqueeze(0)
+        if hq != hkv:
+            ki = ki.repeat_interleave(hq // hkv, dim=1)
+            vi = vi.repeat_interleave(hq // hkv, dim=1)
+        o = F.scaled_dot_product_attention(qi, ki, vi, is_causal=causal, scale=scale, dropout_p=dropout_p)
+        outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, dim=0)
+
+
+def _native_attention_ok(qkv: torch.Tensor, d: int) -> bool:
+    if not (native_available() and qkv.is_cuda and qkv.dtype == torch.bfloat16):
+        return False
+    return hasattr(native(), "attn_fwd") and d in (64, 128) and qkv.stride(-1) == 1 and qkv.stride(0) % 8 == 0
+
+
+class _FusedQKVAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cu_seqlens, max_seqlen, groups, qpg, d, scale, causal):
+        C = native()
+        out, lse = C.attn_fwd(qkv, cu_seqlens, int(max_seqlen), groups, qpg, d, float(scale), causal, status_word(qkv.device))
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens)
+        ctx.meta = (int(max_seqlen), groups, qpg, d, float(scale), causal)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, cu_seqlens = ctx.saved_tensors
+        max_seqlen, groups, qpg, d, scale, causal = ctx.meta
+        dqkv = native().attn_bwd(dout.contiguous(), qkv, out, lse, cu_seqlens, max_seqlen, groups, qpg, d, scale, causal, status_word(qkv.device))
+        return dqkv, None, None, None, None, None, None, None
+
+
+def attention_fused_qkv(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, groups: int, qpg: int, d: int,
+                        scale: float | None = None, causal: bool = True, dropout_p: float = 0.0) -> torch.Tensor:
+    """Attention over a fused projection ``[T, groups*(qpg+2)*d]`` -> ``[T, groups*qpg*d]``."""
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if dropout_p == 0.0 and _native_attention_ok(qkv, d):
+        return _FusedQKVAttentionFn.apply(qkv, cu_seqlens.to(torch.int32), max_seqlen, groups, qpg, d, scale, causal)
+    q, k, v = split_fused_qkv(qkv, groups, qpg, d)
+    out = attention_varlen_reference(q, k, v, cu_seqlens, scale, causal, dropout_p)
+    return out.reshape(qkv.shape[0], groups * qpg * d)
