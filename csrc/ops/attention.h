@@ -1,0 +1,21 @@
+// Launch interface of the packed-sequence attention kernels (attention_fwd.cu, attention_bwd.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace b200 {
+
+// qkv: fused projection [T, groups * (qpg + 2) * head_dim] bf16 (row stride qkv_stride elements).
+// out: [T, groups * qpg * head_dim] bf16. lse: [groups * qpg, T] fp32 (natural log).
+void attn_varlen_fwd(const void* qkv, long long qkv_stride, void* out, long long out_stride, float* lse,
+                     const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale,
+                     bool causal, int* status, cudaStream_t stream);
+
+// dout/out: [T, groups * qpg * head_dim] bf16; dqkv: same layout as qkv (every element is written).
+// delta: scratch [groups * qpg, T] fp32; dq_accum: scratch [T, groups * qpg * head_dim] fp32.
+void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, const void* out, long long out_stride,
+                     const float* lse, float* delta, float* dq_accum, void* dqkv, long long dqkv_stride,
+                     const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale,
+                     bool causal, int* status, cudaStream_t stream);
+
+}  // namespace b200

@@ -1,0 +1,430 @@
+// Causal softmax attention backward over packed variable-length sequences (sm_100a).
+//
+// One CTA owns 128 keys of one document and one key/value head. K and V stay resident in shared memory;
+// the CTA walks the query heads of the group and, for each, the query tiles that can see these keys:
+//   S^T  = K Q^T,  dP^T = V dO^T                      (tcgen05, fp32 in TMEM)
+//   P^T  = exp2(S^T * scale*log2e - lse*log2e),  dS^T = P^T o (dP^T - delta) * scale   (128 threads, row = key)
+//   dV  += P^T dO,  dK += dS^T Q,  dQ_tile = dS K       (tcgen05; dQ goes out through fp32 vector atomics)
+// The tiles of dS^T / Q / dO / K are each loaded or written once and reused through a second descriptor with
+// the other major-ness (e.g. dS^T is the K-major A operand of dK and the MN-major A operand of dQ).
+// Two small kernels bracket it: delta = rowsum(dO o O) before, fp32 dQ -> bf16 into the fused gradient after.
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
+#include "../common/tensor_map.h"
+#include "attention.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BT = 128;  // tile edge for both queries and keys
+constexpr int BWD_THREADS = 192;
+
+template <int D>
+struct BwdSmem {
+  static constexpr int TILE_D = BT * D * 2;    // a [128 x D] bf16 tile
+  static constexpr int TILE_S = BT * BT * 2;   // a [128 x 128] bf16 tile
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + TILE_D;
+  static constexpr int OFF_Q = OFF_V + TILE_D;
+  static constexpr int OFF_DO = OFF_Q + TILE_D;
+  static constexpr int OFF_P = OFF_DO + TILE_D;
+  static constexpr int OFF_DS = OFF_P + TILE_S;
+  static constexpr int OFF_ROW = OFF_DS + TILE_S;       // per softmax warp: lse[128], delta[128] floats
+  static constexpr int OFF_BAR = OFF_ROW + 8 * BT * 4;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 2, B_SDP_FULL = 3, B_PDS_READY = 4, B_MMA2_DONE = 5, B_DQ_DRAINED = 6, B_COUNT = 7 };
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                    const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dq_accum,
+                    __nv_bfloat16* __restrict__ dqkv, long long dqkv_stride, const int* __restrict__ cu_seqlens,
+                    int num_docs, int T, int groups, int qpg, float scale, float scale_log2, int causal, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using L = BwdSmem<D>;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sDO = smem + L::OFF_DO;
+  uint8_t* sP = smem + L::OFF_P;
+  uint8_t* sDS = smem + L::OFF_DS;
+  float* s_rows = reinterpret_cast<float*>(smem + L::OFF_ROW);  // [4 warps][lse 128 | delta 128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_tile = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int grp = blockIdx.y;  // key/value head
+  const int k_col = (grp * (qpg + 2) + qpg) * D;
+  const int v_col = k_col + D;
+  const int hq_total = groups * qpg;
+
+  if (threadIdx.x == 0) {
+    const int want = blockIdx.x;  // early key tiles see the most queries: hand them out first
+    int acc = 0, found = -1, start = 0, len = -1, kt = 0;
+    for (int b = 0; b < num_docs; ++b) {
+      const int s = cu_seqlens[b], e = cu_seqlens[b + 1];
+      const int nt = (e - s + BT - 1) / BT;
+      if (want < acc + nt) {
+        found = b;
+        start = s;
+        len = e - s;
+        kt = want - acc;
+        break;
+      }
+      acc += nt;
+    }
+    s_tile[0] = start;
+    s_tile[1] = found < 0 ? -1 : len;
+    s_tile[2] = kt;
+    mbar_init(&bars[B_KV], 1);
+    mbar_init(&bars[B_QDO_FULL], 1);
+    mbar_init(&bars[B_QDO_EMPTY], 1);
+    mbar_init(&bars[B_SDP_FULL], 1);
+    mbar_init(&bars[B_PDS_READY], 128);
+    mbar_init(&bars[B_MMA2_DONE], 1);
+    mbar_init(&bars[B_DQ_DRAINED], 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const int doc_start = s_tile[0];
+  const int doc_len = s_tile[1];
+  const int kv_tile = s_tile[2];
+  if (doc_len <= 0) return;
+
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;             // 128 cols, later reused for dQ (D cols)
+  const uint32_t tmem_dP = tmem_base + BT;       // 128 cols
+  const uint32_t tmem_dV = tmem_base + 2 * BT;   // D cols
+  const uint32_t tmem_dK = tmem_base + 2 * BT + D;  // D cols
+
+  const int kv0 = kv_tile * BT;
+  const int n_q_tiles = (doc_len + BT - 1) / BT;
+  const int first_q_tile = causal ? kv_tile : 0;
+  const int tiles_per_head = n_q_tiles - first_q_tile;
+  const int n_iter = tiles_per_head * qpg;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_qkv);
+      tma_prefetch_desc(&tm_do);
+      mbar_arrive_expect_tx(&bars[B_KV], 2 * L::TILE_D);
+#pragma unroll
+      for (int kb = 0; kb < D / 64; ++kb) {
+        tma_load_2d(sK + kb * (BT * 128), &tm_qkv, &bars[B_KV], k_col + kb * 64, doc_start + kv0);
+        tma_load_2d(sV + kb * (BT * 128), &tm_qkv, &bars[B_KV], v_col + kb * 64, doc_start + kv0);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int qh = it / tiles_per_head;
+        const int qt = first_q_tile + it % tiles_per_head;
+        if (!mbar_wait(&bars[B_QDO_EMPTY], (it & 1) ^ 1, abort_flag)) {
+          raise_status(status, kStatusWaitTimeoutProducer, abort_flag);
+          break;
+        }
+        mbar_arrive_expect_tx(&bars[B_QDO_FULL], 2 * L::TILE_D);
+        const int q_col = (grp * (qpg + 2) + qh) * D;
+        const int do_col = (grp * qpg + qh) * D;
+        const int row = doc_start + qt * BT;
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb) {
+          tma_load_2d(sQ + kb * (BT * 128), &tm_qkv, &bars[B_QDO_FULL], q_col + kb * 64, row);
+          tma_load_2d(sDO + kb * (BT * 128), &tm_do, &bars[B_QDO_FULL], do_col + kb * 64, row);
+        }
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = umma_idesc_bf16(BT, BT, 0, 0);  // S^T = K Q^T, dP^T = V dO^T
+      constexpr uint32_t idesc_kv = umma_idesc_bf16(BT, D, 0, 1);   // dV = P^T dO, dK = dS^T Q   (B MN-major)
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(BT, D, 1, 1);   // dQ = dS K                 (A and B MN-major)
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+      const uint32_t p_base = smem_u32(sP), ds_base = smem_u32(sDS);
+      bool ok = mbar_wait(&bars[B_KV], 0, abort_flag);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(&bars[B_QDO_FULL], ph, abort_flag)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(&bars[B_DQ_DRAINED], (it - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (BT * 128) + (k % 4) * 32;
+          umma_f16_ss(tmem_S, umma_smem_desc_sw128(k_base + off, 16, 1024), umma_smem_desc_sw128(q_base + off, 16, 1024),
+                      idesc_st, k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (BT * 128) + (k % 4) * 32;
+          umma_f16_ss(tmem_dP, umma_smem_desc_sw128(v_base + off, 16, 1024), umma_smem_desc_sw128(do_base + off, 16, 1024),
+                      idesc_st, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&bars[B_SDP_FULL]);
+
+        if (!mbar_wait(&bars[B_PDS_READY], ph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;  // K-major A: 16 query columns per step
+          const uint32_t b_off = k * 16 * 128;                          // MN-major B: 16 query rows per step
+          umma_f16_ss(tmem_dV, umma_smem_desc_sw128(p_base + a_off, 16, 1024),
+                      umma_smem_desc_sw128(do_base + b_off, BT * 128, 1024), idesc_kv, (acc | (k != 0)) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;
+          const uint32_t b_off = k * 16 * 128;
+          umma_f16_ss(tmem_dK, umma_smem_desc_sw128(ds_base + a_off, 16, 1024),
+                      umma_smem_desc_sw128(q_base + b_off, BT * 128, 1024), idesc_kv, (acc | (k != 0)) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t off = k * 16 * 128;  // 16 key rows per step for both operands
+          umma_f16_ss(tmem_S, umma_smem_desc_sw128(ds_base + off, BT * 128, 1024),
+                      umma_smem_desc_sw128(k_base + off, BT * 128, 1024), idesc_dq, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&bars[B_QDO_EMPTY]);
+        umma_commit(&bars[B_MMA2_DONE]);
+      }
+      if (!ok) raise_status(status, kStatusWaitTimeoutMma, abort_flag);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- P / dS producers, dQ drain, final dK / dV
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;  // key row inside the tile (S^T, dV, dK) / query row inside the tile (dQ)
+    const int kv_local = kv0 + r;
+    const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
+    const bool kv_valid = kv_local < doc_len;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int qh = it / tiles_per_head;
+      const int qt = first_q_tile + it % tiles_per_head;
+      const int head = grp * qpg + qh;
+      const int q0 = qt * BT;
+      // Each warp stages the per-query statistics of this tile for itself (no cross-warp barrier needed).
+      float* w_lse = s_rows + q4 * (2 * BT);
+      float* w_delta = w_lse + BT;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < BT / 32; ++i) {
+        const int col = i * 32 + lane;
+        const int ql = q0 + col;
+        const bool v = ql < doc_len;
+        w_lse[col] = v ? lse[(long long)head * T + doc_start + ql] * 1.4426950408889634f : INFINITY;
+        w_delta[col] = v ? delta[(long long)head * T + doc_start + ql] : 0.f;
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars[B_SDP_FULL], it & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const bool needs_mask = causal && (q0 < kv0 + BT - 1);  // only the diagonal tile
+#pragma unroll 1
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t sv[32], dpv[32];
+        B200_TMEM_LD_32(sv, tmem_S + lane_addr + c * 32);
+        B200_TMEM_LD_32(dpv, tmem_dP + lane_addr + c * 32);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + e + u;  // query column inside the tile
+            float p = exp2f(__uint_as_float(sv[e + u]) * scale_log2 - w_lse[col]);
+            if (!kv_valid || (needs_mask && kv_local > q0 + col)) p = 0.f;
+            pv[u] = p;
+            dv[u] = p * (__uint_as_float(dpv[e + u]) - w_delta[col]) * scale;
+          }
+          pp[e / 2] = pack_bf16x2(pv[0], pv[1]);
+          dd[e / 2] = pack_bf16x2(dv[0], dv[1]);
+        }
+        // 32 columns = half of a 64-column K block: four 16-byte chunks of this thread's row
+        const int kb = c >> 1;
+        uint8_t* prow = sP + kb * (BT * 128) + r * 128;
+        uint8_t* drow = sDS + kb * (BT * 128) + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = ((c & 1) * 4 + ch) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[B_PDS_READY]);
+
+      if (!mbar_wait(&bars[B_MMA2_DONE], it & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      {
+        // dQ rows of this query tile: lane r <-> query row r
+        const int ql = q0 + r;
+        float* dst = dq_accum + (long long)(doc_start + ql) * ((long long)hq_total * D) + (long long)head * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          B200_TMEM_LD_32(o, tmem_S + lane_addr + c * 32);
+          tmem_ld_wait();
+          if (ql < doc_len) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              atomicAdd(reinterpret_cast<float4*>(dst + c * 32) + e,
+                        make_float4(__uint_as_float(o[4 * e]), __uint_as_float(o[4 * e + 1]), __uint_as_float(o[4 * e + 2]),
+                                    __uint_as_float(o[4 * e + 3])));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&bars[B_DQ_DRAINED]);
+    }
+    if (!ok) {
+      raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
+    } else {
+      // dK and dV of this key tile (all MMAs retired: the last MMA2_DONE wait above)
+      tc_fence_after_sync();
+      __nv_bfloat16* krow = dqkv + (long long)(doc_start + kv_local) * dqkv_stride + k_col;
+      __nv_bfloat16* vrow = krow + D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t a[32], b[32];
+        B200_TMEM_LD_32(a, tmem_dK + lane_addr + c * 32);
+        B200_TMEM_LD_32(b, tmem_dV + lane_addr + c * 32);
+        tmem_ld_wait();
+        if (kv_valid) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint4 wk, wv;
+            wk.x = pack_bf16x2(__uint_as_float(a[8 * e + 0]), __uint_as_float(a[8 * e + 1]));
+            wk.y = pack_bf16x2(__uint_as_float(a[8 * e + 2]), __uint_as_float(a[8 * e + 3]));
+            wk.z = pack_bf16x2(__uint_as_float(a[8 * e + 4]), __uint_as_float(a[8 * e + 5]));
+            wk.w = pack_bf16x2(__uint_as_float(a[8 * e + 6]), __uint_as_float(a[8 * e + 7]));
+            wv.x = pack_bf16x2(__uint_as_float(b[8 * e + 0]), __uint_as_float(b[8 * e + 1]));
+            wv.y = pack_bf16x2(__uint_as_float(b[8 * e + 2]), __uint_as_float(b[8 * e + 3]));
+            wv.z = pack_bf16x2(__uint_as_float(b[8 * e + 4]), __uint_as_float(b[8 * e + 5]));
+            wv.w = pack_bf16x2(__uint_as_float(b[8 * e + 6]), __uint_as_float(b[8 * e + 7]));
+            reinterpret_cast<uint4*>(krow + c * 32)[e] = wk;
+            reinterpret_cast<uint4*>(vrow + c * 32)[e] = wv;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                  float* __restrict__ delta, int T, int H, int D, long long stride) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= T * H) return;
+  const int t = w / H, h = w - t * H;
+  const __nv_bfloat16* a = dout + (long long)t * stride + (long long)h * D;
+  const __nv_bfloat16* b = out + (long long)t * stride + (long long)h * D;
+  float s = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + i));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(b + i));
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(long long)h * T + t] = s;
+}
+
+// dqkv[t, q columns] = bf16(dq_accum[t, :]) for every query head of every group.
+__global__ void attn_dq_convert_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dqkv,
+                                       long long dqkv_stride, int T, int groups, int qpg, int D) {
+  const int per_row = groups * qpg * D / 4;
+  const long long total = (long long)T * per_row;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_row);
+    const int c = (int)(idx - (long long)t * per_row) * 4;  // column inside [hq * D]
+    const int head = c / D, within = c - head * D;
+    const int grp = head / qpg, qh = head - grp * qpg;
+    const float4 v = reinterpret_cast<const float4*>(dq_accum)[idx];
+    __nv_bfloat16* dst = dqkv + (long long)t * dqkv_stride + ((long long)grp * (qpg + 2) + qh) * D + within;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
+template <int D>
+void launch_bwd(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do, const float* lse, const float* delta, float* dq_accum,
+                void* dqkv, long long dqkv_stride, const int* cu_seqlens, int num_docs, int T, int groups, int qpg,
+                float scale, bool causal, int* status, cudaStream_t stream) {
+  auto kernel = attn_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL), "attn_bwd smem attr");
+    configured = true;
+  }
+  const int tiles_upper = (T + BT - 1) / BT + num_docs;
+  dim3 grid(tiles_upper, groups);
+  kernel<<<grid, BWD_THREADS, BwdSmem<D>::TOTAL, stream>>>(tm_qkv, tm_do, lse, delta, dq_accum,
+                                                           reinterpret_cast<__nv_bfloat16*>(dqkv), dqkv_stride, cu_seqlens,
+                                                           num_docs, T, groups, qpg, scale, scale * 1.4426950408889634f,
+                                                           causal ? 1 : 0, status);
+  check_cuda(cudaGetLastError(), "attn_bwd launch");
+}
+
+}  // namespace
+
+void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, const void* out, long long out_stride,
+                     const float* lse, float* delta, float* dq_accum, void* dqkv, long long dqkv_stride,
+                     const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale,
+                     bool causal, int* status, cudaStream_t stream) {
+  if (T == 0 || num_docs == 0) return;
+  const int hq = groups * qpg;
+  const long long width = (long long)groups * (qpg + 2) * head_dim;
+  {
+    const long long warps = (long long)T * hq;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                                reinterpret_cast<const __nv_bfloat16*>(out), delta, T, hq,
+                                                                head_dim, out_stride);
+  }
+  check_cuda(cudaMemsetAsync(dq_accum, 0, (size_t)T * hq * head_dim * sizeof(float), stream), "dq_accum memset");
+  const CUtensorMap tm_qkv = make_tensor_map_2d_b16(qkv, width, T, qkv_stride, 64, BT);
+  const CUtensorMap tm_do = make_tensor_map_2d_b16(dout, (long long)hq * head_dim, T, out_stride, 64, BT);
+  if (head_dim == 128) launch_bwd<128>(tm_qkv, tm_do, lse, delta, dq_accum, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
+  else if (head_dim == 64) launch_bwd<64>(tm_qkv, tm_do, lse, delta, dq_accum, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
+  else throw std::runtime_error("attn_varlen_bwd: head_dim must be 64 or 128");
+  {
+    const long long total = (long long)T * hq * head_dim / 4;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    attn_dq_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_accum, reinterpret_cast<__nv_bfloat16*>(dqkv), dqkv_stride,
+                                                                T, groups, qpg, head_dim);
+  }
+  count_launch(3);
+  check_cuda(cudaGetLastError(), "attn_bwd tail launch");
+}
+
+}  // namespace b200

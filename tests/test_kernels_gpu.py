@@ -210,3 +210,50 @@ def test_casts(C):
     acc = torch.ones(1003, device="cuda")
     C.cast_bf16_to_f32(y, acc, True, 0.5)
     assert torch.allclose(acc, 1 + 0.5 * y.float())
+
+
+def _attention_reference(qkv, cu, groups, qpg, d, scale, causal=True):
+    """fp32 per-document softmax attention on the fused layout; returns (out, dqkv given dout) helpers."""
+    T = qkv.shape[0]
+    x = qkv.float().view(T, groups, qpg + 2, d)
+    q = x[:, :, :qpg].reshape(T, groups * qpg, d)
+    k = x[:, :, qpg].repeat_interleave(qpg, dim=1)
+    v = x[:, :, qpg + 1].repeat_interleave(qpg, dim=1)
+    outs = []
+    bounds = cu.tolist()
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        qi, ki, vi = (t[s:e].transpose(0, 1) for t in (q, k, v))
+        att = (qi @ ki.transpose(1, 2)) * scale
+        if causal:
+            n = e - s
+            att = att.masked_fill(torch.ones(n, n, device=att.device, dtype=torch.bool).triu(1), float("-inf"))
+        outs.append((att.softmax(-1) @ vi).transpose(0, 1))
+    return torch.cat(outs, 0).reshape(T, groups * qpg * d)
+
+
+@pytest.mark.parametrize("groups,qpg,d", [(2, 4, 128), (3, 1, 64), (1, 2, 64), (2, 1, 128)])
+@pytest.mark.parametrize("lengths", [[128], [300, 128, 77, 1000], [1, 2, 129, 255, 256, 257]])
+def test_attention_fwd_bwd(C, groups, qpg, d, lengths):
+    torch.manual_seed(0)
+    T = sum(lengths)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device="cuda")
+    width = groups * (qpg + 2) * d
+    qkv = torch.randn(T, width, device="cuda", dtype=torch.bfloat16)
+    scale = d**-0.5
+    st = _status()
+    out, lse = C.attn_fwd(qkv, cu, max(lengths), groups, qpg, d, scale, True, st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    q32 = qkv.float().requires_grad_(True)
+    ref = _attention_reference(q32, cu, groups, qpg, d, scale)
+    assert _rel_err(out, ref) < 1e-2
+    dout = torch.randn_like(out)
+    ref.backward(dout.float())
+    dqkv = C.attn_bwd(dout, qkv, out, lse, cu, max(lengths), groups, qpg, d, scale, True, st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    g = q32.grad.view(T, groups, qpg + 2, d)
+    mine = dqkv.float().view(T, groups, qpg + 2, d)
+    assert _rel_err(mine[:, :, qpg + 1], g[:, :, qpg + 1]) < 2e-2  # dV
+    assert _rel_err(mine[:, :, qpg], g[:, :, qpg]) < 2e-2  # dK
+    assert _rel_err(mine[:, :, :qpg], g[:, :, :qpg]) < 2e-2  # dQ
