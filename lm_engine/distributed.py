@@ -1,0 +1,68 @@
+"""Turns a model container into its distributed-training form.
+
+Parity: lm_engine/distributed.py:140-426 (``wrap_model_container_for_distributed_training``). Where the reference
+hands the model to FSDP2 / torch pipelining, this engine installs its own :class:`ShardedTrainingEngine` on every
+wrapper (flat sharded storage, explicit collectives) and, for pipeline parallel, its own 1F1B schedule.
+"""
+
+from __future__ import annotations
+
+import logging
+
+import torch
+
+from .containers import ModelContainer
+from .gradient_checkpointing import apply_gradient_checkpointing
+from .optimization.params_group import GROUP_ORDER, get_group_function
+from .parallel.engine import ShardedTrainingEngine
+from .utils import ProcessGroupManager, log_rank_0, string_to_torch_dtype
+
+
+def wrap_model_container_for_distributed_training(args, model_container: ModelContainer):
+    dist_args = args.distributed_args
+    dtype = string_to_torch_dtype(args.mixed_precision_args.dtype)
+    comm_dtype = None if dist_args.communication_dtype is None else string_to_torch_dtype(dist_args.communication_dtype)
+    if dist_args.stage not in (0, 2, 3):
+        raise ValueError(f"unexpected ZeRO stage ({dist_args.stage})")
+    if dist_args.cpu_offload:
+        log_rank_0(logging.WARN, "cpu_offload is ignored: optimizer state shards stay in device memory")
+
+    device = ProcessGroupManager.get_device()
+    group_of = get_group_function(args.optimizer_args.params_group_method)
+    frozen = ("teacher_model.",)
+
+    for wrapper in model_container:
+        if dist_args.gradient_checkpointing_method is not None:
+            block_names = getattr(wrapper.model, "_no_split_modules", ["Block"])
+            apply_gradient_checkpointing(wrapper.model, dist_args.gradient_checkpointing_method,
+                                         block_name=block_names[0], **dist_args.gradient_checkpointing_args)
+        for name, p in wrapper.named_parameters():
+            if name.startswith(frozen):
+                p.requires_grad_(False)
+        engine = ShardedTrainingEngine(
+            wrapper,
+            compute_dtype=dtype,
+            zero_stage=dist_args.stage,
+            device=device,
+            block_class_names=getattr(wrapper.model, "_no_split_modules", None),
+            group_of=group_of,
+            group_order=GROUP_ORDER,
+            communication_dtype=comm_dtype,
+            fused_collectives=dist_args.fused_collectives,
+            frozen_prefixes=frozen,
+        )
+        wrapper._lm_engine = engine
+        wrapper.model._lm_engine = engine
+        if hasattr(wrapper, "teacher_model") and wrapper.teacher_model is not None:
+            wrapper.teacher_model.to(device)
+        log_rank_0(logging.INFO, f"sharded engine: {engine.memory_summary()}")
+
+    pipeline_schedule = None
+    if dist_args.num_pipeline_stages > 1:
+        from .parallel.pipeline import build_pipeline_schedule
+
+        pipeline_schedule = build_pipeline_schedule(args, model_container)
+
+    if dist_args.torch_compile:
+        log_rank_0(logging.WARN, "torch_compile is ignored: hot ops run hand-written kernels, not Inductor output")
+    return model_container, pipeline_schedule

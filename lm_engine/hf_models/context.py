@@ -25,6 +25,18 @@ class SequenceContext:
     rope_cos_sin: tuple[torch.Tensor, torch.Tensor] | None = None  # gathered per position, broadcastable to heads
     rope_half_tables: tuple[torch.Tensor, torch.Tensor] | None = None  # fp32 [max_pos, rope_dim/2]
     _bool_mask: torch.Tensor | None = field(default=None, repr=False)
+    _pos_i32: torch.Tensor | None = field(default=None, repr=False)
+    _cu_i32: torch.Tensor | None = field(default=None, repr=False)
+
+    def position_ids_int32(self) -> torch.Tensor:
+        if self._pos_i32 is None:
+            self._pos_i32 = self.position_ids.to(torch.int32).contiguous()
+        return self._pos_i32
+
+    def cu_seqlens_int32(self) -> torch.Tensor:
+        if self._cu_i32 is None:
+            self._cu_i32 = self.cu_seqlens.to(torch.int32).contiguous()
+        return self._cu_i32
 
     @property
     def past_length(self) -> int:

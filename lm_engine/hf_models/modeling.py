@@ -71,8 +71,48 @@ class Block(nn.Module):
         self.sequence_mixer = get_sequence_mixer(config, True, use_padding_free_transformer, layer_idx)
         self.ln_2 = get_normalization_function(config.normalization_function, config.hidden_size, eps=config.layer_norm_epsilon)
         self.mlp_block = get_mlp_block(config, use_padding_free_transformer=use_padding_free_transformer, layer_idx=layer_idx)
+        self._fusable = self._statically_fusable(config, layer_idx)
+
+    def _statically_fusable(self, config: CommonConfig, layer_idx: int) -> bool:
+        """The whole-block kernel schedule covers: RMSNorm, bias-free softmax attention with head width 64/128 and
+        rope/nope positions, bias-free SwiGLU MLP, no dropout, no residual multiplier."""
+        mixer = config.sequence_mixer_blocks[layer_idx]
+        mlp = config.mlp_blocks[layer_idx]
+        if config.normalization_function != "rmsnorm" or config.m_residual is not None:
+            return False
+        if mixer.sequence_mixer_type != "softmax_attention" or mlp.mlp_type != "MLP":
+            return False
+        if mixer.add_bias or mixer.dropout != 0 or mixer.softmax_dropout != 0:
+            return False
+        if mlp.add_bias or mlp.dropout != 0 or mlp.activation_function != "swiglu":
+            return False
+        head_dim = config.hidden_size // mixer.num_attention_heads
+        if head_dim not in (64, 128) or config.position_embedding_type not in ("rope", "nope"):
+            return False
+        if config.position_embedding_type == "rope" and (config.rope_dim % 16 != 0 or config.rope_dim > head_dim):
+            return False
+        return config.hidden_size % 8 == 0 and mlp.intermediate_size % 8 == 0
+
+    def _forward_fused(self, x: torch.Tensor, ctx: SequenceContext) -> torch.Tensor:
+        from ..ops.fused_block import fused_dense_block
+
+        att = self.sequence_mixer
+        cos = sin = None
+        rope_dim = 0
+        if att.position_embedding_type == "rope":
+            cos, sin = ctx.rope_half_tables
+            rope_dim = cos.shape[-1] * 2
+        pos = None if ctx.position_ids is None else ctx.position_ids_int32()
+        return fused_dense_block(
+            x, self.ln_1.weight, att.c_attn.weight, att.c_proj.weight, self.ln_2.weight, self.mlp_block.c_fc.weight,
+            self.mlp_block.c_proj.weight, cos, sin, pos, ctx.cu_seqlens_int32(), ctx.max_seqlen,
+            att.num_key_value_heads, att.group_size, att.head_dim, rope_dim, att.softmax_scale, self.ln_1.eps)
 
     def forward(self, hidden_states: torch.Tensor, ctx: SequenceContext, past_key_values: GenerationCache | None = None) -> torch.Tensor:
+        if (self._fusable and ctx.packed and past_key_values is None and hidden_states.is_cuda
+                and hidden_states.dtype == torch.bfloat16 and hidden_states.dim() == 2
+                and is_kernel_allowed(Kernel.fused_block) and ops.native_available()):
+            return self._forward_fused(hidden_states.contiguous(), ctx)
         residual = hidden_states
         hidden_states = self.ln_1(hidden_states)
         hidden_states = self.sequence_mixer(hidden_states, ctx, past_key_values)

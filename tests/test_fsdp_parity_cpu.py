@@ -1,0 +1,34 @@
+"""The tiny gpt_base pretraining config gives the same 20-step loss curve in one process and on two CPU ranks
+(gloo) with sharded parameters, gradients and optimizer state."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+SCRIPT = os.path.join(os.path.dirname(__file__), "scripts", "tiny_pretrain.py")
+
+
+def _run(tmp_path, world: int, port: int, stage: int = 3):
+    out = tmp_path / f"curve_w{world}_s{stage}.json"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+    if world == 1:
+        cmd = [sys.executable, SCRIPT, str(out), "8", "20", str(stage)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), SCRIPT, str(out), "8", "20", str(stage)]
+    subprocess.run(cmd, check=True, env=env, timeout=600, capture_output=True)
+    return json.loads(out.read_text())
+
+
+@pytest.mark.parametrize("stage", [3, 0])
+def test_two_rank_loss_curve_matches_single_process(tmp_path, stage):
+    single = _run(tmp_path, 1, 29631, stage)
+    double = _run(tmp_path, 2, 29633 + stage, stage)
+    assert len(single) == len(double) == 20
+    for a, b in zip(single, double):
+        assert abs(a["loss"] - b["loss"]) < 2e-5 * max(1.0, abs(a["loss"]))
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-4 * max(1.0, abs(a["grad_norm"]))
+    assert single[-1]["loss"] < single[0]["loss"]
