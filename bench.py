@@ -1,0 +1,280 @@
+"""Headline benchmark: pretraining throughput (tokens/s, whole job) of the 8B dense decoder with sharded (ZeRO-3)
+data parallelism, bf16 compute with fp32 master weights and AdamW, sequence length 4096, micro-batch 2 per GPU and
+16 gradient-accumulation micro-steps per optimizer step (global batch 32 sequences per GPU: 256 on 8 GPUs).
+
+    python bench.py --gpus N --steps K --warmup W                 # this engine
+    python bench.py --impl reference --gpus N --steps K --warmup W   # the unmodified reference from baseline/_ref
+
+For N > 1 launch through ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...``.
+Rank 0 prints one JSON line. Data is synthetic (uniform random tokens), weights are randomly initialised.
+
+Two regions are timed, each over exactly K optimizer steps with a barrier + device synchronise on both sides and
+CUDA events on the launching stream, maximum over ranks:
+  * ``value``: inputs already resident on the device, nothing read back;
+  * ``e2e`` : every micro-step copies its token batch from pinned host memory and every step reads the loss back.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO_ROOT = os.path.dirname(os.path.abspath(__file__))
+
+DENSE_8B = dict(
+    name="dense-8b-gpt_base",
+    vocab_size=128256, hidden_size=4096, num_layers=32, num_attention_heads=32, num_key_value_heads=8,
+    intermediate_size=14336, rope_theta=500000, sequence_length=4096, micro_batch_size=2, gradient_accumulation_steps=16,
+)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not the headline config)")
+    p.add_argument("--gradient-accumulation-steps", type=int, default=None, help="debug only")
+    p.add_argument("--skip-e2e", action="store_true")
+    return p.parse_args()
+
+
+def model_config(spec: dict, layers: int | None) -> dict:
+    n = layers or spec["num_layers"]
+    attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=spec["num_attention_heads"],
+                num_key_value_heads=spec["num_key_value_heads"], add_bias=False)
+    mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=spec["intermediate_size"], add_bias=False)
+    return dict(
+        model_type="gpt_base", vocab_size=spec["vocab_size"], hidden_size=spec["hidden_size"], num_layers=n,
+        max_position_embeddings=spec["sequence_length"], position_embedding_type="rope", rope_theta=spec["rope_theta"],
+        normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.02, tie_word_embeddings=False,
+        bos_token_id=0, eos_token_id=1, pad_token_id=2,
+        sequence_mixer_blocks=[dict(attn) for _ in range(n)], mlp_blocks=[dict(mlp) for _ in range(n)],
+    )
+
+
+def training_config(spec: dict, layers: int | None, ga: int, steps: int, kernels: list[str], extra_distributed: dict | None = None) -> dict:
+    distributed = dict(stage=3, communication_dtype="fp32")
+    distributed.update(extra_distributed or {})
+    return dict(
+        datasets=[dict(class_name="SyntheticDataset", data_name="synthetic",
+                       class_args=dict(sequence_length=spec["sequence_length"], seed=1234, vocab_size=spec["vocab_size"]))],
+        model_args=dict(model_class="AutoModelForCausalLM", pretrained_config=model_config(spec, layers),
+                        use_padding_free_transformer=True, efficient_initialization=True),
+        tuning_args=dict(tuning_method="pretraining"),
+        save_args=dict(save_path=os.path.join(tempfile.gettempdir(), "bench-unused"), save_interval=10**9),
+        training_parameters=dict(num_training_steps=steps, micro_batch_size=spec["micro_batch_size"],
+                                 gradient_accumulation_steps=ga, eval_during_training=False, gradient_clipping=1.0),
+        optimizer_args=dict(class_name="TorchAdamW", class_args=dict(lr=3e-4, weight_decay=0.1, betas=[0.9, 0.95], eps=1e-10)),
+        lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=10, lr_decay_factor=0.1),
+        mixed_precision_args=dict(dtype="bf16"),
+        distributed_args=distributed,
+        kernel_args=dict(kernels=kernels),
+        logging_args=dict(log_interval=10**9),
+    )
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region is being timed."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        with open(self.path) as handle:
+            for line in handle:
+                cells = [c.strip() for c in line.split(",")]
+                if len(cells) < 9:
+                    continue
+                try:
+                    clocks.append(float(cells[1]))
+                    max_clock = float(cells[2])
+                except ValueError:
+                    continue
+                for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), cells[5:9]):
+                    if cell.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def measured_peak_tflops() -> tuple[float, str]:
+    path = os.path.join(REPO_ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            return float(json.load(handle)["bf16_tflops_sustained"]), "measured (sustained cuBLAS bf16)"
+    return 1400.0, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+def run_native(cli) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, REPO_ROOT)
+    from lm_engine import ops
+    from lm_engine.arguments import args_from_dict
+    from lm_engine.distributed import wrap_model_container_for_distributed_training
+    from lm_engine.enums import Kernel, Mode
+    from lm_engine.kernels import enable_kernels
+    from lm_engine.model_wrapper import get_model_container
+    from lm_engine.optimization import get_optimizer_container, get_scheduler_container
+    from lm_engine.pretrain import set_seed, train_step_without_pipeline_parallel
+    from lm_engine.train_utils import get_model_tflops
+    from lm_engine.utils import ProcessGroupManager, StepTracker, init_distributed, set_logger
+
+    set_logger("WARNING")
+    ops.require_native()
+    spec = DENSE_8B
+    ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
+    kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
+    args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels))
+
+    init_distributed(zero_stage=3)
+    world = ProcessGroupManager.get_world_size()
+    assert world == cli.gpus, f"--gpus {cli.gpus} but WORLD_SIZE={world}"
+    rank = ProcessGroupManager.get_global_rank()
+    device = ProcessGroupManager.get_device()
+    StepTracker(spec["micro_batch_size"], ga)
+    set_seed(1234)
+
+    with enable_kernels(args.kernel_args.kernels):
+        container = get_model_container(args, Mode.training)
+        container, _ = wrap_model_container_for_distributed_training(args, container)
+        optimizers = get_optimizer_container("TorchAdamW", args.optimizer_args.class_args, container)
+        schedulers = get_scheduler_container(container, optimizers, 10, 0, None, 10**6, args.lr_scheduler_args.lr_decay_style, 0.1, {})
+        container.train()
+
+        mb, seq = spec["micro_batch_size"], spec["sequence_length"]
+        multiplier = 1.0 / (mb * seq)
+        gen = torch.Generator().manual_seed(1234 + rank)
+        # a fresh micro-batch for every micro-step of every step (nothing is seen twice)
+        n_device = ga * (cli.warmup + cli.steps)
+        n_host = 0 if cli.skip_e2e else ga * cli.steps
+        pool_device = [torch.randint(0, spec["vocab_size"], (mb, seq + 1), generator=gen, dtype=torch.long).to(device) for _ in range(n_device)]
+        pool = [torch.randint(0, spec["vocab_size"], (mb, seq + 1), generator=gen, dtype=torch.long).pin_memory() for _ in range(n_host)]
+
+        class Feed:
+            def __init__(self, tensors):
+                self.tensors, self.i = tensors, 0
+
+            def __next__(self):
+                t = self.tensors[self.i % len(self.tensors)]
+                self.i += 1
+                return {"text": t}
+
+        def step(feed):
+            return train_step_without_pipeline_parallel(container, optimizers, schedulers, feed, 1.0, lm_loss_multiplier=multiplier)
+
+        def timed(feed, read_back: bool):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            launches0 = ops.launch_count()
+            sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+            if sampler:
+                sampler.start()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            last = None
+            for _ in range(cli.steps):
+                metrics = step(feed)
+                if read_back:
+                    last = float(metrics["loss"])  # device -> host read of the step result
+            end.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ms = start.elapsed_time(end)
+            clocks = sampler.stop() if sampler else None
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item(), ops.launch_count() - launches0, clocks, last
+
+        feed_device = Feed(pool_device)
+        for _ in range(cli.warmup):
+            metrics = step(feed_device)
+        loss_after_warmup = float(metrics["loss"])
+        ops.check_status()
+
+        ms, launches, clocks, _ = timed(feed_device, read_back=False)
+        e2e = None
+        if not cli.skip_e2e:
+            ms_e2e, _, _, last_loss = timed(Feed(pool), read_back=True)
+            tokens = cli.steps * ga * mb * seq * world
+            e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / cli.steps,
+                   "h2d_bytes_per_step": ga * mb * (seq + 1) * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss}
+        ops.check_status()
+
+    tokens_per_step = ga * mb * seq * world
+    ms_per_step = ms / cli.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+    tflops_model = get_model_tflops(container[0].config, ga * mb * world, seq)
+    peak, peak_src = measured_peak_tflops()
+    tflops_per_gpu = tflops_model / world / (ms_per_step / 1e3)
+    result = {
+        "impl": "native", "metric": "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": cli.steps, "warmup": cli.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+        "config": {"model": spec["name"] + ("" if cli.layers is None else f"-DEBUG-{cli.layers}-layers"),
+                   "global_batch": ga * mb * world, "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
+                   "parallelism": f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; gathered bf16 weights kept for the step)",
+                   "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)"},
+        "tflops_per_gpu": tflops_per_gpu, "mfu": tflops_per_gpu / peak, "mfu_peak": f"{peak} TFLOP/s {peak_src}",
+        "clocks": clocks, "gpu_launches": launches, "loss_after_warmup": loss_after_warmup,
+        "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
+    }
+    if e2e is not None:
+        result["e2e"] = e2e
+    ProcessGroupManager.destroy_process_groups()
+    return result if rank == 0 else None
+
+
+def main() -> None:
+    cli = parse_args()
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    if cli.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        result = run_reference(cli, DENSE_8B, REPO_ROOT)
+    else:
+        result = run_native(cli)
+    if result is not None:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()
