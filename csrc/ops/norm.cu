@@ -223,3 +223,101 @@ void rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd
 }
 
 }  // namespace b200
+
+// ----------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the RMSNorm backward (declared in noalloc.h).
+//
+// The regular entry point takes its per-CTA partial-sum scratch from the caller (the Python binding allocates it
+// from the tensor allocator on every call). Callers that must not allocate device memory - a C host loop that has
+// handed all device memory to its own arena, code running where a device allocation would synchronise or fail -
+// use this one instead: the scratch is a fixed array that lives in the library image.
+// ----------------------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "noalloc.h"
+
+namespace b200 {
+namespace {
+
+// kNoAllocMaxRows x kNoAllocMaxH floats = 5 MiB, resident on every GPU that loads this library until process exit.
+static __device__ __align__(256) float g_noalloc_rmsnorm_partial[B200_NOALLOC_RMSNORM_MAX_ROWS * B200_NOALLOC_RMSNORM_MAX_H];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_partial_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+void copy_message(char* dst, int len, const char* msg) {
+  if (dst == nullptr || len <= 0) return;
+  int i = 0;
+  for (; i < len - 1 && msg[i] != '\0'; ++i) dst[i] = msg[i];
+  dst[i] = '\0';
+}
+
+template <int TH, int V>
+void launch_noalloc_bwd(int rows, const uint4* DY, const uint4* HH, const uint4* W, const float* rstd, const uint4* DR,
+                        uint4* DH, float* partial, int T, int H, cudaStream_t stream) {
+  rmsnorm_bwd_kernel<TH, V><<<rows, TH, 0, stream>>>(DY, HH, W, rstd, DR, DH, partial, T, H);
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
+                                        void* dh, float* dw, int accumulate_dw, int T, int H, void* stream,
+                                        char* error_message, int error_message_len) {
+  using namespace b200;
+  if (T < 0 || H <= 0 || H % 8 != 0) {
+    copy_message(error_message, error_message_len, "b200_rmsnorm_bwd_noalloc: T must be >= 0 and H a positive multiple of 8");
+    return 1;
+  }
+  if (H > B200_NOALLOC_RMSNORM_MAX_H) {
+    copy_message(error_message, error_message_len,
+                 "b200_rmsnorm_bwd_noalloc: H exceeds B200_NOALLOC_RMSNORM_MAX_H (8192); use the allocating entry point");
+    return 2;
+  }
+  if (T == 0) return 0;
+
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    copy_message(error_message, error_message_len, "b200_rmsnorm_bwd_noalloc: cannot identify the current device");
+    return 3;
+  }
+  float* partial = nullptr;
+  {
+    // First call on a device: resolve the device address of the scratch array with that device current.
+    // (In host code the array's name is only a handle; a kernel must be given the resolved address.)
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_partial_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_rmsnorm_partial);
+      if (e != cudaSuccess || p == nullptr) {
+        copy_message(error_message, error_message_len, cudaGetErrorString(e));
+        return 4;
+      }
+      g_noalloc_partial_ptr[dev] = static_cast<float*>(p);
+    }
+    partial = g_noalloc_partial_ptr[dev];
+  }
+
+  const int rows = T < B200_NOALLOC_RMSNORM_MAX_ROWS ? T : B200_NOALLOC_RMSNORM_MAX_ROWS;
+  auto DY = reinterpret_cast<const uint4*>(dy);
+  auto HH = reinterpret_cast<const uint4*>(h);
+  auto W = reinterpret_cast<const uint4*>(w);
+  auto DR = reinterpret_cast<const uint4*>(dres);
+  auto DH = reinterpret_cast<uint4*>(dh);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nv = H / 8;
+  // Every partial row that the reduction reads is fully overwritten by its CTA first, so nothing needs clearing.
+  if (nv <= 256) launch_noalloc_bwd<256, 1>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
+  else if (nv <= 512) launch_noalloc_bwd<256, 2>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
+  else launch_noalloc_bwd<256, 4>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
+  column_sum_kernel<<<(H + 255) / 256, 256, 0, s>>>(partial, dw, rows, H, accumulate_dw ? 1 : 0);
+  count_launch(2);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    copy_message(error_message, error_message_len, cudaGetErrorString(e));
+    return 5;
+  }
+  return 0;
+}
