@@ -1,0 +1,65 @@
+"""Checkpoint-format parity with the reference package (when it is installed under ``baseline/_ref``): a model of the
+reference and a model of this package built from the same config exchange ``state_dict``s key for key and produce
+the same loss. The reference runs in a child process because both packages are called ``lm_engine``."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+_CHILD = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm, disable_generation_cache
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+blocks = [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": 4, "num_key_value_heads": 2, "add_bias": False}] * 2
+mlps = [{"mlp_type": "MLP", "activation_function": "swiglu", "intermediate_size": 128, "add_bias": False},
+        {"mlp_type": "MoE", "activation_function": "swiglu", "intermediate_size": 64, "add_bias": False, "num_experts": 4, "num_experts_per_tok": 2}]
+c = rm.GPTBaseConfig(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                     rope_theta=500000, sequence_mixer_blocks=blocks, mlp_blocks=mlps, tie_word_embeddings=False)
+from transformers import AutoModelForCausalLM
+torch.manual_seed(0)
+m = AutoModelForCausalLM.from_config(c)
+m.eval()
+ids = torch.randint(0, 256, (2, 16))
+with disable_generation_cache():
+    out = m(input_ids=ids, labels=ids)
+torch.save({"sd": m.state_dict(), "ids": ids, "loss": out.loss.detach(), "logits": out.logits.detach()}, sys.argv[2])
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_state_dict_and_loss_match_reference(tmp_path):
+    out = tmp_path / "ref.pt"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    subprocess.run([sys.executable, "-c", _CHILD, REF, str(out)], check=True, cwd=str(tmp_path), env=env, timeout=600,
+                   capture_output=True)
+    data = torch.load(out)
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    blocks = [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": 4, "num_key_value_heads": 2, "add_bias": False}] * 2
+    mlps = [{"mlp_type": "MLP", "activation_function": "swiglu", "intermediate_size": 128, "add_bias": False},
+            {"mlp_type": "MoE", "activation_function": "swiglu", "intermediate_size": 64, "add_bias": False, "num_experts": 4, "num_experts_per_tok": 2}]
+    config = GPTBaseConfig(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                           rope_theta=500000, sequence_mixer_blocks=blocks, mlp_blocks=mlps, tie_word_embeddings=False)
+    model = GPTBaseForCausalLM(config)
+    result = model.load_state_dict(data["sd"], strict=True)
+    assert not result.missing_keys and not result.unexpected_keys
+    model.eval()
+    with torch.no_grad():
+        mine = model(input_ids=data["ids"], labels=data["ids"])
+    assert torch.allclose(mine.logits, data["logits"], atol=3e-6, rtol=1e-5)
+    assert abs(mine.loss.item() - data["loss"].item()) < 1e-5
