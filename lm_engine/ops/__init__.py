@@ -274,8 +274,9 @@ def embedding(weight: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> to
 
 # ----------------------------------------------------------------------------- fused linear + cross entropy
 def _flce_chunk_rows(T: int, V: int) -> int:
-    # keep the transient logits chunk near 512 MiB of bf16
-    rows = max(256, (256 * 1024 * 1024) // max(V, 1))
+    # One pass over the fp32 weight-gradient accumulator per chunk is the dominant extra traffic of this op, so chunks
+    # are as large as a ~2.2 GB transient bf16 logits buffer allows (the whole micro-batch for 8k tokens x 128k vocab).
+    rows = max(256, (1100 * 1024 * 1024) // max(V, 1))
     rows = (rows // 128) * 128 or 128
     return min(T, rows)
 
