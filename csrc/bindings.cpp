@@ -45,8 +45,12 @@ inline int* status_ptr(const c10::optional<Tensor>& s) {
 
 // out[M,N] (+)= alpha * op(a) op(b)^T; see gemm_bf16.cu for operand conventions.
 //  a: [M,K] (a_mn=false) or [K,M] (a_mn=true); b: [N,K] (b_mn=false) or [K,N] (b_mn=true). Inner dim contiguous.
+// variant: 0 = choose (CTA-pair kernel for M >= 256), 1 = single-CTA kernel, 2 = CTA-pair kernel
+int g_default_gemm_variant = 0;
+void set_gemm_variant(int64_t v) { g_default_gemm_variant = (int)v; }
+
 void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate, double alpha,
-          const c10::optional<Tensor>& status, int64_t max_ctas) {
+          const c10::optional<Tensor>& status, int64_t max_ctas, int64_t variant) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm operands must be 2-D");
@@ -63,8 +67,14 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
   else if (out.scalar_type() == torch::kFloat32) epi = accumulate ? 2 : 1;
   else TORCH_CHECK(false, "gemm: output must be bf16 or fp32");
   const c10::cuda::CUDAGuard guard(a.device());
-  b200::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
-                  out.stride(0), a_mn, b_mn, epi, (float)alpha, status_ptr(status), (int)max_ctas, cur_stream());
+  if (variant == 0) variant = g_default_gemm_variant;
+  const bool pair = variant == 2 || (variant == 0 && M >= 256);
+  if (pair)
+    b200::gemm_bf16_2sm(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                        out.stride(0), a_mn, b_mn, epi, (float)alpha, status_ptr(status), (int)max_ctas, cur_stream());
+  else
+    b200::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                    out.stride(0), a_mn, b_mn, epi, (float)alpha, status_ptr(status), (int)max_ctas, cur_stream());
 }
 
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, double eps,
@@ -291,7 +301,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the engine";
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0, py::arg("status") = py::none(),
-        py::arg("max_ctas") = 0);
+        py::arg("max_ctas") = 0, py::arg("variant") = 0);
+  m.def("set_gemm_variant", &set_gemm_variant);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("eps"),
         py::arg("want_sum") = true);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

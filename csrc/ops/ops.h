@@ -12,6 +12,10 @@ namespace b200 {
 void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream);
 
+// ---- gemm/gemm_bf16_2sm.cu (CTA pairs, 256 x 256 tiles)
+void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                   bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream);
+
 // ---- gemm/grouped_gemm.cu
 void grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offsets, const int* gather_idx,
                        const int* scatter_idx, const float* row_scale, int num_groups, int total_rows, int N, int K,

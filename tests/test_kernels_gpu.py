@@ -21,10 +21,11 @@ def _rel_err(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("a_mn", [False, True])
 @pytest.mark.parametrize("b_mn", [False, True])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1000, 72, 328), (520, 1032, 2048)])
-def test_gemm_layouts(C, a_mn, b_mn, shape):
+def test_gemm_layouts(C, a_mn, b_mn, shape, variant):
     M, N, K = shape
     torch.manual_seed(0)
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -34,33 +35,34 @@ def test_gemm_layouts(C, a_mn, b_mn, shape):
     b_in = b.t().contiguous() if b_mn else b
     st = _status()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    C.gemm(a_in, b_in, out, a_mn, b_mn, False, 1.0, st, 0)
+    C.gemm(a_in, b_in, out, a_mn, b_mn, False, 1.0, st, 0, variant)
     torch.cuda.synchronize()
     assert st.item() == 0
     assert _rel_err(out, ref) < 6e-3
     out32 = torch.empty(M, N, device="cuda", dtype=torch.float32)
-    C.gemm(a_in, b_in, out32, a_mn, b_mn, False, 0.5, st, 0)
+    C.gemm(a_in, b_in, out32, a_mn, b_mn, False, 0.5, st, 0, variant)
     assert _rel_err(out32, 0.5 * ref) < 1e-5
     base = torch.randn(M, N, device="cuda", dtype=torch.float32)
     acc = base.clone()
-    C.gemm(a_in, b_in, acc, a_mn, b_mn, True, 1.0, st, 0)
+    C.gemm(a_in, b_in, acc, a_mn, b_mn, True, 1.0, st, 0, variant)
     assert _rel_err(acc, base + ref) < 1e-5
     assert st.item() == 0
 
 
-def test_gemm_persistent_many_tiles(C):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_gemm_persistent_many_tiles(C, variant):
     torch.manual_seed(1)
     M, N, K = 4096, 4096, 1024
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     st = _status()
-    C.gemm(a, b, out, False, False, False, 1.0, st, 0)
+    C.gemm(a, b, out, False, False, False, 1.0, st, 0, variant)
     ref = (a.float() @ b.float().t())
     assert st.item() == 0
     assert _rel_err(out, ref) < 6e-3
     out2 = torch.empty_like(out)
-    C.gemm(a, b, out2, False, False, False, 1.0, st, 0)
+    C.gemm(a, b, out2, False, False, False, 1.0, st, 0, variant)
     assert torch.equal(out, out2)  # run-to-run determinism
 
 
