@@ -87,12 +87,16 @@ class FusedAdamW(Optimizer):
 
 
 def _engine_param_groups(engine, optimizer_class_args: dict, m_width: float | None) -> list[dict]:
+    """One optimizer group per parameter group that exists anywhere in the model - also on ranks whose shards hold no
+    element of it, so that the group list (and with it scheduler / optimizer state) is the same on every rank and
+    for every world size."""
     groups = []
     by_group = engine.segments_by_group()
+    present = {slot.group for _, slot in engine.named_slots()}
     for name in GROUP_ORDER:
-        if name not in by_group:
+        if name not in present:
             continue
-        entry = {"params": [seg.master for seg in by_group[name]], "name": name}
+        entry = {"params": [seg.master for seg in by_group.get(name, [])], "name": name}
         entry.update(group_overrides(name, optimizer_class_args, m_width))
         groups.append(entry)
     return groups
