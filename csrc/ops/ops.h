@@ -16,12 +16,6 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long 
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                    bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream);
 
-// ---- gemm/grouped_gemm.cu
-void grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offsets, const int* gather_idx,
-                       const int* scatter_idx, const float* row_scale, int num_groups, int total_rows, int N, int K,
-                       long long lda, long long ldb_group, long long ldb, long long ldc, bool b_mn, int epi,
-                       int* status, cudaStream_t stream);
-
 // ---- ops/norm.cu
 int rmsnorm_bwd_partial_rows(int T);
 void rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd, int T, int H,
@@ -51,11 +45,5 @@ void adamw_step(float* p, float* m, float* v, float* g, void* p_bf16, long long 
 void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss, float* lse, int T, int V,
                            long long row_stride, float logit_scale, float grad_scale, long long ignore_index,
                            bool write_grad, cudaStream_t stream);
-
-// ---- ops/attention_fwd.cu / attention_bwd.cu
-void attn_varlen_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
-                     const int* tile_table, int num_tiles, int T, int num_q_heads, int num_kv_heads, int head_dim,
-                     long long q_stride, long long kv_stride, long long o_stride, int q_group_stride_cols,
-                     float softmax_scale, bool causal, int* status, cudaStream_t stream);
 
 }  // namespace b200

@@ -1,6 +1,5 @@
 // Registration hooks of extension parts whose sources are compiled separately.
 #include <pybind11/pybind11.h>
 namespace b200 {
-void register_moe(pybind11::module_&) {}
 void register_comm(pybind11::module_&) {}
 }  // namespace b200

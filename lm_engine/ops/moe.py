@@ -1,0 +1,148 @@
+"""Mixture-of-experts expert computation on grouped rows (the role ScatterMoE plays for the reference, see
+lm_engine/hf_models/modeling_utils/mlp_blocks/moe.py:262-291 there).
+
+Token copies are laid out grouped by expert; every expert's range starts at a multiple of 128 rows and is zero-padded
+to the next multiple, so each 128-row GEMM tile belongs to one expert and nothing about the launch depends on the
+routing outcome (no host synchronisation). One layer is
+
+    gather rows -> grouped GEMM (c_fc) -> SwiGLU -> grouped GEMM (c_proj) -> weighted combine per token
+
+with an explicit backward that recomputes the gathered input and the activation instead of saving them. Under
+expert parallelism the same kernels read token rows / expert outputs directly from the peers' buffers (see
+:mod:`lm_engine.parallel.expert_parallel`).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _weight_grad_target, native, native_available, status_word
+
+TILE = 128
+
+
+@dataclass
+class GroupedLayout:
+    """Placement of ``entries`` (token, slot) pairs into expert-grouped, tile-padded rows."""
+
+    dest_row: torch.Tensor  # int32 [entries]: row of each entry (-1: not placed here)
+    src_entry: torch.Tensor  # int32 [rows]: entry held by each row (-1: padding)
+    tile_expert: torch.Tensor  # int32 [rows / 128]: expert of each tile (>= num_experts: unused tile)
+    padded_offsets: torch.Tensor  # int32 [num_experts + 1]
+    rows: int  # static upper bound, multiple of 128
+
+
+def build_grouped_layout(expert_of_entry: torch.Tensor, num_experts: int, first_expert: int = 0,
+                         num_local_experts: int | None = None) -> GroupedLayout:
+    """Stable counting sort of entries by expert with tile-aligned expert ranges, using device ops only.
+
+    ``expert_of_entry``: int [entries]. Entries whose expert is outside ``[first_expert, first_expert + local)`` are not
+    placed (their ``dest_row`` is -1), which is how one rank of an expert parallel group selects its share.
+    """
+    local = num_experts if num_local_experts is None else num_local_experts
+    entries = expert_of_entry.numel()
+    device = expert_of_entry.device
+    e = expert_of_entry.reshape(-1).to(torch.int64) - first_expert
+    mine = (e >= 0) & (e < local)
+    key = torch.where(mine, e, torch.full_like(e, local))  # foreign entries sort last
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=local + 1)[:local]
+    padded = (counts + TILE - 1) // TILE * TILE
+    padded_end = torch.cumsum(padded, 0)
+    padded_start = padded_end - padded
+    start = torch.cumsum(counts, 0) - counts
+
+    rows = ((entries + local * (TILE - 1)) + TILE - 1) // TILE * TILE
+    sorted_key = key[order]
+    placed = sorted_key < local
+    safe_key = sorted_key.clamp(max=local - 1)
+    position = torch.arange(entries, device=device) - start[safe_key]
+    row_sorted = torch.where(placed, padded_start[safe_key] + position, torch.full_like(position, -1))
+
+    dest_row = torch.empty(entries, dtype=torch.int32, device=device)
+    dest_row[order] = row_sorted.to(torch.int32)
+    src_entry = torch.full((rows + 1,), -1, dtype=torch.int32, device=device)
+    src_entry[torch.where(placed, row_sorted, torch.full_like(row_sorted, rows))] = order.to(torch.int32)
+    src_entry = src_entry[:rows].contiguous()
+
+    tile_start = torch.arange(rows // TILE, device=device) * TILE
+    tile_expert = torch.searchsorted(padded_end, tile_start, right=True).to(torch.int32)  # == local for unused tiles
+    padded_offsets = torch.cat([padded_start.new_zeros(1), padded_end]).to(torch.int32)
+    return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows)
+
+
+def native_moe_ok(x: torch.Tensor, activation_function: str) -> bool:
+    return (native_available() and x.is_cuda and x.dtype == torch.bfloat16 and activation_function == "swiglu"
+            and x.shape[-1] % 8 == 0 and hasattr(native(), "grouped_rows"))
+
+
+def _wgrad(C, dy, x, weight, padded_offsets, st):
+    target = _weight_grad_target(weight)
+    if target is not None:
+        C.grouped_wgrad(dy, x, target.view(weight.shape), padded_offsets, True, st)
+        return None
+    dw = torch.zeros(weight.shape, device=weight.device, dtype=torch.float32)
+    C.grouped_wgrad(dy, x, dw, padded_offsets, False, st)
+    return dw.to(weight.dtype)
+
+
+class _ScatteredExpertsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, num_experts, top_k):
+        C = native()
+        st = status_word(x.device)
+        T, H = x.shape
+        layout = build_grouped_layout(selected_experts.reshape(-1), num_experts)
+        xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * top_k, top_k, x)
+        fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
+        del xg
+        act = C.swiglu_fwd(fc)
+        y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
+        del act
+        weights32 = router_weights.reshape(-1).float().contiguous()
+        out = C.moe_combine([y.data_ptr()], layout.dest_row, weights32, T, H, top_k, layout.rows, x)
+        ctx.save_for_backward(x, w_fc, w_proj, weights32, fc, layout.dest_row, layout.src_entry, layout.tile_expert, layout.padded_offsets)
+        ctx.meta = (num_experts, top_k, layout.rows, router_weights.dtype, router_weights.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w_fc, w_proj, weights32, fc, dest_row, src_entry, tile_expert, padded_offsets = ctx.saved_tensors
+        num_experts, top_k, rows, w_dtype, w_shape = ctx.meta
+        C = native()
+        st = status_word(x.device)
+        T, H = x.shape
+        dout = dout.contiguous()
+        entries = T * top_k
+
+        # dY of the second GEMM without the routing weight, and the activation recomputed from the saved c_fc output
+        dyg = C.moe_gather([dout.data_ptr()], [], src_entry, H, entries, top_k, x)
+        dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)  # [rows, I] = dyg @ w_proj[e]
+        act = C.swiglu_fwd(fc)
+        # d(router weight) = <dout[token], expert output row> = <dact_row, act_row>
+        d_weights = C.moe_rowdot(dact, act, dest_row).view(w_shape).to(w_dtype)
+        # per-row routing weight (0 for padding rows)
+        row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
+        row_weight[torch.where(dest_row >= 0, dest_row, torch.full_like(dest_row, rows)).long()] = weights32
+        row_weight = row_weight[:rows].contiguous()
+        C.scale_rows_(act, row_weight)
+        g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
+        del dyg, act
+        C.scale_rows_(dact, row_weight)
+        dfc = C.swiglu_bwd(dact, fc, False)[0]
+        del dact
+        xg = C.moe_gather([x.data_ptr()], [], src_entry, H, entries, top_k, x)
+        g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
+        del xg
+        dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)  # [rows, H] = dfc @ w_fc[e]
+        dx = C.moe_combine([dxg.data_ptr()], dest_row, None, T, H, top_k, rows, x)
+        return dx, g_fc, g_proj, d_weights, None, None, None
+
+
+def scattered_experts_mlp(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor, router_weights: torch.Tensor,
+                          selected_experts: torch.Tensor, num_experts: int, top_k: int, activation_function: str) -> torch.Tensor:
+    """``sum_s router_weights[t, s] * c_proj[e](swiglu(c_fc[e](x[t])))`` with ``e = selected_experts[t, s]``."""
+    assert activation_function == "swiglu"
+    return _ScatteredExpertsFn.apply(x.contiguous(), w_fc, w_proj, router_weights, selected_experts, num_experts, top_k)

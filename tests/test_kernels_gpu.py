@@ -259,3 +259,38 @@ def test_attention_fwd_bwd(C, groups, qpg, d, lengths):
     assert _rel_err(mine[:, :, qpg + 1], g[:, :, qpg + 1]) < 2e-2  # dV
     assert _rel_err(mine[:, :, qpg], g[:, :, qpg]) < 2e-2  # dK
     assert _rel_err(mine[:, :, :qpg], g[:, :, :qpg]) < 2e-2  # dQ
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(300, 256, 128, 4, 2), (1000, 512, 256, 8, 4), (64, 128, 64, 40, 8)])
+def test_scattered_experts_fwd_bwd(C, T, H, I, E, k):
+    from lm_engine.ops.moe import scattered_experts_mlp
+
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w_fc = (0.05 * torch.randn(E, 2 * I, H, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    w_proj = (0.05 * torch.randn(E, H, I, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda")
+    top, experts = logits.topk(k, dim=-1)
+    weights = top.softmax(-1).to(torch.bfloat16).requires_grad_(True)
+
+    out = scattered_experts_mlp(x, w_fc, w_proj, weights, experts, E, k, "swiglu")
+    dout = torch.randn_like(out)
+    out.backward(dout)
+
+    # fp32 reference: naive loop over experts
+    xf, wf, wp, wr = (t.detach().float().requires_grad_(True) for t in (x, w_fc, w_proj, weights))
+    ref = torch.zeros(T, H, device="cuda")
+    for e in range(E):
+        tok, slot = (experts == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = xf[tok] @ wf[e].t()
+        up, gate = h.chunk(2, -1)
+        y = (up * torch.nn.functional.silu(gate)) @ wp[e].t()
+        ref = ref.index_add(0, tok, y * wr[tok, slot].unsqueeze(-1))
+    ref.backward(dout.float())
+    assert _rel_err(out, ref) < 1.5e-2
+    assert _rel_err(x.grad, xf.grad) < 2e-2
+    assert _rel_err(w_fc.grad, wf.grad) < 2e-2
+    assert _rel_err(w_proj.grad, wp.grad) < 2e-2
+    assert _rel_err(weights.grad, wr.grad) < 3e-2
