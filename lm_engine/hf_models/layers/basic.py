@@ -12,6 +12,25 @@ from ... import ops
 from ..parameter import mark_parameter_as_no_weight_decay
 
 
+def loaded_from_checkpoint(p: torch.Tensor) -> bool:
+    """True for a tensor that ``from_pretrained`` already filled; initialisers must leave it alone (the loader only
+    guards the ``torch.nn.init`` functions, not plain in-place writes)."""
+    return getattr(p, "_is_hf_initialized", False)
+
+
+def init_zeros_(p: torch.Tensor | None) -> None:
+    if p is not None and not loaded_from_checkpoint(p):
+        p.zero_()
+
+
+def init_fill_(p: torch.Tensor | None, value) -> None:
+    if p is not None and not loaded_from_checkpoint(p):
+        if torch.is_tensor(value):
+            p.copy_(value)
+        else:
+            p.fill_(value)
+
+
 class ParameterizedLinear(nn.Linear):
     def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None,
                  std: float | None = None) -> None:
@@ -28,8 +47,7 @@ class ParameterizedLinear(nn.Linear):
             super().reset_parameters()
         else:
             nn.init.normal_(self.weight, mean=0.0, std=self.std)
-        if getattr(self, "bias", None) is not None:
-            self.bias.zero_()
+        init_zeros_(getattr(self, "bias", None))
 
 
 class ParameterizedEmbedding(nn.Embedding):
@@ -47,7 +65,7 @@ class ParameterizedEmbedding(nn.Embedding):
             super().reset_parameters()
         else:
             nn.init.normal_(self.weight, mean=0.0, std=self.std)
-            if self.padding_idx is not None:
+            if self.padding_idx is not None and not loaded_from_checkpoint(self.weight):
                 self.weight[self.padding_idx].zero_()
 
 
@@ -66,8 +84,7 @@ class ParameterizedConv1d(nn.Conv1d):
             super().reset_parameters()
         else:
             nn.init.normal_(self.weight, mean=0.0, std=self.std)
-            if getattr(self, "bias", None) is not None:
-                self.bias.zero_()
+            init_zeros_(getattr(self, "bias", None))
 
 
 def dropout(p: float) -> nn.Module:

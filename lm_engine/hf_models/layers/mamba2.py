@@ -19,7 +19,7 @@ from ...utils import divide_if_divisible
 from ..context import SequenceContext
 from ..parameter import mark_parameter_as_mup_learning_rate, mark_parameter_as_no_weight_decay
 from .activations import get_activation_function
-from .basic import ParameterizedConv1d, ParameterizedLinear
+from .basic import ParameterizedConv1d, ParameterizedLinear, init_fill_
 from .normalization import get_normalization_function
 
 
@@ -99,9 +99,9 @@ class Mamba2(nn.Module):
 
     @torch.no_grad()
     def reset_parameters(self) -> None:
-        self.A_log.copy_(torch.log(torch.arange(1, self.num_heads + 1, dtype=torch.float32)))
-        self.D.fill_(1.0)
-        self.dt_bias.fill_(1.0)
+        init_fill_(self.A_log, torch.log(torch.arange(1, self.num_heads + 1, dtype=torch.float32)))
+        init_fill_(self.D, 1.0)
+        init_fill_(self.dt_bias, 1.0)
 
     def _split(self, projected: torch.Tensor):
         return projected.split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)

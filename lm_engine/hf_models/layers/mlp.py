@@ -23,7 +23,7 @@ from ...utils import ProcessGroupManager
 from ..loss import add_aux_loss
 from ..parameter import mark_parameter_as_mup_learning_rate, mark_parameter_as_no_weight_decay
 from .activations import get_activation_function, is_glu
-from .basic import ParameterizedLinear
+from .basic import ParameterizedLinear, init_zeros_
 
 
 def _std(initializer_range: float, init_method: str, m_width: float | None, depth_scale: int | None = None) -> float:
@@ -72,8 +72,7 @@ class ParameterizedExperts(nn.Module):
     @torch.no_grad()
     def reset_parameters(self) -> None:
         nn.init.normal_(self.weight, mean=0.0, std=self.std if self.std is not None else 0.02)
-        if self.bias is not None:
-            self.bias.zero_()
+        init_zeros_(self.bias)
 
     def forward_grouped(self, x: torch.Tensor, tokens_per_expert: list[int]) -> torch.Tensor:
         """``x`` holds the rows of expert 0, then expert 1, ...; one dense product per non-empty expert."""

@@ -22,6 +22,7 @@ import torch.nn.functional as F
 from ...utils import divide_if_divisible
 from ..config import DesyncResidualConfig
 from ..context import SequenceContext
+from ..layers.basic import init_zeros_
 from ..layers.activations import get_activation_function, is_glu
 from ..layers.normalization import get_normalization_function
 from ..layers.rope import apply_rotary_pos_emb
@@ -44,8 +45,7 @@ class DesyncResidualLinear(nn.Module):
     @torch.no_grad()
     def reset_parameters(self) -> None:
         nn.init.normal_(self.weight, mean=0.0, std=self.std)
-        if self.bias is not None:
-            self.bias.zero_()
+        init_zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[1:-1]

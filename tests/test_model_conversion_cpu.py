@@ -1,0 +1,76 @@
+"""HF import/export: logits of a random HF model equal the imported model's, and export(import(x)) == x."""
+
+import os
+
+import pytest
+import torch
+from transformers import AutoConfig, AutoModelForCausalLM
+
+from lm_engine.hf_models import GPTBaseForCausalLM, export_to_huggingface, import_from_huggingface
+from lm_engine.utils import SafeTensorsWeightsManager
+
+
+def _hf_config(model_type: str):
+    common = dict(vocab_size=96, hidden_size=32, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                  max_position_embeddings=64, tie_word_embeddings=False, bos_token_id=0, eos_token_id=1, pad_token_id=2)
+    granite = dict(attention_multiplier=0.3, embedding_multiplier=1.7, residual_multiplier=0.6, logits_scaling=2.5)
+    if model_type == "llama":
+        return AutoConfig.for_model("llama", intermediate_size=48, **common)
+    if model_type == "llama_bias":
+        return AutoConfig.for_model("llama", intermediate_size=48, attention_bias=True, mlp_bias=True, **common)
+    if model_type == "granite":
+        return AutoConfig.for_model("granite", intermediate_size=48, **common, **granite)
+    if model_type == "granitemoe":
+        return AutoConfig.for_model("granitemoe", intermediate_size=24, num_local_experts=4, num_experts_per_tok=2, **common, **granite)
+    if model_type == "granitemoeshared":
+        return AutoConfig.for_model("granitemoeshared", intermediate_size=24, num_local_experts=4, num_experts_per_tok=2,
+                                    shared_intermediate_size=40, **common, **granite)
+    if model_type == "granitemoehybrid":
+        return AutoConfig.for_model("granitemoehybrid", intermediate_size=24, num_local_experts=4, num_experts_per_tok=2,
+                                    shared_intermediate_size=40, layer_types=["mamba", "attention", "mamba"], mamba_n_heads=4,
+                                    mamba_d_state=8, mamba_n_groups=1, mamba_expand=2, mamba_d_conv=4, mamba_chunk_size=8,
+                                    mamba_d_head=16, position_embedding_type="nope", **common, **granite)
+    if model_type == "gpt_bigcode_mqa":
+        return AutoConfig.for_model("gpt_bigcode", vocab_size=96, n_embd=32, n_layer=2, n_head=4, n_positions=64, multi_query=True,
+                                    resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    if model_type == "gpt_bigcode_mha":
+        return AutoConfig.for_model("gpt_bigcode", vocab_size=96, n_embd=32, n_layer=2, n_head=4, n_positions=64, multi_query=False,
+                                    resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    raise ValueError(model_type)
+
+
+@pytest.mark.parametrize("name", ["llama", "llama_bias", "granite", "granitemoe", "granitemoeshared", "granitemoehybrid",
+                                  "gpt_bigcode_mqa", "gpt_bigcode_mha"])
+def test_import_export_round_trip(name, tmp_path):
+    torch.manual_seed(0)
+    hf_config = _hf_config(name)
+    hf_model = AutoModelForCausalLM.from_config(hf_config).eval().float()
+    with torch.no_grad():  # non-trivial values everywhere (norm weights, biases)
+        for p in hf_model.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    hf_dir, ours_dir, back_dir = (str(tmp_path / d) for d in ("hf", "ours", "back"))
+    hf_model.save_pretrained(hf_dir, safe_serialization=True)
+
+    import_from_huggingface(hf_dir, ours_dir)
+    model = GPTBaseForCausalLM.from_pretrained(ours_dir).eval().float()
+
+    ids = torch.randint(3, 96, (2, 24))
+    with torch.no_grad():
+        expected = hf_model(input_ids=ids).logits
+        got = model(input_ids=ids).logits
+    assert got.shape == expected.shape
+    torch.testing.assert_close(got, expected, atol=2e-5, rtol=1e-4)
+
+    export_to_huggingface(ours_dir, back_dir, hf_config.model_type)
+    original, exported = SafeTensorsWeightsManager(hf_dir), SafeTensorsWeightsManager(back_dir)
+    original_state = original.state_dict()
+    exported_state = exported.state_dict()
+    for key, value in original_state.items():
+        if key == "lm_head.weight" and key not in exported_state:
+            continue
+        assert torch.equal(exported_state[key], value), key
+    reloaded = AutoModelForCausalLM.from_pretrained(back_dir).eval().float()
+    with torch.no_grad():
+        torch.testing.assert_close(reloaded(input_ids=ids).logits, expected, atol=2e-5, rtol=1e-4)
+    assert os.path.isfile(os.path.join(back_dir, "config.json"))
