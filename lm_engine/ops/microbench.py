@@ -1,0 +1,185 @@
+"""Kernel micro-benchmarks: ``python -m lm_engine.ops.microbench {gemm,attention,moe,elementwise} [options]``.
+
+Every case is timed with CUDA events around single launches after warm-up, with a write larger than L2 between
+launches, and reports the median. ``--profile`` runs each case exactly ``--iters`` times with no comparison library and
+no flush kernel in between, which is the form to put under a profiler (small, few launches, ends by itself).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import native, status_word
+
+L2_FLUSH_BYTES = 256 * 1024 * 1024
+
+
+def _time(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _emit(record: dict) -> None:
+    print(json.dumps(record), flush=True)
+
+
+def bench_gemm(args) -> None:
+    C, st = native(), status_word(torch.device("cuda"))
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes] if args.shapes else [
+        (8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 8192, 8192), (4096, 128256, 4096)]
+    for M, N, K in shapes:
+        flops = 2.0 * M * N * K
+        for layout in args.layouts:
+            a_mn, b_mn = layout[0] == "t", layout[1] == "n"
+            a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+            b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            record = dict(op="gemm", layout=layout, m=M, n=N, k=K)
+            for name, variant in (("cta1", 1), ("cta_pair", 2)):
+                if args.variant not in ("all", name):
+                    continue
+                ms = _time(lambda: C.gemm(a, b, out, a_mn, b_mn, False, 1.0, st, 0, variant), args.iters, args.warmup, flush)
+                record[f"{name}_ms"], record[f"{name}_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+            if not args.profile:
+                am, bm = (a.t() if a_mn else a), (b if b_mn else b.t())
+                ms = _time(lambda: torch.matmul(am, bm, out=out), args.iters, args.warmup, flush)
+                record["cublas_ms"], record["cublas_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+            record["status"] = int(st.item())
+            _emit(record)
+
+
+def bench_attention(args) -> None:
+    C, st = native(), status_word(torch.device("cuda"))
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    groups, qpg, d = args.kv_heads, args.heads // args.kv_heads, args.head_dim
+    for spec in args.shapes or ["2x4096", "1x8192"]:
+        nseq, L = (int(v) for v in spec.split("x"))
+        T = nseq * L
+        cu = torch.arange(0, T + 1, L, dtype=torch.int32, device="cuda")
+        qkv = torch.randn(T, groups * (qpg + 2) * d, device="cuda", dtype=torch.bfloat16)
+        out, lse = C.attn_fwd(qkv, cu, L, groups, qpg, d, d**-0.5, True, st)
+        dout = torch.randn_like(out)
+        flops = 4.0 * L * L * d * groups * qpg * nseq / 2
+        record = dict(op="attention", causal=True, sequences=nseq, seq_len=L, heads=args.heads, kv_heads=groups, head_dim=d)
+        if args.direction in ("all", "fwd"):
+            ms = _time(lambda: C.attn_fwd(qkv, cu, L, groups, qpg, d, d**-0.5, True, st), args.iters, args.warmup, flush)
+            record["fwd_ms"], record["fwd_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+        if args.direction in ("all", "bwd"):
+            ms = _time(lambda: C.attn_bwd(dout, qkv, out, lse, cu, L, groups, qpg, d, d**-0.5, True, st), args.iters, args.warmup, flush)
+            record["bwd_ms"], record["bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
+        if not args.profile:
+            try:
+                from flash_attn import flash_attn_varlen_func
+
+                x = qkv.view(T, groups, qpg + 2, d)
+                q = x[:, :, :qpg].reshape(T, groups * qpg, d).contiguous().requires_grad_(True)
+                k = x[:, :, qpg].contiguous().requires_grad_(True)
+                v = x[:, :, qpg + 1].contiguous().requires_grad_(True)
+                o = flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True)
+                ms = _time(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True), args.iters, args.warmup, flush)
+                record["flash_attn2_fwd_ms"], record["flash_attn2_fwd_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+                do = dout.view(T, groups * qpg, d)
+                ms = _time(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True), args.iters, args.warmup, flush)
+                record["flash_attn2_bwd_ms"], record["flash_attn2_bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
+            except ImportError:
+                pass
+        record["status"] = int(st.item())
+        _emit(record)
+
+
+def bench_moe(args) -> None:
+    from .moe import build_grouped_layout
+
+    C, st = native(), status_word(torch.device("cuda"))
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    T, H, I, E, k = args.tokens, args.hidden, args.intermediate, args.experts, args.top_k
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w_fc = torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    w_proj = torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) * 0.02
+    selected = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]) if T <= 4096 else torch.randint(0, E, (T, k), device="cuda")
+    layout = build_grouped_layout(selected.reshape(-1), E)
+    xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * k, k, x)
+    record = dict(op="moe_grouped_gemm", tokens=T, hidden=H, intermediate=I, experts=E, top_k=k, rows=layout.rows)
+    ms = _time(lambda: C.grouped_rows(xg, w_fc, layout.tile_expert, False, st), args.iters, args.warmup, flush)
+    record["c_fc_ms"], record["c_fc_tflops_useful"] = round(ms, 4), round(2.0 * T * k * 2 * I * H / ms / 1e9, 1)
+    act = torch.randn(layout.rows, I, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: C.grouped_rows(act, w_proj, layout.tile_expert, False, st), args.iters, args.warmup, flush)
+    record["c_proj_ms"], record["c_proj_tflops_useful"] = round(ms, 4), round(2.0 * T * k * I * H / ms / 1e9, 1)
+    dw = torch.zeros(E, 2 * I, H, device="cuda", dtype=torch.float32)
+    dfc = torch.randn(layout.rows, 2 * I, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: C.grouped_wgrad(dfc, xg, dw, layout.padded_offsets, True, st), args.iters, args.warmup, flush)
+    record["wgrad_fc_ms"], record["wgrad_fc_tflops_useful"] = round(ms, 4), round(2.0 * T * k * 2 * I * H / ms / 1e9, 1)
+    ms = _time(lambda: C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * k, k, x), args.iters, args.warmup, flush)
+    record["gather_ms"], record["gather_gbs"] = round(ms, 4), round(2.0 * layout.rows * H * 2 / ms / 1e6, 1)
+    record["status"] = int(st.item())
+    _emit(record)
+
+
+def bench_elementwise(args) -> None:
+    C = native()
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    T, H, I, V = args.tokens, args.hidden, args.intermediate, args.vocab
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn_like(x)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: C.rmsnorm_fwd(x, res, w, 1e-5, True), args.iters, args.warmup, flush)
+    _emit(dict(op="rmsnorm_fwd_residual", tokens=T, hidden=H, ms=round(ms, 4), gbs=round(4.0 * T * H * 2 / ms / 1e6, 1)))
+    fc = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: C.swiglu_fwd(fc), args.iters, args.warmup, flush)
+    _emit(dict(op="swiglu_fwd", tokens=T, intermediate=I, ms=round(ms, 4), gbs=round(3.0 * T * I * 2 / ms / 1e6, 1)))
+    rows = min(T, 4096)
+    logits = torch.randn(rows, V, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    ms = _time(lambda: C.cross_entropy_(logits, labels, 1.0, 1.0, -100, True), args.iters, args.warmup, flush)
+    _emit(dict(op="cross_entropy_inplace", rows=rows, vocab=V, ms=round(ms, 4), gbs=round(2.0 * rows * V * 2 / ms / 1e6, 1)))
+    n = 256 * 1024 * 1024
+    p32, g32 = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(p32), torch.zeros_like(p32)
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    # reads p, m, v, g (fp32); writes p, m, v, g (zeroed) and the bf16 copy
+    ms = _time(lambda: C.adamw_step(p32, m, v, g32, p16, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1, None, 1.0, True), args.iters, args.warmup, flush)
+    _emit(dict(op="adamw_step", elements=n, ms=round(ms, 4), gbs=round(n * (4 * 4 + 4 * 4 + 2) / ms / 1e6, 1)))
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument("op", choices=["gemm", "attention", "moe", "elementwise"])
+    parser.add_argument("--shapes", nargs="*", help="gemm: MxNxK ...; attention: SEQUENCESxLENGTH ...")
+    parser.add_argument("--layouts", nargs="*", default=["nt"], help="gemm: nt (y = x w^T), nn (dgrad), tn (wgrad)")
+    parser.add_argument("--variant", default="all", choices=["all", "cta1", "cta_pair"])
+    parser.add_argument("--direction", default="all", choices=["all", "fwd", "bwd"])
+    parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--profile", action="store_true", help="no comparison library, no L2 flush kernel")
+    parser.add_argument("--heads", type=int, default=32)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--tokens", type=int, default=8192)
+    parser.add_argument("--hidden", type=int, default=4096)
+    parser.add_argument("--intermediate", type=int, default=14336)
+    parser.add_argument("--experts", type=int, default=40)
+    parser.add_argument("--top-k", type=int, default=8)
+    parser.add_argument("--vocab", type=int, default=128256)
+    args = parser.parse_args()
+    {"gemm": bench_gemm, "attention": bench_attention, "moe": bench_moe, "elementwise": bench_elementwise}[args.op](args)
+
+
+if __name__ == "__main__":
+    main()
