@@ -44,6 +44,8 @@ class FusedAdamW(Optimizer):
     @torch.no_grad()
     def step(self, closure=None):
         loss = None if closure is None else closure()
+        # True when every updated segment that has peers stored its result on all of them (see adamw_step_bcast)
+        self.last_step_broadcast = True
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
             for p in group["params"]:
@@ -57,11 +59,19 @@ class FusedAdamW(Optimizer):
                 state["step"] += 1
                 seg = getattr(p, "_lm_engine_segment", None)
                 target = None if seg is None else seg.compute
-                if p.is_cuda and ops.native_available() and p.numel() % 4 == 0 and self.decoupled:
+                bcast = None if seg is None else seg.broadcast
+                if bcast is not None and p.is_cuda and ops.native_available() and p.numel() % 8 == 0 and self.decoupled:
+                    # update + store of the bf16 result into every rank's compute copy (no parameter all-gather)
+                    ops.native().adamw_step_bcast(p.data, state["exp_avg"], state["exp_avg_sq"], p.grad, bcast[0], bcast[1], bcast[2],
+                                                  group["lr"], beta1, beta2, group["eps"], group["weight_decay"], state["step"],
+                                                  self.grad_scale, self.grad_mul, True)
+                elif p.is_cuda and ops.native_available() and p.numel() % 4 == 0 and self.decoupled:
+                    self.last_step_broadcast = False
                     ops.native().adamw_step(p.data, state["exp_avg"], state["exp_avg_sq"], p.grad, target, group["lr"], beta1,
                                             beta2, group["eps"], group["weight_decay"], state["step"], self.grad_scale,
                                             self.grad_mul, True)
                 else:
+                    self.last_step_broadcast = False
                     self._step_torch(p, state, group, target)
         return loss
 

@@ -1,4 +1,5 @@
-"""Collective shims shared by the CPU (gloo) and GPU (NCCL / peer-memory kernels) paths.
+"""Collective shims shared by the CPU (gloo) and GPU (NCCL) paths; the peer-memory kernels that replace them on
+NVLink are driven by the training engine directly (:mod:`lm_engine.parallel.symmetric`).
 
 Every function works in place on one flat buffer split into ``world`` equal shards, which is how the sharded
 training engine stores parameters and gradients. gloo lacks ``reduce_scatter_tensor`` and ``ReduceOp.AVG``, so
@@ -27,17 +28,12 @@ def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
-def reduce_scatter_in_place(buf: torch.Tensor, shard_numel: int, rank: int, group=None, fused: bool = False) -> torch.Tensor:
+def reduce_scatter_in_place(buf: torch.Tensor, shard_numel: int, rank: int, group=None, fused: bool = False) -> torch.Tensor:  # noqa: ARG001
     """Afterwards ``buf[rank * shard_numel : (rank + 1) * shard_numel]`` holds the sum over ranks of that slice."""
     shard = buf[rank * shard_numel : (rank + 1) * shard_numel]
     if _on_cpu(buf):
         dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
         return shard
-    if fused:
-        from .symmetric import fused_reduce_scatter_in_place
-
-        if fused_reduce_scatter_in_place(buf, shard_numel, rank, group):
-            return shard
     dist.reduce_scatter_tensor(shard, buf, op=dist.ReduceOp.SUM, group=group)
     return shard
 
@@ -53,11 +49,6 @@ def all_gather_in_place(buf: torch.Tensor, shard_numel: int, rank: int, group=No
             if r != rank:
                 buf[r * shard_numel : (r + 1) * shard_numel].copy_(piece)
         return buf
-    if fused:
-        from .symmetric import fused_all_gather_in_place
-
-        if fused_all_gather_in_place(buf, shard_numel, rank, group):
-            return buf
     dist.all_gather_into_tensor(buf, shard, group=group)
     return buf
 

@@ -61,12 +61,13 @@ class Segment:
     numel: int
     master: nn.Parameter = None  # fp32 view of the master shard (what the optimizer updates)
     compute: torch.Tensor | None = None  # view of the compute copy covering the same elements
+    broadcast: tuple | None = None  # (address of the compute arena per rank, multicast address or 0, element offset)
 
 
 class FlatUnit:
     def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], group_of: Callable[[str, nn.Parameter], str],
                  group_order: list[str], shard_world: int, shard_rank: int, compute_dtype: torch.dtype,
-                 device: torch.device) -> None:
+                 device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None) -> None:
         self.name = name
         self.world = shard_world
         self.rank = shard_rank
@@ -90,11 +91,12 @@ class FlatUnit:
         self.shard_range = (lo, lo + self.shard_numel)
 
         aliased = compute_dtype == torch.float32
-        self.compute = torch.zeros(self.numel, dtype=compute_dtype, device=device)
+        new = storage if storage is not None else (lambda n, dtype: torch.zeros(n, dtype=dtype, device=device))
+        self.compute = new(self.numel, compute_dtype)
         # fp32 training keeps no separate master: the shard region of the compute buffer is the master
         self.master = self.compute[lo : lo + self.shard_numel] if aliased else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
         self.master_is_alias = aliased
-        self.grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
+        self.grad = new(self.numel, torch.float32)
         self.grad_shard = self.grad[lo : lo + self.shard_numel]
 
         self.segments: list[Segment] = []
@@ -108,6 +110,14 @@ class FlatUnit:
             seg.compute = None if aliased else self.compute[s0:s1]
             seg.master._lm_engine_segment = seg
             self.segments.append(seg)
+
+    @staticmethod
+    def planned_numel(params: list[tuple[str, nn.Parameter]], shard_world: int) -> int:
+        """Length of the flat buffers a unit of these parameters will have (independent of their order)."""
+        cursor = 0
+        for _, p in params:
+            cursor = _round_up(cursor + p.numel(), _ALIGN)
+        return _round_up(max(cursor, _ALIGN), _ALIGN * shard_world)
 
     # ------------------------------------------------------------------ parameter materialisation
     @torch.no_grad()
@@ -206,12 +216,42 @@ class ShardedTrainingEngine:
         if rest:
             plan.append(("__root__", None, rest))
 
+        storage = self._peer_storage(sum(FlatUnit.planned_numel(params, self.shard_world) for _, _, params in plan))
         for unit_name, module, params in plan:
             unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
-                            self.compute_dtype, self.device)
+                            self.compute_dtype, self.device, storage)
             self._materialise(unit, module)
             self.units.append(unit)
+            if self.peer is not None:
+                arena = self.arenas[self.compute_dtype]
+                for seg in unit.segments:
+                    if seg.compute is not None:
+                        # where the fused optimizer stores the updated values on every rank (element offset in the arena)
+                        seg.broadcast = (arena.ptrs, arena.multicast_ptr, arena.offset_of(seg.compute) // seg.compute.element_size())
         self._materialise_buffers(model)
+
+    def _peer_storage(self, total_numel: int):
+        """With peer-memory collectives every unit's compute and gradient buffers are slices of two symmetric arenas
+        (one rendezvous each), so that kernels can address the same element on every rank. Returns the carving
+        function for :class:`FlatUnit`, or ``None`` to let units allocate ordinary tensors."""
+        self.peer = None
+        self.arenas: dict[torch.dtype, object] = {}
+        if not (self.fused_collectives and self.shard_world > 1 and self.device.type == "cuda" and self.compute_dtype != torch.float32):
+            return None
+        from .symmetric import get_peer_group
+
+        self.peer = get_peer_group(self.shard_group, self.device)
+        if self.peer is None:
+            return None
+        self.arenas = {self.compute_dtype: self.peer.alloc(total_numel, self.compute_dtype), torch.float32: self.peer.alloc(total_numel, torch.float32)}
+        cursors = {dtype: 0 for dtype in self.arenas}
+
+        def carve(numel: int, dtype: torch.dtype) -> torch.Tensor:
+            start = cursors[dtype]
+            cursors[dtype] = start + numel
+            return self.arenas[dtype].tensor[start : start + numel]
+
+        return carve
 
     @torch.no_grad()
     def _materialise(self, unit: FlatUnit, module: nn.Module | None) -> None:
@@ -315,9 +355,17 @@ class ShardedTrainingEngine:
     @torch.no_grad()
     def reduce_gradients(self) -> None:
         """Sum gradients over the data parallel ranks; afterwards ``unit.grad_shard`` holds this rank's slice."""
+        if self.peer is not None:
+            # every rank has finished its backward pass; then each sums its own slice of all copies; then nobody
+            # clears or refills its copy before the others have read it
+            arena = self.arenas[torch.float32]
+            self.peer.barrier()
+            for unit in self.units:
+                self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
+            self.peer.barrier()
         for unit in self.units:
-            if self.shard_world > 1:
-                reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, self.fused_collectives)
+            if self.shard_world > 1 and self.peer is None:
+                reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
             if self.replica_world > 1:
                 all_reduce_sum(unit.grad_shard, self.replica_group)
         self.micro_steps_since_reduce = 0
@@ -359,8 +407,9 @@ class ShardedTrainingEngine:
 
     # ------------------------------------------------------------------ parameter refresh
     @torch.no_grad()
-    def refresh_parameters(self, masters_already_cast: bool = False) -> None:
+    def refresh_parameters(self, masters_already_cast: bool = False, broadcast_done: bool = False) -> None:
         """After the optimizer step: cast updated masters into the compute copy and gather the other shards."""
+        broadcast_by_optimizer = masters_already_cast and broadcast_done and self.peer is not None
         for unit in self.units:
             if not unit.master_is_alias and not masters_already_cast:
                 lo, hi = unit.shard_range
@@ -369,8 +418,17 @@ class ShardedTrainingEngine:
                     ops.native().cast_f32_to_bf16(unit.master, dst)
                 else:
                     dst.copy_(unit.master)
-            if self.shard_world > 1:
-                all_gather_in_place(unit.compute, unit.shard_numel, unit.rank, self.shard_group, self.fused_collectives)
+        if self.shard_world > 1 and not broadcast_by_optimizer:
+            if self.peer is not None:
+                arena = self.arenas[self.compute_dtype]
+                self.peer.barrier()
+                for unit in self.units:
+                    self.peer.all_gather(arena, unit.compute, unit.shard_numel)
+            else:
+                for unit in self.units:
+                    all_gather_in_place(unit.compute, unit.shard_numel, unit.rank, self.shard_group, False)
+        if self.peer is not None:
+            self.peer.barrier()  # every rank's stores into this rank's copy have landed before the next forward pass
 
     # ------------------------------------------------------------------ one optimizer step
     @torch.no_grad()
@@ -391,7 +449,7 @@ class ShardedTrainingEngine:
         optimizer.step()
         if lr_scheduler is not None:
             lr_scheduler.step()
-        self.refresh_parameters(masters_already_cast=fused)
+        self.refresh_parameters(masters_already_cast=fused, broadcast_done=fused and getattr(optimizer, "last_step_broadcast", False))
         if fused and self.shard_world == 1:
             pass  # the fused kernel cleared every gradient element it consumed
         else:
