@@ -50,6 +50,7 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
             communication_dtype=comm_dtype,
             fused_collectives=dist_args.fused_collectives,
             frozen_prefixes=frozen,
+            sequence_parallel=dist_args.sequence_parallel,
         )
         wrapper._lm_engine = engine
         wrapper.model._lm_engine = engine

@@ -377,11 +377,13 @@ class MoE_TP(MoE):
         std_in, std_out = _std(initializer_range, init_method, m_width), _std(initializer_range, init_method, m_width, num_layers)
 
         self.gate = ReplicatedLinear(hidden_size, num_experts, bias=False, std=std_in, partial_grad="sequence_parallel")
+        # construction order = order of the single-device module, so that both draw the same random numbers
         self.c_fc = _ShardedExperts(num_experts, hidden_size, width * intermediate_size, add_bias, std_in, dim=1, parts=width)
+        if shared_intermediate_size is not None:
+            self.c_fc_shared = ColumnParallelLinear(hidden_size, width * shared_intermediate_size, bias=add_bias, std=std_in, parts=width)
         self.act = get_activation_function(activation_function)
         self.c_proj = _ShardedExperts(num_experts, intermediate_size, hidden_size, add_bias, std_out, dim=2)
         if shared_intermediate_size is not None:
-            self.c_fc_shared = ColumnParallelLinear(hidden_size, width * shared_intermediate_size, bias=add_bias, std=std_in, parts=width)
             self.c_proj_shared = RowParallelLinear(shared_intermediate_size, hidden_size, bias=add_bias, std=std_out)
         self.dropout = _dropout(dropout, sequence_parallel)
         for module in (self.gate, self.c_fc, self.c_proj):
@@ -559,10 +561,9 @@ class BaseModelMixin_TP(PreTrainedModelMixin_TP, BaseModelMixin):
         x = self.wte(input_ids) if inputs_embeds is None else inputs_embeds
         if self.position_embedding_type == "learned_absolute":
             pos = self.wpe(position_ids)
-            if pos.dim() == 3 and pos.shape[0] == 1 and x.dim() == 3:
-                pos = pos.expand(x.shape[0] if not self.sequence_parallel else pos.shape[0], -1, -1)
-            if self.sequence_parallel:
-                pos = tp.slice_tokens(pos, tp.token_dim(pos))
+            if self.sequence_parallel and tp.tp_world() > 1:
+                # this rank's tokens only; the gradient of the table is then this rank's share (summed later)
+                pos = pos.chunk(tp.tp_world(), dim=tp.token_dim(pos))[tp.tp_rank()]
             x = x + pos
         if token_type_ids is not None:
             x = x + self.wte(token_type_ids)
@@ -655,6 +656,10 @@ class CausalLMModelMixin_TP(PreTrainedModelMixin_TP, CausalLMModelMixin):
         lm_logits = self.get_lm_logits(hidden_states)
         if self.m_width is not None:
             lm_logits = lm_logits / self.m_width
+        start, end, per_rank = tensor_parallel_vocab_info(self.vocab_size)
+        if end - start < per_rank:  # columns of the vocabulary padding must not take part in the softmax
+            padding = torch.arange(per_rank, device=lm_logits.device) >= max(end - start, 0)
+            lm_logits = lm_logits.masked_fill(padding, float("-inf"))
         loss = None
         if labels is not None:
             loss = get_autoregressive_language_modeling_loss(

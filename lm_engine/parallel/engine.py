@@ -163,8 +163,10 @@ class ShardedTrainingEngine:
         communication_dtype: torch.dtype | None = None,
         fused_collectives: bool = True,
         frozen_prefixes: tuple[str, ...] = (),
+        sequence_parallel: bool = False,
     ) -> None:
         self.model = model
+        self.sequence_parallel = sequence_parallel
         self.compute_dtype = compute_dtype
         self.zero_stage = zero_stage
         self.communication_dtype = communication_dtype
@@ -184,6 +186,8 @@ class ShardedTrainingEngine:
             self.shard_group = self.replica_group = None
             self.shard_world, self.shard_rank, self.replica_world = 1, 0, 1
         self.dp_world = self.shard_world * self.replica_world
+        self.tp_world = ProcessGroupManager.get_tensor_parallel_world_size() if ProcessGroupManager.is_initialized() else 1
+        self.tp_group = ProcessGroupManager.get_tensor_parallel_group() if self.tp_world > 1 else None
 
         if group_of is None:
             from ..optimization.params_group import default_group_of
@@ -354,7 +358,12 @@ class ShardedTrainingEngine:
 
     @torch.no_grad()
     def reduce_gradients(self) -> None:
-        """Sum gradients over the data parallel ranks; afterwards ``unit.grad_shard`` holds this rank's slice."""
+        """Sum gradients over the data parallel ranks; afterwards ``unit.grad_shard`` holds this rank's slice. Under
+        tensor parallelism the partial gradients of replicated parameters are first summed over that group."""
+        if self.tp_world > 1:
+            from ..hf_models.models.tensor_parallel import reduce_tensor_parallel_grads
+
+            reduce_tensor_parallel_grads(self.model, self.sequence_parallel)
         if self.peer is not None:
             # every rank has finished its backward pass; then each sums its own slice of all copies; then nobody
             # clears or refills its copy before the others have read it
@@ -389,8 +398,17 @@ class ShardedTrainingEngine:
             total.zero_()
             for unit in self.units:
                 total.add_(unit.grad_shard.double().pow(2).sum().float())
+        if self.tp_world > 1:
+            # parameters replicated over the tensor-parallel group count once, the sharded ones once per rank
+            replicated = self._replicated_grad_norm_sq()
+            total.sub_(replicated)
+            if self.shard_world > 1:
+                all_reduce_sum(replicated, self.shard_group)
         if self.shard_world > 1:
             all_reduce_sum(total, self.shard_group)
+        if self.tp_world > 1:
+            all_reduce_sum(total, self.tp_group)
+            total.add_(replicated)
         for group in extra_norm_groups or []:
             all_reduce_sum(total, group)
         norm = total.sqrt() * (1.0 / self.dp_world)
@@ -400,6 +418,20 @@ class ShardedTrainingEngine:
         else:
             self.clip_coef.fill_(1.0)
         return self.grad_norm
+
+    def _replicated_grad_norm_sq(self) -> torch.Tensor:
+        """Squared gradient norm of this rank's shard elements that belong to parameters without a tensor-parallel
+        split (identical on every rank of that group after :meth:`reduce_gradients`)."""
+        out = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for unit in self.units:
+            lo, hi = unit.shard_range
+            for slot in unit.slots:
+                if getattr(slot.param, "_tp_shard_dim", None) is not None:
+                    continue
+                a, b = max(slot.offset, lo), min(slot.offset + slot.numel, hi)
+                if b > a:
+                    out += unit.grad_shard[a - lo : b - lo].double().pow(2).sum().float()
+        return out
 
     @property
     def grad_mul(self) -> float:

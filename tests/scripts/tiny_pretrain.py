@@ -1,6 +1,6 @@
 """Runs N optimizer steps of the tiny gpt_base pretraining config on CPU (any world size) and writes the loss curve.
 
-Usage: [torchrun ...] tiny_pretrain.py <output.json> <global_batch> <steps>
+Usage: [torchrun ...] tiny_pretrain.py <output.json> <global_batch> <steps> [zero stage] [tensor parallel size] [sequence parallel 0/1]
 """
 
 import json
@@ -22,7 +22,7 @@ from lm_engine.train_utils import all_reduce_metrics_tracker
 from lm_engine.utils import ProcessGroupManager, StepTracker, init_distributed
 
 
-def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3) -> dict:
+def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, tp: int = 1, sp: bool = False) -> dict:
     layer_attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=4, add_bias=False)
     layer_mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=256, add_bias=False)
     return dict(
@@ -43,16 +43,18 @@ def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3) 
         optimizer_args=dict(class_name="TorchAdamW", class_args=dict(lr=3e-4, weight_decay=0.1, betas=[0.9, 0.95], eps=1e-10)),
         lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=2),
         mixed_precision_args=dict(dtype="fp32"),
-        distributed_args=dict(stage=stage),
+        distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp),
     )
 
 
 def main() -> None:
     out_path, global_batch, steps = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
     stage = int(sys.argv[4]) if len(sys.argv) > 4 else 3
+    tp = int(sys.argv[5]) if len(sys.argv) > 5 else 1
+    sp = bool(int(sys.argv[6])) if len(sys.argv) > 6 else False
     world = int(os.environ.get("WORLD_SIZE", 1))
-    args = args_from_dict(Mode.training, tiny_config(global_batch // world, steps, stage=stage))
-    init_distributed(zero_stage=stage)
+    args = args_from_dict(Mode.training, tiny_config(global_batch // (world // tp), steps, stage=stage, tp=tp, sp=sp))
+    init_distributed(zero_stage=stage, tensor_parallel_world_size=tp)
     StepTracker(args.training_parameters.micro_batch_size, 1)
     set_seed(42)
     container = get_model_container(args, Mode.training)
