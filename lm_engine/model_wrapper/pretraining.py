@@ -85,7 +85,7 @@ class ModelWrapperForPretraining(ModelWrapper):
         inputs = self._prepare_model_inputs(batch)
         labels = inputs.pop("labels")
         if self.is_pipeline_parallel_enabled:
-            return self._forward_pipeline_stage(inputs, labels, aux_loss_from_pipeline_parallel)
+            return self._forward_pipeline_stage(inputs, labels, batch.get("pipeline_parallel_input"), lm_loss_multiplier)
         output = self.model(**inputs, return_dict=True)
         return self.get_loss(output, labels, lm_loss_multiplier=lm_loss_multiplier)
 
@@ -120,10 +120,11 @@ class ModelWrapperForPretraining(ModelWrapper):
         # the model already divided the hidden states by m_width when no labels were passed to it
         return model_outputs.last_hidden_state
 
-    def _forward_pipeline_stage(self, inputs: dict, labels, aux_loss_in):
+    def _forward_pipeline_stage(self, inputs: dict, labels, boundary_input, lm_loss_multiplier: float = 1):
+        """``boundary_input``: ``(hidden_states, aux_loss)`` from the previous stage (``None`` on the first stage)."""
         from ..parallel.pipeline import run_stage
 
-        return run_stage(self, inputs, labels, aux_loss_in)
+        return run_stage(self, inputs, labels, boundary_input, lm_loss_multiplier)
 
     def get_extra_metrics(self) -> MetricsTrackingDict:
         return self._extra_metrics

@@ -380,12 +380,9 @@ class ShardedTrainingEngine:
         self.micro_steps_since_reduce = 0
 
     @torch.no_grad()
-    def clip_grad_norm(self, max_norm: float | None, extra_norm_groups: list | None = None) -> torch.Tensor:
-        """Global gradient norm of the averaged gradient; sets ``self.clip_coef`` (device scalar) for the optimizer.
-
-        Gradients in the buffers are SUMS over data parallel ranks; the averaging factor ``1 / dp_world`` is applied
-        here and inside the optimizer, never by rewriting the buffers.
-        """
+    def grad_norm_sq(self) -> torch.Tensor:
+        """Squared norm of the summed gradient held by this engine's ranks (all data- and tensor-parallel ranks of
+        one pipeline stage), after :meth:`reduce_gradients`. Every parameter counts once."""
         native = ops.native_available() and self.device.type == "cuda"
         total = self._grad_norm_sq
         if native:
@@ -398,6 +395,7 @@ class ShardedTrainingEngine:
             total.zero_()
             for unit in self.units:
                 total.add_(unit.grad_shard.double().pow(2).sum().float())
+        replicated = None
         if self.tp_world > 1:
             # parameters replicated over the tensor-parallel group count once, the sharded ones once per rank
             replicated = self._replicated_grad_norm_sq()
@@ -409,8 +407,23 @@ class ShardedTrainingEngine:
         if self.tp_world > 1:
             all_reduce_sum(total, self.tp_group)
             total.add_(replicated)
-        for group in extra_norm_groups or []:
-            all_reduce_sum(total, group)
+        return total
+
+    @torch.no_grad()
+    def clip_grad_norm(self, max_norm: float | None, extra_norm_groups: list | None = None,
+                       precomputed_norm_sq: torch.Tensor | None = None) -> torch.Tensor:
+        """Global gradient norm of the averaged gradient; sets ``self.clip_coef`` (device scalar) for the optimizer.
+
+        Gradients in the buffers are SUMS over data parallel ranks; the averaging factor ``1 / dp_world`` is applied
+        here and inside the optimizer, never by rewriting the buffers. ``precomputed_norm_sq`` carries a squared norm
+        that already covers more than this engine (all pipeline stages).
+        """
+        if precomputed_norm_sq is None:
+            total = self.grad_norm_sq()
+            for group in extra_norm_groups or []:
+                all_reduce_sum(total, group)
+        else:
+            total = precomputed_norm_sq
         norm = total.sqrt() * (1.0 / self.dp_world)
         self.grad_norm.copy_(norm)
         if max_norm is not None and max_norm > 0:
@@ -465,11 +478,12 @@ class ShardedTrainingEngine:
     # ------------------------------------------------------------------ one optimizer step
     @torch.no_grad()
     def optimizer_step(self, optimizer, lr_scheduler=None, max_norm: float | None = None,
-                       extra_norm_groups: list | None = None) -> torch.Tensor:
+                       extra_norm_groups: list | None = None, precomputed_norm_sq: torch.Tensor | None = None) -> torch.Tensor:
         """Reduce gradients, clip, update the fp32 shards, refresh the compute copy. Returns the gradient norm
         (a device scalar; nothing here synchronises with the host)."""
-        self.reduce_gradients()
-        grad_norm = self.clip_grad_norm(max_norm, extra_norm_groups)
+        if precomputed_norm_sq is None:
+            self.reduce_gradients()
+        grad_norm = self.clip_grad_norm(max_norm, extra_norm_groups, precomputed_norm_sq)
         fused = getattr(optimizer, "writes_compute_copy", False)
         if fused:
             optimizer.grad_scale = self.clip_coef

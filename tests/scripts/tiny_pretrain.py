@@ -1,6 +1,7 @@
 """Runs N optimizer steps of the tiny gpt_base pretraining config on CPU (any world size) and writes the loss curve.
 
 Usage: [torchrun ...] tiny_pretrain.py <output.json> <global_batch> <steps> [zero stage] [tensor parallel size] [sequence parallel 0/1]
+       [pipeline parallel size] [pipeline stages] [schedule] [gradient accumulation steps]
 """
 
 import json
@@ -22,7 +23,8 @@ from lm_engine.train_utils import all_reduce_metrics_tracker
 from lm_engine.utils import ProcessGroupManager, StepTracker, init_distributed
 
 
-def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, tp: int = 1, sp: bool = False) -> dict:
+def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, tp: int = 1, sp: bool = False, pp: int = 1,
+                stages: int = 1, schedule: str | None = None) -> dict:
     layer_attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=4, add_bias=False)
     layer_mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=256, add_bias=False)
     return dict(
@@ -43,7 +45,8 @@ def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, 
         optimizer_args=dict(class_name="TorchAdamW", class_args=dict(lr=3e-4, weight_decay=0.1, betas=[0.9, 0.95], eps=1e-10)),
         lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=2),
         mixed_precision_args=dict(dtype="fp32"),
-        distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp),
+        distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp, pipeline_parallel_world_size=pp,
+                              num_pipeline_stages=stages, pipeline_parallel_schedule=schedule),
     )
 
 
@@ -52,13 +55,33 @@ def main() -> None:
     stage = int(sys.argv[4]) if len(sys.argv) > 4 else 3
     tp = int(sys.argv[5]) if len(sys.argv) > 5 else 1
     sp = bool(int(sys.argv[6])) if len(sys.argv) > 6 else False
+    pp = int(sys.argv[7]) if len(sys.argv) > 7 else 1
+    stages = int(sys.argv[8]) if len(sys.argv) > 8 else 1
+    schedule = sys.argv[9] if len(sys.argv) > 9 else None
+    ga = int(sys.argv[10]) if len(sys.argv) > 10 else 1
     world = int(os.environ.get("WORLD_SIZE", 1))
-    args = args_from_dict(Mode.training, tiny_config(global_batch // (world // tp), steps, stage=stage, tp=tp, sp=sp))
-    init_distributed(zero_stage=stage, tensor_parallel_world_size=tp)
-    StepTracker(args.training_parameters.micro_batch_size, 1)
+    micro = global_batch // (world // (tp * pp)) // ga
+    args = args_from_dict(Mode.training, tiny_config(micro, steps, ga=ga, stage=stage, tp=tp, sp=sp, pp=pp, stages=stages, schedule=schedule))
+    init_distributed(zero_stage=stage, tensor_parallel_world_size=tp, pipeline_parallel_world_size=pp)
+    StepTracker(args.training_parameters.micro_batch_size, ga)
     set_seed(42)
     container = get_model_container(args, Mode.training)
-    container, _ = wrap_model_container_for_distributed_training(args, container)
+    container, pipeline_schedule = wrap_model_container_for_distributed_training(args, container)
+    if len(sys.argv) > 11 and sys.argv[11] == "sync":
+        # every layout starts from the weights of one single-device model, cut to what each rank holds
+        from lm_engine.hf_models import GPTBaseForCausalLM
+        from lm_engine.hf_models.tp_weights import shard_state_dict
+
+        torch.manual_seed(123)
+        reference = GPTBaseForCausalLM(container[0].config)
+        full_state = reference.state_dict()
+        for wrapper in container:
+            if tp > 1 or pp > 1:
+                part = shard_state_dict(wrapper.config, full_state, ProcessGroupManager.get_tensor_parallel_rank(), tp, stages,
+                                        wrapper.pipeline_stage_id)
+            else:
+                part = full_state
+            wrapper._lm_engine.load_full_state_dict({f"model.{k}": v for k, v in part.items()})
     optimizers = get_optimizer_container("TorchAdamW", args.optimizer_args.class_args, container)
     schedulers = get_scheduler_container(container, optimizers, 2, 0, None, steps, args.lr_scheduler_args.lr_decay_style, 0.1, {})
     loader, _, _ = get_pretraining_dataloaders(args, None, 0)
@@ -66,13 +89,22 @@ def main() -> None:
     multiplier = 1 / (args.training_parameters.micro_batch_size * 128)
     curve = []
     for _ in range(steps):
-        metrics = train_step_without_pipeline_parallel(container, optimizers, schedulers, loader, 1.0, lm_loss_multiplier=multiplier)
+        if pipeline_schedule is None:
+            metrics = train_step_without_pipeline_parallel(container, optimizers, schedulers, loader, 1.0, lm_loss_multiplier=multiplier)
+        else:
+            from lm_engine.parallel.pipeline import pipeline_train_step
+
+            metrics = pipeline_train_step(container, pipeline_schedule, optimizers, schedulers, loader, 1.0, 128, lm_loss_multiplier=multiplier)
         for key in list(metrics.keys()):
             metrics[key] = float(metrics[key])
         grad_norm = metrics["grad_norm"]
-        metrics = all_reduce_metrics_tracker(metrics)
-        curve.append({"loss": metrics["loss"], "grad_norm": grad_norm})
-    if ProcessGroupManager.get_global_rank() == 0:
+        has_loss = "loss" in list(metrics.keys())
+        if has_loss:
+            metrics = all_reduce_metrics_tracker(metrics)
+        curve.append({"loss": metrics["loss"] if has_loss else None, "grad_norm": grad_norm})
+    from lm_engine.utils import is_tracking_rank
+
+    if is_tracking_rank():
         with open(out_path, "w") as handle:
             json.dump(curve, handle)
     ProcessGroupManager.destroy_process_groups()
