@@ -71,9 +71,40 @@ void py_adamw_step_bcast(Tensor& p, Tensor& m, Tensor& v, Tensor& g, const std::
                    (float)weight_decay, (float)bc1, (float)bc2, gs, (float)grad_mul, zero_grad, stream_of(p));
 }
 
+bool is_bf16_2d(const Tensor& t) { return t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1; }
+
+// out[M, N] = gather(x)[M, K] . w^T (w: [N, K], or [K, N] when w_mn). staging: [M, K] contiguous with this rank's rows in place.
+void py_ag_gemm(const std::vector<int64_t>& x_ptrs, Tensor& staging, Tensor& ready, int64_t epoch, const Tensor& w, Tensor& out, bool w_mn,
+                int64_t rank, int64_t copy_ctas, Tensor& status) {
+  TORCH_CHECK(is_bf16_2d(staging) && staging.is_contiguous(), "staging: contiguous bf16 [M, K]");
+  TORCH_CHECK(is_bf16_2d(w) && is_bf16_2d(out), "w and out: bf16 matrices with unit inner stride");
+  const int M = (int)staging.size(0), K = (int)staging.size(1);
+  const int N = (int)(w_mn ? w.size(1) : w.size(0));
+  TORCH_CHECK((w_mn ? w.size(0) : w.size(1)) == K && out.size(0) == M && out.size(1) == N, "ag_gemm: shape mismatch");
+  TORCH_CHECK(ready.is_cuda() && ready.scalar_type() == torch::kInt32 && ready.numel() >= M / 128, "ready: int32 flags, one per 128 rows");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status: int32 CUDA tensor");
+  const c10::cuda::CUDAGuard guard(staging.device());
+  ag_gemm_bf16(table(x_ptrs, "ag_gemm"), staging.data_ptr(), ready.data_ptr<int>(), (int)epoch, w.data_ptr(), out.data_ptr(), M, N, K,
+               w.stride(0), out.stride(0), w_mn, (int)rank, (int)copy_ctas, status.data_ptr<int>(), stream_of(staging));
+}
+
+// For every rank r: out_r[M / world, N] (fp32, contiguous, zeroed beforehand) += (x[M, K] . w^T)[rows of r].
+void py_gemm_rs(const Tensor& x, const Tensor& w, const std::vector<int64_t>& out_ptrs, bool w_mn, int64_t rank, Tensor& status) {
+  TORCH_CHECK(is_bf16_2d(x) && is_bf16_2d(w), "x and w: bf16 matrices with unit inner stride");
+  const int M = (int)x.size(0), K = (int)x.size(1);
+  const int N = (int)(w_mn ? w.size(1) : w.size(0));
+  TORCH_CHECK((w_mn ? w.size(0) : w.size(1)) == K, "gemm_rs: shape mismatch");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status: int32 CUDA tensor");
+  const c10::cuda::CUDAGuard guard(x.device());
+  gemm_rs_bf16(x.data_ptr(), w.data_ptr(), table(out_ptrs, "gemm_rs"), M, N, K, x.stride(0), w.stride(0), N, w_mn, (int)rank,
+               status.data_ptr<int>(), stream_of(x));
+}
+
 }  // namespace
 
 void register_comm(py::module_& m) {
+  m.def("ag_gemm", &py_ag_gemm);
+  m.def("gemm_rs", &py_gemm_rs);
   m.def("peer_barrier", &py_peer_barrier);
   m.def("peer_reduce_scatter_f32", &py_peer_reduce_scatter_f32);
   m.def("peer_all_gather", &py_peer_all_gather);

@@ -22,4 +22,10 @@ void adamw_step_bcast(float* p, float* m, float* v, float* g, const PeerPtrs& ds
                       long long n, float lr, float beta1, float beta2, float eps, float weight_decay, float bias_c1, float bias_c2,
                       const float* grad_scale, float grad_mul, bool zero_grad, cudaStream_t stream);
 
+// Fused tensor-parallel GEMMs (tp_gemm.cu).
+void ag_gemm_bf16(const PeerPtrs& x_ptrs, void* staging, int* ready, int epoch, const void* W, void* Y, int M, int N, int K, long long ldw,
+                  long long ldc, bool w_mn, int rank, int copy_ctas, int* status, cudaStream_t stream);
+void gemm_rs_bf16(const void* X, const void* W, const PeerPtrs& out_ptrs, int M, int N, int K, long long ldx, long long ldw, long long ldc,
+                  bool w_mn, int rank, int* status, cudaStream_t stream);
+
 }  // namespace b200

@@ -131,6 +131,11 @@ class ColumnParallelLinear(nn.Module):
         init_zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.sequence_parallel and x.is_cuda:
+            from ...parallel import fused_tp
+
+            if fused_tp.fused_ok(x, self.weight, x.shape[0] * tp.tp_world()):
+                return fused_tp.ag_linear(x, self.weight, self.bias)  # all-gather inside the GEMM kernel
         x = tp.column_parallel_input(x, self.sequence_parallel)
         return ops.linear(x, self.weight, self.bias)
 
@@ -159,6 +164,12 @@ class RowParallelLinear(nn.Module):
         init_zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.sequence_parallel and x.is_cuda:
+            from ...parallel import fused_tp
+
+            if fused_tp.fused_ok(x, self.weight, x.shape[0]):
+                y = fused_tp.linear_rs(x, self.weight)  # reduce-scatter inside the GEMM epilogue
+                return y if self.bias is None else y + self.bias
         y = ops.linear(x, self.weight, None)
         y = tp.row_parallel_output(y, self.sequence_parallel)
         return y if self.bias is None else y + self.bias

@@ -119,11 +119,12 @@ class ProcessGroupManager:
                 del members
             assert _State.ep_group is not None and dp_rank is not None
 
-        if use_async_tensor_parallel and device_type == "cuda":
-            from torch.distributed._symmetric_memory import enable_symm_mem_for_group
+        # asynchronous tensor parallelism = the sequence-parallel linears run their collective inside the GEMM kernel
+        _State.symmetric_memory_enabled = bool(use_async_tensor_parallel and device_type == "cuda")
 
-            enable_symm_mem_for_group(ProcessGroupManager.get_tensor_parallel_group().group_name)
-            _State.symmetric_memory_enabled = True
+    @staticmethod
+    def is_async_tensor_parallel_enabled() -> bool:
+        return _State.symmetric_memory_enabled or os.environ.get("LM_ENGINE_FUSED_TP", "0") == "1"
 
     # ------------------------------------------------------------------ helpers
     @staticmethod
