@@ -88,7 +88,7 @@ void py_ag_gemm(const std::vector<int64_t>& x_ptrs, Tensor& staging, Tensor& rea
                w.stride(0), out.stride(0), w_mn, (int)rank, (int)copy_ctas, status.data_ptr<int>(), stream_of(staging));
 }
 
-// For every rank r: out_r[M / world, N] (fp32, contiguous, zeroed beforehand) += (x[M, K] . w^T)[rows of r].
+// For every rank r: slots_r[this rank][M / world, N] (bf16, contiguous) = (x[M, K] . w^T)[rows of r].
 void py_gemm_rs(const Tensor& x, const Tensor& w, const std::vector<int64_t>& out_ptrs, bool w_mn, int64_t rank, Tensor& status) {
   TORCH_CHECK(is_bf16_2d(x) && is_bf16_2d(w), "x and w: bf16 matrices with unit inner stride");
   const int M = (int)x.size(0), K = (int)x.size(1);
@@ -102,7 +102,18 @@ void py_gemm_rs(const Tensor& x, const Tensor& w, const std::vector<int64_t>& ou
 
 }  // namespace
 
+// out[rows, N] = sum over the `world` slots of slots[world, rows, N] (bf16, fp32 accumulation).
+Tensor py_sum_slots(const Tensor& slots, int64_t world) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == torch::kBFloat16 && slots.is_contiguous() && slots.dim() == 3 && slots.size(0) == world,
+              "slots: contiguous bf16 [world, rows, N]");
+  const c10::cuda::CUDAGuard guard(slots.device());
+  Tensor out = torch::empty({slots.size(1), slots.size(2)}, slots.options());
+  sum_slots_bf16(slots.data_ptr(), out.data_ptr(), out.numel(), (int)world, stream_of(slots));
+  return out;
+}
+
 void register_comm(py::module_& m) {
+  m.def("sum_slots", &py_sum_slots);
   m.def("ag_gemm", &py_ag_gemm);
   m.def("gemm_rs", &py_gemm_rs);
   m.def("peer_barrier", &py_peer_barrier);

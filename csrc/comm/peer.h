@@ -28,4 +28,6 @@ void ag_gemm_bf16(const PeerPtrs& x_ptrs, void* staging, int* ready, int epoch, 
 void gemm_rs_bf16(const void* X, const void* W, const PeerPtrs& out_ptrs, int M, int N, int K, long long ldx, long long ldw, long long ldc,
                   bool w_mn, int rank, int* status, cudaStream_t stream);
 
+void sum_slots_bf16(const void* slots, void* out, long long n, int world, cudaStream_t stream);
+
 }  // namespace b200

@@ -12,10 +12,11 @@
 //   blocks starting with this rank's own rows (already in place), so the first T / tp rows of math hide the transfer;
 //   before the first TMA load of a remote row block the producer thread waits (bounded) for its flag. Every remote
 //   byte crosses NVLink exactly once and is then read from local memory / L2 by all the column tiles that need it.
-// * reduce-scatter: the epilogue adds each fp32 accumulator fragment straight into the owner rank's output with
-//   16-byte `red.global.add.v4.f32` (peer address for remote owners). Row blocks owned by other ranks are computed
-//   first and this rank's own last, so the remote adds drain while local tiles still compute. The outputs must be
-//   zero before any rank starts and complete after all ranks finish: the caller brackets the launch with peer barriers.
+// * reduce-scatter: the epilogue stores each bf16 fragment straight into the owner rank's memory (16-byte peer
+//   stores), into the slot reserved there for this source rank: slots[source][T / tp, N]. Row blocks owned by other
+//   ranks are computed first and this rank's own last, so the remote stores drain while local tiles still compute.
+//   After a peer barrier every rank sums its `tp` slots in fp32 (`sum_slots_bf16`): no atomics, every partial result
+//   crosses NVLink once as bf16, and the sum is in rank order (reproducible).
 //
 // B (the weight) is K-major [N, K] (forward) or MN-major [K, N] (data gradients). A is row-major [T, K].
 // Shapes: T a multiple of 128 * tp; K, N multiples of 8.
@@ -92,12 +93,8 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 struct FusedArgs {
-  PeerPtrs peers;     // AG: X_r of every rank (bf16 [T / tp, K]); RS: fp32 outputs of every rank ([T / tp, N])
+  PeerPtrs peers;     // AG: X_r of every rank (bf16 [T / tp, K]); RS: slot buffers of every rank (bf16 [tp][T / tp, N])
   void* staging;      // AG: local [T, K] bf16 gather target (this rank's own rows already in place)
   int* ready;         // AG: one flag per row block
   int epoch;          // AG: value that marks a flag as set for this launch
@@ -327,19 +324,16 @@ __global__ void __launch_bounds__(THREADS, 1)
         uint32_t v[32];
         B200_TMEM_LD_32(v, t_row + c * 32);
         tmem_ld_wait();
-        if (MODE == MODE_RS) {
-          const int owner = tc.m0 / rows_per_rank;
-          float* dst = reinterpret_cast<float*>(fa.peers.p[owner]) + (long long)(row - owner * rows_per_rank) * ldc + col0;
-          if (col0 + 32 <= N) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              red_add_f32x4(dst + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                            __uint_as_float(v[4 * j + 3]));
+        {
+          __nv_bfloat16* dst;
+          if (MODE == MODE_RS) {
+            // slot of this source rank in the owner's buffer: [world][rows_per_rank][ldc]
+            const int owner = tc.m0 / rows_per_rank;
+            dst = reinterpret_cast<__nv_bfloat16*>(fa.peers.p[owner]) +
+                  ((long long)fa.rank * rows_per_rank + (row - owner * rows_per_rank)) * ldc + col0;
           } else {
-            for (int e = 0; e < 32 && col0 + e < N; ++e) atomicAdd_system(dst + e, __uint_as_float(v[e]));
+            dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (long long)row * ldc + col0;
           }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (long long)row * ldc + col0;
           if (col0 + 32 <= N) {
             uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -367,6 +361,19 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[i] = sum over s of slots[s][i] (bf16 in, fp32 sum in slot order, bf16 out); i in units of 8 elements.
+__global__ void sum_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, long long nv, int world) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = slots[(long long)s * nv + i];
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      acc[0] += a.x, acc[1] += a.y, acc[2] += b.x, acc[3] += b.y, acc[4] += c.x, acc[5] += c.y, acc[6] += d.x, acc[7] += d.y;
+    }
+    out[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
   }
 }
 
@@ -413,17 +420,29 @@ void ag_gemm_bf16(const PeerPtrs& x_ptrs, void* staging, int* ready, int epoch, 
   else launch<0, MODE_AG>(tmA, tmB, Y, M, N, K, ldc, fa, status, stream);
 }
 
-// out_r[M / world, N] (fp32, row stride ldc, zero before the first rank starts) += (X[M, K] . W^T)[rows of r] for every r.
+// slots_r[rank][M / world, N] (bf16, row stride ldc) = (X[M, K] . W^T)[rows of r] for every r; rank r then sums its slots.
 void gemm_rs_bf16(const void* X, const void* W, const PeerPtrs& out_ptrs, int M, int N, int K, long long ldx, long long ldw, long long ldc,
                   bool w_mn, int rank, int* status, cudaStream_t stream) {
   const int world = out_ptrs.n;
   check_shapes(M, N, K, world, "gemm_rs");
-  if (ldx % 8 || ldw % 8 || ldc % 4) throw std::runtime_error("gemm_rs: leading dimensions must be multiples of 8 (inputs) and 4 (output)");
+  if (ldx % 8 || ldw % 8 || ldc % 8) throw std::runtime_error("gemm_rs: leading dimensions must be multiples of 8");
   const CUtensorMap tmA = make_tensor_map_2d_b16(X, K, M, ldx, BK, BM);
   const CUtensorMap tmB = w_mn ? make_tensor_map_2d_b16(W, N, K, ldw, 64, BK) : make_tensor_map_2d_b16(W, K, N, ldw, BK, BN);
   FusedArgs fa{out_ptrs, nullptr, nullptr, 0, rank, world, 0};
   if (w_mn) launch<1, MODE_RS>(tmA, tmB, nullptr, M, N, K, ldc, fa, status, stream);
   else launch<0, MODE_RS>(tmA, tmB, nullptr, M, N, K, ldc, fa, status, stream);
+}
+
+void sum_slots_bf16(const void* slots, void* out, long long n, int world, cudaStream_t stream) {
+  if (n == 0) return;
+  if (n % 8) throw std::runtime_error("sum_slots: length must be a multiple of 8");
+  const long long nv = n / 8;
+  long long blocks = (nv + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  sum_slots_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(slots), reinterpret_cast<uint4*>(out), nv, world);
+  count_launch();
+  check_cuda(cudaGetLastError(), "sum_slots launch");
 }
 
 }  // namespace b200

@@ -92,6 +92,35 @@ class ParameterizedExperts(nn.Module):
         return f"num_experts={self.num_experts}, in_features={self.in_features}, out_features={self.out_features}"
 
 
+class ExpertParallelExperts(ParameterizedExperts):
+    """The ``num_experts / ep`` experts of this rank of the expert-parallel group. Initialisation draws the whole bank
+    and keeps this rank's experts, so the group starts from the weights a single device would have."""
+
+    def __init__(self, num_experts: int, in_features: int, out_features: int, add_bias: bool = False, std: float | None = None) -> None:
+        self.ep_world = ProcessGroupManager.get_expert_parallel_world_size()
+        self.ep_rank = ProcessGroupManager.get_expert_parallel_rank()
+        self.num_global_experts = num_experts
+        if num_experts % self.ep_world != 0:
+            raise ValueError("the number of experts must be divisible by the expert parallel size")
+        super().__init__(num_experts // self.ep_world, in_features, out_features, add_bias=add_bias, std=std)
+        for p in self.parameters():
+            p._expert_parallel = True
+
+    @torch.no_grad()
+    def reset_parameters(self) -> None:
+        from .basic import loaded_from_checkpoint
+
+        if not loaded_from_checkpoint(self.weight):
+            full = torch.empty(self.num_global_experts, *self.weight.shape[1:], dtype=torch.float32, device=self.weight.device)
+            full.normal_(mean=0.0, std=self.std if self.std is not None else 0.02)
+            self.weight.copy_(full.chunk(self.ep_world)[self.ep_rank])
+        init_zeros_(self.bias)
+
+
+def _expert_parallel_world() -> int:
+    return ProcessGroupManager.get_expert_parallel_world_size() if ProcessGroupManager.is_initialized() else 1
+
+
 class MoE(nn.Module):
     linear_class = ParameterizedExperts
 
@@ -111,14 +140,16 @@ class MoE(nn.Module):
         width = 2 if self.is_glu else 1
 
         self.gate = ParameterizedLinear(hidden_size, num_experts, bias=False, std=_std(initializer_range, init_method, m_width))
-        self.c_fc = ParameterizedExperts(num_experts, hidden_size, width * intermediate_size, add_bias=add_bias,
-                                         std=_std(initializer_range, init_method, m_width))
+        self.expert_parallel = _expert_parallel_world() > 1
+        bank = ExpertParallelExperts if self.expert_parallel else ParameterizedExperts
+        self.c_fc = bank(num_experts, hidden_size, width * intermediate_size, add_bias=add_bias,
+                         std=_std(initializer_range, init_method, m_width))
         if shared_intermediate_size is not None:
             self.c_fc_shared = ParameterizedLinear(hidden_size, width * shared_intermediate_size, bias=add_bias,
                                                    std=_std(initializer_range, init_method, m_width))
         self.act = get_activation_function(activation_function)
-        self.c_proj = ParameterizedExperts(num_experts, intermediate_size, hidden_size, add_bias=add_bias,
-                                           std=_std(initializer_range, init_method, m_width, num_layers))
+        self.c_proj = bank(num_experts, intermediate_size, hidden_size, add_bias=add_bias,
+                           std=_std(initializer_range, init_method, m_width, num_layers))
         if shared_intermediate_size is not None:
             self.c_proj_shared = ParameterizedLinear(shared_intermediate_size, hidden_size, bias=add_bias,
                                                      std=_std(initializer_range, init_method, m_width, num_layers))
@@ -159,6 +190,11 @@ class MoE(nn.Module):
                                      self.top_k, self.activation_function)
 
     def experts(self, x: torch.Tensor, weights: torch.Tensor, selected: torch.Tensor) -> torch.Tensor:
+        if self.expert_parallel:
+            from ...parallel.expert_parallel import expert_parallel_mlp
+
+            return expert_parallel_mlp(x, self.c_fc.weight, self.c_proj.weight, self.c_fc.bias, self.c_proj.bias, weights, selected,
+                                       self.num_experts, self.top_k, self.activation_function, self.act)
         if is_kernel_allowed(Kernel.scattermoe) and self.c_fc.bias is None:
             from ...ops.moe import native_moe_ok
 

@@ -69,6 +69,7 @@ class FlatUnit:
                  group_order: list[str], shard_world: int, shard_rank: int, compute_dtype: torch.dtype,
                  device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None) -> None:
         self.name = name
+        self.local_only = False  # True: this rank's own parameters (expert parallelism), no collective touches them
         self.world = shard_world
         self.rank = shard_rank
         self.compute_dtype = compute_dtype
@@ -220,13 +221,30 @@ class ShardedTrainingEngine:
         if rest:
             plan.append(("__root__", None, rest))
 
-        storage = self._peer_storage(sum(FlatUnit.planned_numel(params, self.shard_world) for _, _, params in plan))
+        # Expert-parallel parameters differ from rank to rank (every rank owns other experts) and receive the gradient
+        # of all ranks' tokens through the dispatch: they get units of their own that are never reduced or gathered.
+        split_plan = []
         for unit_name, module, params in plan:
-            unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
-                            self.compute_dtype, self.device, storage)
-            self._materialise(unit, module)
+            local = [(n, p) for n, p in params if getattr(p, "_expert_parallel", False)]
+            shared = [(n, p) for n, p in params if not getattr(p, "_expert_parallel", False)]
+            if shared:
+                split_plan.append((unit_name, module, shared, False))
+            if local:
+                split_plan.append((unit_name + ".experts", module, local, True))
+
+        storage = self._peer_storage(sum(FlatUnit.planned_numel(params, self.shard_world) for _, _, params, local in split_plan if not local))
+        materialised: set[int] = set()
+        for unit_name, module, params, local_only in split_plan:
+            if local_only:
+                unit = FlatUnit(unit_name, params, group_of, self.group_order, 1, 0, self.compute_dtype, self.device, None)
+            else:
+                unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
+                                self.compute_dtype, self.device, storage)
+            unit.local_only = local_only
+            self._materialise(unit, module if id(module) not in materialised else None)
+            materialised.add(id(module))
             self.units.append(unit)
-            if self.peer is not None:
+            if self.peer is not None and not local_only:
                 arena = self.arenas[self.compute_dtype]
                 for seg in unit.segments:
                     if seg.compute is not None:
@@ -370,9 +388,12 @@ class ShardedTrainingEngine:
             arena = self.arenas[torch.float32]
             self.peer.barrier()
             for unit in self.units:
-                self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
+                if not unit.local_only:
+                    self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
             self.peer.barrier()
         for unit in self.units:
+            if unit.local_only:
+                continue
             if self.shard_world > 1 and self.peer is None:
                 reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
             if self.replica_world > 1:
@@ -468,10 +489,12 @@ class ShardedTrainingEngine:
                 arena = self.arenas[self.compute_dtype]
                 self.peer.barrier()
                 for unit in self.units:
-                    self.peer.all_gather(arena, unit.compute, unit.shard_numel)
+                    if not unit.local_only:
+                        self.peer.all_gather(arena, unit.compute, unit.shard_numel)
             else:
                 for unit in self.units:
-                    all_gather_in_place(unit.compute, unit.shard_numel, unit.rank, self.shard_group, False)
+                    if not unit.local_only:
+                        all_gather_in_place(unit.compute, unit.shard_numel, unit.rank, self.shard_group, False)
         if self.peer is not None:
             self.peer.barrier()  # every rank's stores into this rank's copy have landed before the next forward pass
 

@@ -1,0 +1,246 @@
+"""Expert parallelism: every rank of the group owns ``num_experts / ep`` experts and serves the tokens of all ranks.
+
+The reference has no expert parallelism (its MoE is sharded by FSDP or sliced by tensor parallelism); this is the
+engine's own design for NVLink domains. Dispatch and combine are not all-to-all collectives: token rows stay where they
+were produced, in symmetric memory, and the kernels that feed and drain the grouped GEMMs read them from there.
+
+forward, on every rank (T local tokens, k experts per token, E_local local experts):
+  1. all-gather of the routing decisions (``[ep, T, k]`` expert ids and weights: a few hundred KB, NCCL)
+  2. layout of the (token, slot) entries of ALL ranks that picked a local expert: expert-grouped rows, every expert
+     padded to a multiple of 128 rows (device ops only, static upper bound on the row count)
+  3. ``moe_gather`` pulls those token rows from the owners' activations through peer pointers (dispatch)
+  4. grouped tcgen05 GEMM (c_fc) -> SwiGLU -> grouped GEMM (c_proj), output rows in symmetric memory
+  5. all-to-all of the row numbers (int32) so that every token owner knows where its k results are
+  6. ``moe_combine`` sums the k rows of each local token straight from the owners' output buffers, weighted (combine)
+backward mirrors it: the output gradient is pulled like the tokens, the input gradient combined like the outputs, and
+the gradient of the routing weights travels back with one small all-to-all. Bounded peer barriers order the phases.
+
+On CPU (and for tensors the kernels do not take) ``expert_parallel_mlp`` falls back to a differentiable gather ->
+local experts -> reduce-scatter over the group with the same results, which is what the gloo tests run.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops.moe import TILE, _wgrad, build_grouped_layout
+from ..utils import ProcessGroupManager
+from .symmetric import PeerBuffer, PeerGroup, get_peer_group
+
+_WORKSPACES: dict[int, "_Workspace"] = {}
+
+
+def ep_world() -> int:
+    return ProcessGroupManager.get_expert_parallel_world_size() if ProcessGroupManager.is_initialized() else 1
+
+
+def ep_rank() -> int:
+    return ProcessGroupManager.get_expert_parallel_rank() if ProcessGroupManager.is_initialized() else 0
+
+
+def ep_group():
+    return ProcessGroupManager.get_expert_parallel_group()
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# reference path: plain collectives, any device
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        pieces = [torch.empty_like(x) for _ in range(ep_world())]
+        dist.all_gather(pieces, x.contiguous(), group=ep_group())
+        return torch.cat(pieces, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        total = g.contiguous().clone()
+        dist.all_reduce(total, group=ep_group())
+        return total.chunk(ep_world(), dim=0)[ep_rank()].contiguous()
+
+
+class _ScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        total = x.contiguous().clone()
+        dist.all_reduce(total, group=ep_group())
+        return total.chunk(ep_world(), dim=0)[ep_rank()].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        pieces = [torch.empty_like(g) for _ in range(ep_world())]
+        dist.all_gather(pieces, g.contiguous(), group=ep_group())
+        return torch.cat(pieces, dim=0)
+
+
+def _reference(x, w_fc, w_proj, b_fc, b_proj, weights, selected, num_experts, activation):
+    local = w_fc.shape[0]
+    first = ep_rank() * local
+    x_all = _GatherRows.apply(x)
+    weights_all = _GatherRows.apply(weights)
+    selected_all = torch.cat(_all_gather_plain(selected), dim=0)
+    out = torch.zeros_like(x_all)
+    for e in range(local):
+        token, slot = torch.where(selected_all == first + e)
+        if token.numel() == 0:
+            continue
+        h = torch.nn.functional.linear(x_all[token], w_fc[e], None if b_fc is None else b_fc[e])
+        h = torch.nn.functional.linear(activation(h), w_proj[e], None if b_proj is None else b_proj[e])
+        out = out.index_add(0, token, h * weights_all[token, slot].unsqueeze(-1))
+    return _ScatterRows.apply(out)
+
+
+def _all_gather_plain(t: torch.Tensor) -> list[torch.Tensor]:
+    pieces = [torch.empty_like(t) for _ in range(ep_world())]
+    dist.all_gather(pieces, t.contiguous(), group=ep_group())
+    return pieces
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# peer-memory path
+class _Workspace:
+    """Symmetric buffers of one expert-parallel group, shared by all layers (they run one after the other)."""
+
+    def __init__(self, peer: PeerGroup) -> None:
+        self.peer = peer
+        self.tokens: PeerBuffer | None = None  # [T, H] rows this rank owns (activations, or their gradients)
+        self.rows: PeerBuffer | None = None  # [rows, H] rows this rank computed (expert outputs, or input gradients)
+
+    def buffer(self, attr: str, numel: int) -> PeerBuffer:
+        buf = getattr(self, attr)
+        if buf is None or buf.tensor.numel() < numel:
+            buf = self.peer.alloc(numel, torch.bfloat16, zero=False)
+            setattr(self, attr, buf)
+        return buf
+
+
+def workspace(device: torch.device) -> _Workspace | None:
+    key = id(ep_group())
+    if key not in _WORKSPACES:
+        peer = get_peer_group(ep_group(), device)
+        _WORKSPACES[key] = None if peer is None else _Workspace(peer)
+    return _WORKSPACES[key]
+
+
+def _exchange_rows(dest_row: torch.Tensor, entries: int, rows: int) -> torch.Tensor:
+    """``dest_row``: for all ``ep * entries`` global entries, the row on THIS rank (-1 if another rank's expert).
+    Returns for this rank's ``entries`` the global row ``owner * rows + row`` on the owner."""
+    world = ep_world()
+    received = torch.empty_like(dest_row)
+    dist.all_to_all_single(received, dest_row.contiguous(), group=ep_group())
+    received = received.view(world, entries)
+    owner = received.argmax(dim=0)  # exactly one owner reports a row >= 0
+    local = received.max(dim=0).values
+    return (owner.to(torch.int32) * rows + local).to(torch.int32).contiguous()
+
+
+def _exchange_values(per_entry: torch.Tensor, entries: int) -> torch.Tensor:
+    """Sum over owners of a per-entry fp32 value computed for all global entries (zero where not owned)."""
+    received = torch.empty_like(per_entry)
+    dist.all_to_all_single(received, per_entry.contiguous(), group=ep_group())
+    return received.view(ep_world(), entries).sum(dim=0)
+
+
+class _ExpertParallelFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, num_experts, top_k):
+        C = ops.native()
+        st = ops.status_word(x.device)
+        ws = workspace(x.device)
+        peer = ws.peer
+        world, rank = peer.world, peer.rank
+        T, H = x.shape
+        local = w_fc.shape[0]
+        entries = T * top_k
+
+        selected_all = torch.cat(_all_gather_plain(selected_experts.reshape(-1).to(torch.int32)))
+        weights_all = torch.cat(_all_gather_plain(router_weights.reshape(-1).float()))
+        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local)
+        rows = layout.rows
+
+        tokens = ws.buffer("tokens", T * H)
+        out_rows = ws.buffer("rows", rows * H)
+        peer.barrier()  # the previous users of the buffers are done everywhere
+        tokens.tensor[: T * H].view(T, H).copy_(x)
+        peer.barrier()  # every rank's tokens are readable
+        xg = C.moe_gather(tokens.ptrs, [], layout.src_entry, H, entries, top_k, x)  # dispatch: pull rows from their owners
+        fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
+        del xg
+        act = C.swiglu_fwd(fc)
+        y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
+        del act
+        out_rows.tensor[: rows * H].view(rows, H).copy_(y)
+        del y
+        global_row = _exchange_rows(layout.dest_row, entries, rows)
+        peer.barrier()  # every rank's expert outputs are readable
+        weights32 = router_weights.reshape(-1).float().contiguous()
+        out = C.moe_combine(out_rows.ptrs, global_row, weights32, T, H, top_k, rows, x)  # combine: pull the k results per token
+
+        ctx.save_for_backward(x, w_fc, w_proj, weights_all, fc, layout.dest_row, layout.src_entry, layout.tile_expert,
+                              layout.padded_offsets, global_row)
+        ctx.meta = (num_experts, top_k, rows, router_weights.dtype, router_weights.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w_fc, w_proj, weights_all, fc, dest_row, src_entry, tile_expert, padded_offsets, global_row = ctx.saved_tensors
+        num_experts, top_k, rows, w_dtype, w_shape = ctx.meta
+        C = ops.native()
+        st = ops.status_word(x.device)
+        ws = workspace(x.device)
+        peer = ws.peer
+        T, H = x.shape
+        entries = T * top_k
+        tokens = ws.buffer("tokens", T * H)
+        out_rows = ws.buffer("rows", rows * H)
+
+        peer.barrier()
+        tokens.tensor[: T * H].view(T, H).copy_(dout)
+        peer.barrier()
+        dyg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x)  # output gradients of the rows computed here
+        dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)
+        act = C.swiglu_fwd(fc)
+        # gradient of the routing weight of every entry served here, sent back to the token owners
+        served = dest_row >= 0
+        per_entry = C.moe_rowdot(dact, act, dest_row).reshape(-1).float()  # one value per global entry, 0 where not served here
+        d_weights = _exchange_values(per_entry, entries).view(w_shape).to(w_dtype)
+
+        row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
+        row_weight[torch.where(served, dest_row, torch.full_like(dest_row, rows)).long()] = weights_all
+        row_weight = row_weight[:rows].contiguous()
+        C.scale_rows_(act, row_weight)
+        g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
+        del dyg, act
+        C.scale_rows_(dact, row_weight)
+        dfc = C.swiglu_bwd(dact, fc, False)[0]
+        del dact
+
+        peer.barrier()  # all ranks have pulled the output gradients; the token buffer can take the activations again
+        tokens.tensor[: T * H].view(T, H).copy_(x)
+        peer.barrier()
+        xg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x)
+        g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
+        del xg
+        dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)
+        out_rows.tensor[: rows * H].view(rows, H).copy_(dxg)
+        del dxg
+        peer.barrier()
+        dx = C.moe_combine(out_rows.ptrs, global_row, None, T, H, top_k, rows, x)
+        return dx, g_fc, g_proj, d_weights, None, None, None
+
+
+def native_ok(x: torch.Tensor, w_fc: torch.Tensor, activation_function: str, has_bias: bool) -> bool:
+    from ..ops.moe import native_moe_ok
+
+    return (not has_bias and native_moe_ok(x, activation_function) and w_fc.dtype == torch.bfloat16 and x.dim() == 2
+            and hasattr(ops.native(), "peer_barrier") and workspace(x.device) is not None)
+
+
+def expert_parallel_mlp(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor, b_fc, b_proj, router_weights: torch.Tensor,
+                        selected_experts: torch.Tensor, num_experts: int, top_k: int, activation_function: str, activation) -> torch.Tensor:
+    """``sum_s router_weights[t, s] * expert[selected[t, s]](x[t])`` where the experts live on the ranks of the
+    expert-parallel group (``w_fc`` / ``w_proj`` hold this rank's ``num_experts / ep``)."""
+    if native_ok(x, w_fc, activation_function, b_fc is not None):
+        return _ExpertParallelFn.apply(x.contiguous(), w_fc, w_proj, router_weights, selected_experts, num_experts, top_k)
+    return _reference(x, w_fc, w_proj, b_fc, b_proj, router_weights, selected_experts, num_experts, activation)

@@ -2,8 +2,8 @@
 
 ``ag_linear``    ``y[T, N] = gather(x_local)[T, K] @ w^T``: gather CTAs pull the other ranks' rows over NVLink into a
                  local staging buffer while the tensor-core CTAs already work on this rank's rows.
-``linear_rs``    ``y_local[T / tp, N] = reduce_scatter(x[T, K] @ w^T)``: the epilogue adds fp32 fragments into the owner
-                 rank's buffer with vector ``red`` operations.
+``linear_rs``    ``y_local[T / tp, N] = reduce_scatter(x[T, K] @ w^T)``: the epilogue stores bf16 fragments into the
+                 owner rank's slot for this source rank; each rank then sums its slots in fp32.
 
 Both are differentiable; each backward is the other kernel on the transposed weight plus a weight-gradient GEMM that
 accumulates into ``weight.main_grad`` when the training engine provides it. This is the role async tensor parallelism
@@ -30,7 +30,7 @@ class _Workspace:
     def __init__(self, peer: PeerGroup) -> None:
         self.peer = peer
         self.x_sym: PeerBuffer | None = None  # this rank's rows, readable by the others (bf16)
-        self.out_sym: PeerBuffer | None = None  # fp32 reduce-scatter target
+        self.out_sym: PeerBuffer | None = None  # reduce-scatter target: one bf16 slot per source rank
         self.staging: torch.Tensor | None = None  # gathered rows (bf16)
         self.ready = torch.zeros(1 << 16, dtype=torch.int32, device=peer.device)
         self.epoch = 0
@@ -68,14 +68,11 @@ class _Workspace:
         total, _ = x.shape
         rows = total // world
         n = w.shape[1] if w_mn else w.shape[0]
-        out_sym = self._grow("out_sym", rows * n, torch.float32)
-        out = out_sym.tensor[: rows * n]
-        peer.barrier()  # the previous result has been consumed everywhere (also orders the growth above)
-        out.zero_()
-        peer.barrier()  # all targets are zero before anybody adds
+        out_sym = self._grow("out_sym", world * rows * n, torch.bfloat16)
+        peer.barrier()  # every rank has summed its slots of the previous call
         ops.native().gemm_rs(x, w, out_sym.ptrs, w_mn, rank, ops.status_word(x.device))
-        peer.barrier()  # all adds have landed
-        return out.view(rows, n).to(torch.bfloat16)
+        peer.barrier()  # every rank's partial results have landed in this rank's slots
+        return ops.native().sum_slots(out_sym.tensor[: world * rows * n].view(world, rows, n), world)
 
 
 def workspace() -> _Workspace | None:

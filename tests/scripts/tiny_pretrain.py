@@ -1,7 +1,8 @@
 """Runs N optimizer steps of the tiny gpt_base pretraining config on CPU (any world size) and writes the loss curve.
 
 Usage: [torchrun ...] tiny_pretrain.py <output.json> <global_batch> <steps> [zero stage] [tensor parallel size] [sequence parallel 0/1]
-       [pipeline parallel size] [pipeline stages] [schedule] [gradient accumulation steps]
+       [pipeline parallel size] [pipeline stages] [schedule] [gradient accumulation steps] [sync|nosync] [expert parallel size:
+       the model then has mixture-of-experts MLPs]
 """
 
 import json
@@ -24,9 +25,11 @@ from lm_engine.utils import ProcessGroupManager, StepTracker, init_distributed
 
 
 def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, tp: int = 1, sp: bool = False, pp: int = 1,
-                stages: int = 1, schedule: str | None = None) -> dict:
+                stages: int = 1, schedule: str | None = None, ep: int = 0) -> dict:
     layer_attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=4, add_bias=False)
     layer_mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=256, add_bias=False)
+    if ep > 0:
+        layer_mlp = dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, add_bias=False, num_experts=4, num_experts_per_tok=2)
     return dict(
         datasets=[dict(class_name="SyntheticDataset", data_name="synthetic", class_args=dict(sequence_length=128, seed=7))],
         model_args=dict(
@@ -46,7 +49,7 @@ def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, 
         lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=2),
         mixed_precision_args=dict(dtype="fp32"),
         distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp, pipeline_parallel_world_size=pp,
-                              num_pipeline_stages=stages, pipeline_parallel_schedule=schedule),
+                              num_pipeline_stages=stages, pipeline_parallel_schedule=schedule, **({"expert_parallel_world_size": ep} if ep > 1 else {})),
     )
 
 
@@ -59,10 +62,11 @@ def main() -> None:
     stages = int(sys.argv[8]) if len(sys.argv) > 8 else 1
     schedule = sys.argv[9] if len(sys.argv) > 9 else None
     ga = int(sys.argv[10]) if len(sys.argv) > 10 else 1
+    ep = int(sys.argv[12]) if len(sys.argv) > 12 else 0
     world = int(os.environ.get("WORLD_SIZE", 1))
     micro = global_batch // (world // (tp * pp)) // ga
-    args = args_from_dict(Mode.training, tiny_config(micro, steps, ga=ga, stage=stage, tp=tp, sp=sp, pp=pp, stages=stages, schedule=schedule))
-    init_distributed(zero_stage=stage, tensor_parallel_world_size=tp, pipeline_parallel_world_size=pp)
+    args = args_from_dict(Mode.training, tiny_config(micro, steps, ga=ga, stage=stage, tp=tp, sp=sp, pp=pp, stages=stages, schedule=schedule, ep=ep))
+    init_distributed(zero_stage=stage, tensor_parallel_world_size=tp, pipeline_parallel_world_size=pp, expert_parallel_world_size=max(ep, 1))
     StepTracker(args.training_parameters.micro_batch_size, ga)
     set_seed(42)
     container = get_model_container(args, Mode.training)
@@ -72,11 +76,20 @@ def main() -> None:
         from lm_engine.hf_models import GPTBaseForCausalLM
         from lm_engine.hf_models.tp_weights import shard_state_dict
 
+        from lm_engine.utils import parallel as parallel_state
+
+        saved_ep = parallel_state._State.ep_world_size
+        parallel_state._State.ep_world_size = 1  # the reference holds all experts
         torch.manual_seed(123)
         reference = GPTBaseForCausalLM(container[0].config)
+        parallel_state._State.ep_world_size = saved_ep
         full_state = reference.state_dict()
         for wrapper in container:
-            if tp > 1 or pp > 1:
+            if ep > 1:
+                per = 4 // ep
+                lo = ProcessGroupManager.get_expert_parallel_rank() * per
+                part = {k: (v[lo : lo + per] if ".mlp_block.c_fc." in k or ".mlp_block.c_proj." in k else v) for k, v in full_state.items()}
+            elif tp > 1 or pp > 1:
                 part = shard_state_dict(wrapper.config, full_state, ProcessGroupManager.get_tensor_parallel_rank(), tp, stages,
                                         wrapper.pipeline_stage_id)
             else:

@@ -58,3 +58,12 @@ def test_fused_tensor_parallel_gemms_match_nccl():
            "--master-port", "29535", os.path.join(ROOT, "tests", "scripts", "fused_tp_check.py")]
     done = subprocess.run(cmd, env=dict(os.environ, NCCL_DEBUG="WARN"), capture_output=True, text=True, timeout=900)
     assert done.returncode == 0 and "FUSED_TP_OK" in done.stdout, (done.stdout[-3000:], done.stderr[-3000:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_over_peer_memory_matches_single_device():
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", "29537", os.path.join(ROOT, "tests", "scripts", "ep_check.py")]
+    done = subprocess.run(cmd, env=dict(os.environ, NCCL_DEBUG="WARN"), capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0 and "EP_CHECK_OK" in done.stdout, (done.stdout[-3000:], done.stderr[-3000:])
