@@ -27,15 +27,15 @@ def main():
     cuda = torch.cuda.is_available()
     device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
     dtype = torch.bfloat16 if cuda else torch.float32
-    if cuda:
+    from contextlib import nullcontext
+
+    def context():
+        if not cuda:
+            return nullcontext()
         from lm_engine.enums import Kernel
         from lm_engine.kernels import enable_kernels
 
-        context = enable_kernels([Kernel.scattermoe])
-    else:
-        from contextlib import nullcontext
-
-        context = nullcontext()
+        return enable_kernels([Kernel.scattermoe])
 
     for hidden, inter, experts, top_k, tokens in ((64, 32, 8, 2, 96), (256, 128, 8, 4, 512)) if not cuda else ((512, 256, 8, 2, 1024), (1536, 512, 40, 8, 2048)):
         if experts % world:
@@ -57,7 +57,7 @@ def main():
         dy_all = (torch.randn(world * tokens, hidden, device=device) * 0.1).to(dtype)
         x = x_all[rank * tokens : (rank + 1) * tokens].clone().requires_grad_(True)
         x_ref = x_all.clone().requires_grad_(True)
-        with context:
+        with context():
             y = local(x)
             y.backward(dy_all[rank * tokens : (rank + 1) * tokens])
             y_ref = full(x_ref)
