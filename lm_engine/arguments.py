@@ -384,7 +384,8 @@ _ARGS_OF_MODE = {
 
 
 def args_from_dict(mode: Mode, config: dict) -> TrainingArgs | InferenceArgs | UnshardingArgs | DistillationArgs:
-    return _ARGS_OF_MODE[mode](**config)
+    # top-level keys that start with an underscore only hold YAML anchors (shared layer descriptions)
+    return _ARGS_OF_MODE[mode](**{k: v for k, v in config.items() if not k.startswith("_")})
 
 
 def get_args(mode: Mode, argv: list[str] | None = None):
