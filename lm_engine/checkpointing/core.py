@@ -96,6 +96,32 @@ def _to_full(value: torch.Tensor) -> torch.Tensor:
     return value
 
 
+def _as_expert_sharded(local: torch.Tensor, engine) -> torch.Tensor:
+    """Expert-parallel parameters: every rank of the sharding group holds other experts, i.e. its tensor IS the rank's
+    dim-0 shard of the bank of all experts."""
+    if not _distributed() or engine.shard_world == 1:
+        return local
+    from torch.distributed.tensor import DTensor, Shard
+
+    assert engine.replica_world == 1, "expert parallelism spans the sharding group of the engine"
+    mesh = ProcessGroupManager.get_mesh()["fsdp"]
+    shape = (local.shape[0] * engine.shard_world, *local.shape[1:])
+    stride = torch.empty(shape, device="meta").stride()
+    return DTensor.from_local(local.contiguous(), mesh, [Shard(0)], run_check=False, shape=torch.Size(shape), stride=stride)
+
+
+def _view(unit, full_slot: torch.Tensor, engine) -> torch.Tensor:
+    return _as_expert_sharded(full_slot, engine) if getattr(unit, "local_only", False) else _as_sharded(full_slot, engine)
+
+
+def _local_value(unit, value: torch.Tensor, engine) -> torch.Tensor:
+    """What this rank keeps of a loaded tensor: everything, or (expert-parallel units) its own experts."""
+    full = _to_full(value) if isinstance(value, torch.Tensor) else value
+    if getattr(unit, "local_only", False) and engine.shard_world > 1 and full.dim() > 0:
+        return full.chunk(engine.shard_world, dim=0)[engine.shard_rank]
+    return full
+
+
 def _unit_full_fp32(unit, engine, source: str, optimizer=None) -> torch.Tensor:
     """Gather one flat quantity of a unit (``master``, ``exp_avg`` or ``exp_avg_sq``) from all shards."""
     from ..parallel.collectives import all_gather_in_place
@@ -136,7 +162,7 @@ def get_model_state_dict(model_container) -> dict[str, torch.Tensor]:
         for unit in engine.units:
             full = _unit_full_fp32(unit, engine, "master")
             for slot in unit.slots:
-                out[slot.name] = _as_sharded(full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
+                out[slot.name] = _view(unit, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
             del full
     return out
 
@@ -149,7 +175,7 @@ def set_model_state_dict(model_container, state: dict[str, torch.Tensor]) -> Non
             continue
         for unit, slot in engine.named_slots():
             if slot.name in state:
-                unit.adopt(slot, _to_full(state[slot.name]).reshape(slot.shape).to(device=engine.device, dtype=torch.float32))
+                unit.adopt(slot, _local_value(unit, state[slot.name], engine).reshape(slot.shape).to(device=engine.device, dtype=torch.float32))
 
 
 def _hyperparameters(group: dict) -> dict:
@@ -189,7 +215,7 @@ def get_optimizer_state_dict(model_container, optimizer_container) -> dict[str, 
             fulls = {f: _unit_full_fp32(unit, engine, f, optimizer) for f in fields}
             for slot in unit.slots:
                 for f, full in fulls.items():
-                    out[f"state.{slot.name}.{f}"] = _as_sharded(full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
+                    out[f"state.{slot.name}.{f}"] = _view(unit, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
                 out[f"state.{slot.name}.step"] = torch.tensor(float(step_of_group_name.get(slot.group, 0)))
                 for key, value in hyper_of_group_name.get(slot.group, {}).items():
                     out[f"param_groups.{slot.name}.{key}"] = value
@@ -218,7 +244,7 @@ def set_optimizer_state_dict(model_container, optimizer_container, state: dict[s
                 for slot in unit.slots:
                     key = f"state.{slot.name}.{f}"
                     if key in state:
-                        full[slot.offset : slot.offset + slot.numel].copy_(_to_full(state[key]).reshape(-1))
+                        full[slot.offset : slot.offset + slot.numel].copy_(_local_value(unit, state[key], engine).reshape(-1))
                 _scatter_unit_quantity(unit, full, f, optimizer)
             for seg in unit.segments:
                 first = next(s for s in unit.slots if s.group == seg.group)

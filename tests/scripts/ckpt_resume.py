@@ -1,5 +1,5 @@
 """Phase "save": train 3 steps, checkpoint, train 2 more and record their losses. Phase "resume": load the checkpoint
-and train the 2 steps again. Usage: [torchrun ...] ckpt_resume.py <phase> <save_dir> <out.json> [async]"""
+and train the 2 steps again. Usage: [torchrun ...] ckpt_resume.py <phase> <save_dir> <out.json> [async|sync] [expert parallel size]"""
 
 import json
 import os
@@ -28,12 +28,13 @@ def main() -> None:
     phase, save_dir, out_path = sys.argv[1], sys.argv[2], sys.argv[3]
     use_async = len(sys.argv) > 4 and sys.argv[4] == "async"
     world = int(os.environ.get("WORLD_SIZE", 1))
-    config = tiny_config(8 // world, 5)
+    ep = int(sys.argv[5]) if len(sys.argv) > 5 else 0
+    config = tiny_config(8 // world, 5, ep=ep)
     config["save_args"] = dict(save_path=save_dir, save_interval=3, async_checkpointing=use_async)
     if phase == "resume":
         config["load_args"] = dict(load_path=save_dir)
     args = args_from_dict(Mode.training, config)
-    init_distributed(zero_stage=3)
+    init_distributed(zero_stage=3, expert_parallel_world_size=max(ep, 1))
     StepTracker(args.training_parameters.micro_batch_size, 1)
     set_seed(42 if phase == "save" else 7)  # a resumed run must not depend on its own seed
     container = get_model_container(args, Mode.training)

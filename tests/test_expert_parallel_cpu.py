@@ -32,3 +32,16 @@ def test_expert_parallel_training_matches_single_process(tmp_path):
     for a, b in zip(json.loads(single.read_text()), json.loads(double.read_text())):
         assert abs(a["loss"] - b["loss"]) < 2e-5 * max(1.0, abs(a["loss"]))
         assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-4 * max(1.0, abs(a["grad_norm"]))
+
+
+def test_expert_parallel_checkpoint_resume(tmp_path):
+    """Save after 3 steps with the experts spread over two ranks, resume, and get the losses of the uninterrupted run."""
+    save_dir, a, b = tmp_path / "ckpt", tmp_path / "a.json", tmp_path / "b.json"
+    for phase, port, out in (("save", 29587, a), ("resume", 29589, b)):
+        done = subprocess.run(_torchrun(2, port, "ckpt_resume.py", phase, str(save_dir), str(out), "sync", "2"), env=ENV, cwd=str(tmp_path),
+                              capture_output=True, text=True, timeout=900)
+        assert done.returncode == 0, done.stderr[-4000:]
+    first, second = json.loads(a.read_text()), json.loads(b.read_text())
+    assert len(first["losses"]) == len(second["losses"]) == 2
+    for x, y in zip(first["losses"], second["losses"]):
+        assert abs(x - y) < 2e-5 * max(1.0, abs(x)), (first, second)
