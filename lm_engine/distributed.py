@@ -20,6 +20,8 @@ from .utils import ProcessGroupManager, log_rank_0, string_to_torch_dtype
 
 def wrap_model_container_for_distributed_training(args, model_container: ModelContainer):
     dist_args = args.distributed_args
+    if args.mixed_precision_args.dtype == "fp8":
+        raise NotImplementedError("fp8 training (block-scaled e4m3 GEMMs) is not built yet; use dtype: bf16")
     dtype = string_to_torch_dtype(args.mixed_precision_args.dtype)
     comm_dtype = None if dist_args.communication_dtype is None else string_to_torch_dtype(dist_args.communication_dtype)
     if dist_args.stage not in (0, 2, 3):
