@@ -21,6 +21,7 @@ void register_data_helpers(pybind11::module_& m);
 void register_attention(pybind11::module_& m);
 void register_moe(pybind11::module_& m);
 void register_comm(pybind11::module_& m);
+void register_sequence(pybind11::module_& m);
 }  // namespace b200
 
 namespace {
@@ -322,5 +323,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   b200::register_attention(m);
   b200::register_moe(m);
   b200::register_comm(m);
+  b200::register_sequence(m);
   b200::register_data_helpers(m);
 }

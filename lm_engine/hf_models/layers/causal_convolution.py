@@ -49,7 +49,12 @@ class CausalConvolution(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, ctx: SequenceContext, past_key_values=None) -> torch.Tensor:
         x = self.input_projection(hidden_states)
-        if ctx.packed:
+        depthwise = self.num_groups == self.in_channels == self.conv1d.out_channels
+        if ctx.packed and depthwise and x.is_cuda:
+            from ...ops.sequence import causal_conv1d_packed
+
+            y = causal_conv1d_packed(x, self.conv1d.weight, self.conv1d.bias, ctx.cu_seqlens)  # no host round trip
+        elif ctx.packed:
             bounds = ctx.cu_seqlens.tolist()
             pieces = [self._conv(x[s:e].t().unsqueeze(0), None).squeeze(0).t() for s, e in zip(bounds[:-1], bounds[1:]) if e > s]
             y = torch.cat(pieces, dim=0)

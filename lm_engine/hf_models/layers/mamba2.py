@@ -81,6 +81,7 @@ class Mamba2(nn.Module):
         self.chunk_size = chunk_size
         self.time_step_limit = tuple(time_step_limit)
         self.activation = get_activation_function(ssm_activation_function)
+        self._silu_activation = ssm_activation_function in ("silu", "swish")
 
         std = initializer_range / (math.sqrt(m_width) if init_method == "mup" else 1)
         self.conv_dim = self.intermediate_size + 2 * self.n_groups * self.ssm_state_size
@@ -127,8 +128,16 @@ class Mamba2(nn.Module):
         if mask is not None:
             xbc = xbc * mask[..., None].to(xbc.dtype)
         conv_in = xbc.transpose(1, 2)
-        conv_out = self.conv1d(conv_in)[..., : conv_in.shape[-1]]
-        xbc_act = self.activation(conv_out.transpose(1, 2))
+        if xbc.is_cuda and self._silu_activation and self.conv_kernel_size <= 8:
+            from ...ops.sequence import causal_conv1d_packed
+
+            # every row of the batch is one sequence: depthwise conv + SiLU in one kernel on the [tokens, channels] layout
+            rows, length = xbc.shape[:2]
+            cu = torch.arange(0, rows * length + 1, length, dtype=torch.int32, device=xbc.device)
+            xbc_act = causal_conv1d_packed(xbc.reshape(rows * length, -1), self.conv1d.weight, self.conv1d.bias, cu, "silu").view_as(xbc)
+        else:
+            conv_out = self.conv1d(conv_in)[..., : conv_in.shape[-1]]
+            xbc_act = self.activation(conv_out.transpose(1, 2))
         if mask is not None:
             xbc_act = xbc_act * mask[..., None].to(xbc_act.dtype)
         x, b, c, dt = self._ssm_inputs(xbc_act, dt)

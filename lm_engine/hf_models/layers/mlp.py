@@ -164,6 +164,11 @@ class MoE(nn.Module):
     # ------------------------------------------------------------------ routing
     def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         logits = self.gate(x)
+        if x.is_cuda and logits.dim() == 2 and is_kernel_allowed(Kernel.scattermoe):
+            from ...ops.sequence import topk_route
+
+            weights, experts, _ = topk_route(logits, self.top_k)  # one kernel: top-k + softmax of the selected logits
+            return logits, weights.type_as(x), experts
         if self.top_k == 1:
             top_logits, experts = logits.max(dim=-1, keepdim=True)
         else:
