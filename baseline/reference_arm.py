@@ -101,7 +101,11 @@ def _run(cli, spec: dict, repo_root: str):
     attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=spec["num_attention_heads"],
                 num_key_value_heads=spec["num_key_value_heads"], add_bias=False)
     mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=spec["intermediate_size"], add_bias=False)
+    if "num_experts" in spec:  # the reference's MoE: FSDP over the expert bank, eager per-expert loop (its scattermoe kernel is absent)
+        mlp = dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=spec["intermediate_size"], add_bias=False,
+                   num_experts=spec["num_experts"], num_experts_per_tok=spec["num_experts_per_tok"])
     pretrained_config = dict(
+        router_aux_loss_coef=spec.get("router_aux_loss_coef", 0.001),
         model_type="gpt_base", vocab_size=spec["vocab_size"], hidden_size=spec["hidden_size"], num_layers=layers,
         max_position_embeddings=seq, position_embedding_type="rope", rope_theta=spec["rope_theta"],
         normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.02, tie_word_embeddings=False,
@@ -123,7 +127,7 @@ def _run(cli, spec: dict, repo_root: str):
                                 unk_token="<unk>").save_pretrained(tokenizer_dir)
     notes.append("stub 4-token tokenizer created locally (the reference requires tokenizer_args.tokenizer_name)")
 
-    checkpointing = world == 1 and cli.layers is None
+    checkpointing = world == 1 and cli.layers is None and "num_experts" not in spec  # the 8B dense model does not fit one GPU otherwise
     distributed_args = dict(stage=3, fsdp_algorithm=2, communication_dtype="fp32", torch_compile=False)
     if checkpointing:
         distributed_args["gradient_checkpointing_method"] = "block"
@@ -238,7 +242,8 @@ def _run(cli, spec: dict, repo_root: str):
     tokens_per_step = ga * mb * seq * world
     tflops = get_model_tflops(container[0].config, ga * mb * world, seq, None, {}) / world / (ms_per_step / 1e3)
     result = {
-        "impl": "reference", "metric": "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)",
+        "impl": "reference", "metric": ("pretraining tokens/s (40-expert top-8 MoE, expert parallel)" if "num_experts" in spec else
+                                        "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)"),
         "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": cli.steps,
         "warmup": cli.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",

@@ -33,6 +33,15 @@ DENSE_8B = dict(
     intermediate_size=14336, rope_theta=500000, sequence_length=4096, micro_batch_size=2, gradient_accumulation_steps=16,
 )
 
+# BASELINE config 5: scattered-MoE decoder, 40 experts top-8; experts spread over the GPUs (expert parallel = world size)
+MOE_40E = dict(
+    name="moe-40e-top8-gpt_base",
+    vocab_size=49152, hidden_size=1536, num_layers=32, num_attention_heads=24, num_key_value_heads=8,
+    intermediate_size=512, num_experts=40, num_experts_per_tok=8, router_aux_loss_coef=0.01, rope_theta=10000,
+    sequence_length=4096, micro_batch_size=4, gradient_accumulation_steps=4,
+)
+SPECS = {"dense": DENSE_8B, "moe": MOE_40E}
+
 
 def parse_args():
     p = argparse.ArgumentParser()
@@ -40,6 +49,7 @@ def parse_args():
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    p.add_argument("--config", type=str, default="dense", choices=sorted(SPECS), help="dense: 8B dense FSDP (headline); moe: 40-expert top-8 MoE")
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not the headline config)")
     p.add_argument("--gradient-accumulation-steps", type=int, default=None, help="debug only")
     p.add_argument("--skip-e2e", action="store_true")
@@ -51,7 +61,11 @@ def model_config(spec: dict, layers: int | None) -> dict:
     attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=spec["num_attention_heads"],
                 num_key_value_heads=spec["num_key_value_heads"], add_bias=False)
     mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=spec["intermediate_size"], add_bias=False)
+    if "num_experts" in spec:
+        mlp = dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=spec["intermediate_size"], add_bias=False,
+                   num_experts=spec["num_experts"], num_experts_per_tok=spec["num_experts_per_tok"])
     return dict(
+        router_aux_loss_coef=spec.get("router_aux_loss_coef", 0.001),
         model_type="gpt_base", vocab_size=spec["vocab_size"], hidden_size=spec["hidden_size"], num_layers=n,
         max_position_embeddings=spec["sequence_length"], position_embedding_type="rope", rope_theta=spec["rope_theta"],
         normalization_function="rmsnorm", layer_norm_epsilon=1e-5, initializer_range=0.02, tie_word_embeddings=False,
@@ -157,12 +171,15 @@ def run_native(cli) -> dict:
 
     set_logger("WARNING")
     ops.require_native()
-    spec = DENSE_8B
+    spec = SPECS[cli.config]
+    moe = "num_experts" in spec
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
-    args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels))
+    expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
+    extra = {"expert_parallel_world_size": expert_parallel} if expert_parallel > 1 else None
+    args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
 
-    init_distributed(zero_stage=3)
+    init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel)
     world = ProcessGroupManager.get_world_size()
     assert world == cli.gpus, f"--gpus {cli.gpus} but WORLD_SIZE={world}"
     rank = ProcessGroupManager.get_global_rank()
@@ -246,12 +263,14 @@ def run_native(cli) -> dict:
     peak, peak_src = measured_peak_tflops()
     tflops_per_gpu = tflops_model / world / (ms_per_step / 1e3)
     result = {
-        "impl": "native", "metric": "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)", "value": value, "unit": "tokens/s",
+        "impl": "native", "metric": ("pretraining tokens/s (40-expert top-8 MoE, expert parallel)" if moe else
+                                     "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)"), "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": cli.steps, "warmup": cli.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
         "config": {"model": spec["name"] + ("" if cli.layers is None else f"-DEBUG-{cli.layers}-layers"),
                    "global_batch": ga * mb * world, "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
-                   "parallelism": f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; gathered bf16 weights kept for the step)",
+                   "parallelism": (f"ep{expert_parallel} x " if moe else "") +
+                   f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; gathered bf16 weights kept for the step)",
                    "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)"},
         "tflops_per_gpu": tflops_per_gpu, "mfu": tflops_per_gpu / peak, "mfu_peak": f"{peak} TFLOP/s {peak_src}",
         "clocks": clocks, "gpu_launches": launches, "loss_after_warmup": loss_after_warmup,
@@ -269,7 +288,7 @@ def main() -> None:
     if cli.impl == "reference":
         from baseline.reference_arm import run_reference
 
-        result = run_reference(cli, DENSE_8B, REPO_ROOT)
+        result = run_reference(cli, SPECS[cli.config], REPO_ROOT)
     else:
         result = run_native(cli)
     if result is not None:

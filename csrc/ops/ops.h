@@ -46,4 +46,9 @@ void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss, f
                            long long row_stride, float logit_scale, float grad_scale, long long ignore_index,
                            bool write_grad, cudaStream_t stream);
 
+// fp8 GEMM (gemm/gemm_fp8.cu): a_fmt / b_fmt 0 = e4m3, 1 = e5m2; scale_a / scale_b device fp32 scalars or null.
+void gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
+              bool b_mn, int a_fmt, int b_fmt, int epi, float alpha, const float* scale_a, const float* scale_b, int* status,
+              cudaStream_t stream);
+
 }  // namespace b200

@@ -20,8 +20,6 @@ from .utils import ProcessGroupManager, log_rank_0, string_to_torch_dtype
 
 def wrap_model_container_for_distributed_training(args, model_container: ModelContainer):
     dist_args = args.distributed_args
-    if args.mixed_precision_args.dtype == "fp8":
-        raise NotImplementedError("fp8 training (block-scaled e4m3 GEMMs) is not built yet; use dtype: bf16")
     dtype = string_to_torch_dtype(args.mixed_precision_args.dtype)
     comm_dtype = None if dist_args.communication_dtype is None else string_to_torch_dtype(dist_args.communication_dtype)
     if dist_args.stage not in (0, 2, 3):
@@ -59,6 +57,12 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
         if hasattr(wrapper, "teacher_model") and wrapper.teacher_model is not None:
             wrapper.teacher_model.to(device)
         log_rank_0(logging.INFO, f"sharded engine: {engine.memory_summary()}")
+
+    if args.mixed_precision_args.dtype == "fp8":
+        from .fp8 import FP8Manager
+
+        manager = FP8Manager([w.model for w in model_container])
+        log_rank_0(logging.INFO, f"fp8: {manager.converted} linear layers run tensor-scaled e4m3/e5m2 GEMMs (compute dtype of the rest: bf16)")
 
     pipeline_schedule = None
     if dist_args.num_pipeline_stages > 1:

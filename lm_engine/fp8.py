@@ -1,0 +1,109 @@
+"""8-bit floating point training of the linear layers (API parity: lm_engine/fp8.py:51-101).
+
+The reference converts linears with ``torchao.float8`` (one dynamic scale per tensor). Here the same numerics run on
+this engine's own kernels: per-tensor dynamic scaling, e4m3 for activations and weights, e5m2 for output gradients,
+fp32 accumulation in the tcgen05 ``kind::f8f6f4`` GEMM (``csrc/gemm/gemm_fp8.cu``), which reads K-major and MN-major
+operands, so the forward, data-gradient and weight-gradient products use the same three quantised tensors and no
+transposed copies. Block-scaled (MX, 1x32) operands are not built yet.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+E4M3, E5M2 = 0, 1
+
+
+def quantize(x: torch.Tensor, fmt: int = E4M3) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(uint8 payload shaped like x, fp32 device scalar to multiply back with)``; no host synchronisation."""
+    x = x.contiguous()
+    amax = x.abs().amax().float().reshape(1)
+    q, scale_inv = ops.native().quantize_fp8(x if x.dtype == torch.bfloat16 else x.bfloat16(), amax, fmt)
+    return q, scale_inv
+
+
+def dequantize(q: torch.Tensor, scale_inv: torch.Tensor, fmt: int = E4M3) -> torch.Tensor:
+    dtype = torch.float8_e4m3fn if fmt == E4M3 else torch.float8_e5m2
+    return q.view(dtype).float() * scale_inv
+
+
+class _FP8Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        C, st = ops.native(), ops.status_word(x.device)
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        xq, xs = quantize(x2, E4M3)
+        wq, ws = quantize(weight, E4M3)
+        y = torch.empty(x2.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+        C.gemm_fp8(xq, wq, y, False, False, E4M3, E4M3, False, 1.0, xs, ws, st)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(xq, xs, wq, ws)
+        ctx.weight, ctx.shape, ctx.has_bias = weight, shape, bias is not None
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, xs, wq, ws = ctx.saved_tensors
+        weight = ctx.weight
+        C, st = ops.native(), ops.status_word(dy.device)
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        gq, gs = quantize(dy2, E5M2)
+        # dx[T, in] = dy[T, out] . W[out, in]: W read MN-major
+        dx = torch.empty(dy2.shape[0], weight.shape[1], dtype=torch.bfloat16, device=dy.device)
+        C.gemm_fp8(gq, wq, dx, False, True, E5M2, E4M3, False, 1.0, gs, ws, st)
+        # dW[out, in] = dy^T . x: both read MN-major; accumulated into the fp32 main gradient when the engine provides one
+        target = getattr(weight, "main_grad", None)
+        if target is not None:
+            C.gemm_fp8(gq, xq, target, True, True, E5M2, E4M3, True, 1.0, gs, xs, st)
+            dw = None
+        else:
+            dw32 = torch.empty(weight.shape, dtype=torch.float32, device=dy.device)
+            C.gemm_fp8(gq, xq, dw32, True, True, E5M2, E4M3, False, 1.0, gs, xs, st)
+            dw = dw32.to(weight.dtype)
+        db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx.view(ctx.shape), dw, db
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    return _FP8Linear.apply(x, weight, bias)
+
+
+def _eligible(module: nn.Module) -> bool:
+    return isinstance(module, nn.Linear) and module.in_features % 16 == 0 and module.out_features % 16 == 0
+
+
+class FP8Manager:
+    """Switches the linear layers of every model of a container to fp8 GEMMs (the output projection / LM head stays in
+    bf16, like in the reference). The scaling-type arguments are accepted for compatibility; scaling is dynamic."""
+
+    def __init__(self, model_container, enable_fsdp_fp8_all_gather: bool = False, precompute_fp8_dynamic_scale_for_fsdp: bool = False,
+                 torch_compile: bool = False, scaling_type_input=None, scaling_type_weight=None, scaling_type_grad_output=None) -> None:
+        if not ops.native_available() or not hasattr(ops.native(), "gemm_fp8"):
+            raise RuntimeError("fp8 training needs the sm_100a extension")
+        self.converted = 0
+        for model in model_container:
+            for name, module in model.named_modules():
+                if hasattr(module, "_fusable"):
+                    module._fusable = False  # the whole-block bf16 schedule would bypass the converted linears
+                if _eligible(module) and not name.endswith(("lm_head", "output")):
+                    module.forward = _fp8_forward.__get__(module, type(module))
+                    self.converted += 1
+
+    @staticmethod
+    def precompute_float8_dynamic_scale_for_fsdp(model_container) -> None:
+        """Nothing to do: weights are quantised from the gathered bf16 copy when they are used."""
+
+    @staticmethod
+    def sync_float8_amax_and_scale_history(model_container) -> None:
+        """Nothing to do: scaling is dynamic (no amax history)."""
+
+
+def _fp8_forward(self, x: torch.Tensor) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.numel() // x.shape[-1] % 16 == 0:
+        return fp8_linear(x, self.weight, self.bias)
+    return ops.linear(x, self.weight, self.bias)
