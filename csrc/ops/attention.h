@@ -18,4 +18,8 @@ void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, co
                      const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale,
                      bool causal, int* status, cudaStream_t stream);
 
+// Stick-breaking attention forward (sb_attention_fwd.cu): same buffers; rem: [groups * qpg, T] fp32 = 1 - sum of weights.
+void sb_attn_varlen_fwd(const void* qkv, long long qkv_stride, void* out, long long out_stride, float* rem, const int* cu_seqlens,
+                        int num_docs, int T, int groups, int qpg, int head_dim, float scale, int* status, cudaStream_t stream);
+
 }  // namespace b200

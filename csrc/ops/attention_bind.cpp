@@ -51,9 +51,26 @@ Tensor attn_bwd(const Tensor& dout, const Tensor& qkv, const Tensor& out, const 
   return dqkv;
 }
 
+// Stick-breaking attention: returns (out [T, groups*qpg*d] bf16 without the head-bias term, rem [groups*qpg, T] fp32).
+std::vector<Tensor> sb_attn_fwd(const Tensor& qkv, const Tensor& cu_seqlens, int64_t groups, int64_t qpg, int64_t d, double scale,
+                                const c10::optional<Tensor>& status) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == torch::kBFloat16 && qkv.dim() == 2 && qkv.stride(1) == 1, "qkv: [T, C] bf16");
+  TORCH_CHECK(cu_seqlens.is_cuda() && cu_seqlens.scalar_type() == torch::kInt32 && cu_seqlens.is_contiguous(), "cu_seqlens: int32");
+  TORCH_CHECK(qkv.size(1) >= groups * (qpg + 2) * d, "qkv row is too narrow");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int64_t T = qkv.size(0);
+  Tensor out = torch::empty({T, groups * qpg * d}, qkv.options());
+  Tensor rem = torch::empty({groups * qpg, T}, qkv.options().dtype(torch::kFloat32));
+  sb_attn_varlen_fwd(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), rem.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
+                     (int)cu_seqlens.numel() - 1, (int)T, (int)groups, (int)qpg, (int)d, (float)scale, status_of(status),
+                     at::cuda::getCurrentCUDAStream().stream());
+  return {out, rem};
+}
+
 }  // namespace
 
 void register_attention(pybind11::module_& m) {
+  m.def("sb_attn_fwd", &sb_attn_fwd);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
 }

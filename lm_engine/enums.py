@@ -46,6 +46,7 @@ Kernel = _enum(
         "ladder_residual_overlapped_layer",
         # additions of this engine
         "gemm_tcgen05",
+        "stickbreaking_attention",
         "rope_fused",
         "fused_block",
         "adamw_fused",

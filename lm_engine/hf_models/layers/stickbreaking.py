@@ -39,6 +39,41 @@ def stickbreaking_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     return out.to(q.dtype), rem.to(q.dtype)
 
 
+class _FusedStickBreaking(torch.autograd.Function):
+    """Forward: the sm_100a kernel on the fused qkv buffer of a packed batch. Backward: the dense fp32 formulation above,
+    recomputed document by document under autograd (a backward kernel does not exist yet)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cu_seqlens, groups, group_size, head_dim, scale):
+        from ... import ops
+
+        out, rem = ops.native().sb_attn_fwd(qkv, cu_seqlens, groups, group_size, head_dim, scale, ops.status_word(qkv.device))
+        ctx.save_for_backward(qkv, cu_seqlens)
+        ctx.meta = (groups, group_size, head_dim, scale)
+        return out, rem
+
+    @staticmethod
+    def backward(ctx, d_out, d_rem):
+        qkv, cu_seqlens = ctx.saved_tensors
+        groups, g, d, scale = ctx.meta
+        d_qkv = torch.zeros_like(qkv)
+        bounds = cu_seqlens.tolist()
+        for s, e in zip(bounds[:-1], bounds[1:]):
+            if e <= s:
+                continue
+            with torch.enable_grad():
+                piece = qkv[s:e].detach().requires_grad_(True)
+                v4 = piece.view(e - s, groups, g + 2, d)
+                q = v4[:, :, :g].reshape(e - s, groups * g, d).transpose(0, 1)
+                k = v4[:, :, g].repeat_interleave(g, dim=1).transpose(0, 1)
+                v = v4[:, :, g + 1].repeat_interleave(g, dim=1).transpose(0, 1)
+                out, rem = stickbreaking_attention(q, k, v, scale)  # [h, n, d], [h, n]
+                out = out.transpose(0, 1).reshape(e - s, groups * g * d)
+                torch.autograd.backward([out, rem], [d_out[s:e].to(out.dtype), d_rem[:, s:e].to(rem.dtype)])
+            d_qkv[s:e] = piece.grad
+        return d_qkv, None, None, None, None, None
+
+
 class StickBreakingAttention(Attention):
     def __init__(self, hidden_size: int, num_attention_heads: int, num_key_value_heads: int,
                  attention_multiplier: float | None, add_bias: bool, dropout: float, init_method: str,
@@ -52,6 +87,14 @@ class StickBreakingAttention(Attention):
                          use_padding_free_transformer=use_padding_free_transformer)
         self.head_bias = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
         self.norm = nn.GroupNorm(self.num_heads, self.hidden_size)
+
+    def _kernel_ok(self, qkv: torch.Tensor) -> bool:
+        from ... import ops
+        from ...enums import Kernel
+        from ...kernels import is_kernel_allowed
+
+        return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.native_available()
+                and hasattr(ops.native(), "sb_attn_fwd") and is_kernel_allowed(Kernel.stickbreaking_attention))
 
     def _heads(self, qkv: torch.Tensor):
         """``[n, C] -> q [hq, n, d], k / v [hq, n, d]`` (keys and values repeated over their query group)."""
@@ -70,7 +113,13 @@ class StickBreakingAttention(Attention):
 
     def forward(self, hidden_states: torch.Tensor, ctx: SequenceContext, past_key_values=None) -> torch.Tensor:
         qkv = self.c_attn(hidden_states)
-        if ctx.packed:
+        if ctx.packed and self._kernel_ok(qkv):
+            out, rem = _FusedStickBreaking.apply(qkv.contiguous(), ctx.cu_seqlens_int32(), self.num_key_value_heads, self.group_size,
+                                                 self.head_dim, self.softmax_scale)
+            tokens = qkv.shape[0]
+            mixed = out.view(tokens, self.num_heads, self.head_dim) + rem.t().unsqueeze(-1).to(out.dtype) * self.head_bias.to(out.dtype)
+            mixed = self.norm(mixed.reshape(tokens, self.hidden_size))
+        elif ctx.packed:
             bounds = ctx.cu_seqlens.tolist()
             pieces = [self._mix(*self._heads(qkv[s:e])) for s, e in zip(bounds[:-1], bounds[1:]) if e > s]
             mixed = torch.cat(pieces, dim=0)

@@ -294,3 +294,39 @@ def test_scattered_experts_fwd_bwd(C, T, H, I, E, k):
     assert _rel_err(w_fc.grad, wf.grad) < 2e-2
     assert _rel_err(w_proj.grad, wp.grad) < 2e-2
     assert _rel_err(weights.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,groups,qpg", [(64, 2, 2), (128, 1, 4)])
+def test_stickbreaking_attention_forward_matches_dense_formulation(head_dim, groups, qpg):
+    """The kernel on a packed fused-qkv buffer against the fp32 dense formulation, document by document; gradients flow
+    through the recomputing backward."""
+    from lm_engine import ops
+    from lm_engine.hf_models.layers.stickbreaking import _FusedStickBreaking, stickbreaking_attention
+
+    torch.manual_seed(0)
+    lengths = [300, 1, 129, 514]
+    bounds = [0]
+    for n in lengths:
+        bounds.append(bounds[-1] + n)
+    T = bounds[-1]
+    cu = torch.tensor(bounds, dtype=torch.int32, device="cuda")
+    width = groups * (qpg + 2) * head_dim
+    qkv = (torch.randn(T, width, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+    scale = head_dim**-0.5
+    out, rem = _FusedStickBreaking.apply(qkv, cu, groups, qpg, head_dim, scale)
+    ops.check_status()
+    ref_out, ref_rem = [], []
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        v4 = qkv[s:e].detach().float().view(e - s, groups, qpg + 2, head_dim)
+        q = v4[:, :, :qpg].reshape(e - s, groups * qpg, head_dim).transpose(0, 1)
+        k = v4[:, :, qpg].repeat_interleave(qpg, dim=1).transpose(0, 1)
+        v = v4[:, :, qpg + 1].repeat_interleave(qpg, dim=1).transpose(0, 1)
+        o, r = stickbreaking_attention(q, k, v, scale)
+        ref_out.append(o.transpose(0, 1).reshape(e - s, -1))
+        ref_rem.append(r)
+    ref_out, ref_rem = torch.cat(ref_out), torch.cat(ref_rem, dim=1)
+    torch.testing.assert_close(out.float(), ref_out, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(rem, ref_rem, atol=2e-2, rtol=2e-2)
+    (out.float().square().sum() + rem.sum()).backward()
+    assert torch.isfinite(qkv.grad).all() and float(qkv.grad.abs().sum()) > 0
