@@ -133,7 +133,13 @@ Tensor rmsnorm_bwd(const Tensor& dy, const Tensor& h, const Tensor& w, const Ten
   return dh;
 }
 
-Tensor swiglu_fwd(const Tensor& x) {
+const int* tile_owner_ptr(const c10::optional<Tensor>& t, int64_t rows) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt32 && t->is_contiguous() && t->numel() * 128 >= rows, "tile_owner: int32, one entry per 128 rows");
+  return t->data_ptr<int>();
+}
+
+Tensor swiglu_fwd(const Tensor& x, const c10::optional<Tensor>& tile_owner, int64_t owners) {
   check_bf16(x, "x");
   TORCH_CHECK(x.is_contiguous(), "swiglu input must be contiguous");
   const int64_t I = x.size(-1) / 2;
@@ -142,11 +148,11 @@ Tensor swiglu_fwd(const Tensor& x) {
   sizes.back() = I;
   const c10::cuda::CUDAGuard guard(x.device());
   Tensor y = torch::empty(sizes, x.options());
-  b200::swiglu_fwd(x.data_ptr(), y.data_ptr(), T, (int)I, cur_stream());
+  b200::swiglu_fwd(x.data_ptr(), y.data_ptr(), T, (int)I, cur_stream(), tile_owner_ptr(tile_owner, T), (int)owners);
   return y;
 }
 
-std::vector<Tensor> swiglu_bwd(const Tensor& dy, const Tensor& x, bool recompute_y) {
+std::vector<Tensor> swiglu_bwd(const Tensor& dy, const Tensor& x, bool recompute_y, const c10::optional<Tensor>& tile_owner, int64_t owners) {
   check_bf16(dy, "dy");
   check_bf16(x, "x");
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous(), "swiglu_bwd inputs must be contiguous");
@@ -160,7 +166,7 @@ std::vector<Tensor> swiglu_bwd(const Tensor& dy, const Tensor& x, bool recompute
     y = torch::empty_like(dy);
     yp = y.data_ptr();
   }
-  b200::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), yp, T, (int)I, cur_stream());
+  b200::swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), yp, T, (int)I, cur_stream(), tile_owner_ptr(tile_owner, T), (int)owners);
   if (recompute_y) return {dx, y};
   return {dx};
 }
@@ -308,8 +314,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("eps"),
         py::arg("want_sum") = true);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd, py::arg("x"), py::arg("tile_owner") = py::none(), py::arg("owners") = 0);
+  m.def("swiglu_bwd", &swiglu_bwd, py::arg("dy"), py::arg("x"), py::arg("recompute_y"), py::arg("tile_owner") = py::none(), py::arg("owners") = 0);
   m.def("rope_", &rope_);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);

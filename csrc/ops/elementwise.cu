@@ -21,11 +21,15 @@ inline int ew_grid(long long work_items, int threads) {
 
 // ------------------------------------------------------------------------- SwiGLU
 // x is [T, 2I] with up = x[:, :I], gate = x[:, I:]; y = up * silu(gate).
-__global__ void swiglu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long T, int Iv) {
+// `tile_owner` (optional): one entry per 128 rows; rows of tiles whose entry is >= `owners` hold no data and are skipped
+// (expert-grouped buffers are sized for the worst case, only the used tiles are touched).
+__global__ void swiglu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long T, int Iv,
+                                  const int* __restrict__ tile_owner, int owners) {
   const long long total = T * Iv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / Iv;
+    if (tile_owner != nullptr && tile_owner[t >> 7] >= owners) continue;
     const int c = (int)(idx - t * Iv);
     const uint4 u = x[t * 2 * Iv + c];
     const uint4 g = x[t * 2 * Iv + Iv + c];
@@ -42,11 +46,12 @@ __global__ void swiglu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict
 
 // dx[:, :I] = dy * silu(gate); dx[:, I:] = dy * up * dsilu(gate); optionally re-emits y.
 __global__ void swiglu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, uint4* __restrict__ dx,
-                                  uint4* __restrict__ y, long long T, int Iv) {
+                                  uint4* __restrict__ y, long long T, int Iv, const int* __restrict__ tile_owner, int owners) {
   const long long total = T * Iv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / Iv;
+    if (tile_owner != nullptr && tile_owner[t >> 7] >= owners) continue;
     const int c = (int)(idx - t * Iv);
     const uint4 u = x[t * 2 * Iv + c];
     const uint4 g = x[t * 2 * Iv + Iv + c];
@@ -284,23 +289,24 @@ __global__ void adamw_kernel(float4* __restrict__ p, float4* __restrict__ m, flo
 
 }  // namespace
 
-void swiglu_fwd(const void* x, void* y, long long T, int I, cudaStream_t stream) {
+void swiglu_fwd(const void* x, void* y, long long T, int I, cudaStream_t stream, const int* tile_owner, int owners) {
   if (T == 0) return;
   if (I % 8) throw std::runtime_error("swiglu: intermediate size must be a multiple of 8");
   const int Iv = I / 8;
   swiglu_fwd_kernel<<<ew_grid(T * Iv, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(x),
-                                                             reinterpret_cast<uint4*>(y), T, Iv);
+                                                             reinterpret_cast<uint4*>(y), T, Iv, tile_owner, owners);
   count_launch();
   check_cuda(cudaGetLastError(), "swiglu_fwd launch");
 }
 
-void swiglu_bwd(const void* dy, const void* x, void* dx, void* y_recompute, long long T, int I, cudaStream_t stream) {
+void swiglu_bwd(const void* dy, const void* x, void* dx, void* y_recompute, long long T, int I, cudaStream_t stream,
+                const int* tile_owner, int owners) {
   if (T == 0) return;
   if (I % 8) throw std::runtime_error("swiglu: intermediate size must be a multiple of 8");
   const int Iv = I / 8;
   swiglu_bwd_kernel<<<ew_grid(T * Iv, 256), 256, 0, stream>>>(
       reinterpret_cast<const uint4*>(dy), reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(dx),
-      reinterpret_cast<uint4*>(y_recompute), T, Iv);
+      reinterpret_cast<uint4*>(y_recompute), T, Iv, tile_owner, owners);
   count_launch();
   check_cuda(cudaGetLastError(), "swiglu_bwd launch");
 }

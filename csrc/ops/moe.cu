@@ -30,10 +30,11 @@ struct PtrTable {
 
 // entry e (global numbering over ranks) -> (rank, token): rank = e / entries_per_rank, token = (e % entries_per_rank) / k
 __global__ void moe_gather_kernel(PtrTable src, PtrTable scale, const int* __restrict__ src_entry, uint4* __restrict__ out,
-                                  int rows, int Hv, int entries_per_rank, int k) {
+                                  int rows, int Hv, int entries_per_rank, int k, const int* __restrict__ tile_owner, int owners) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= rows) return;
+  if (tile_owner != nullptr && tile_owner[warp >> 7] >= owners) return;  // tile beyond the used rows: nothing reads it
   const int e = src_entry[warp];
   uint4* dst = out + (size_t)warp * Hv;
   if (e < 0) {
@@ -120,9 +121,11 @@ __global__ void moe_rowdot_kernel(const uint4* __restrict__ a, const uint4* __re
 }
 
 // rows[r] *= w[r] (bf16 rows, fp32 per-row factors)
-__global__ void scale_rows_kernel(uint4* __restrict__ x, const float* __restrict__ w, long long rows, int Hv) {
+__global__ void scale_rows_kernel(uint4* __restrict__ x, const float* __restrict__ w, long long rows, int Hv,
+                                  const int* __restrict__ tile_owner, int owners) {
   const long long total = rows * Hv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    if (tile_owner != nullptr && tile_owner[(idx / Hv) >> 7] >= owners) continue;
     const float f = w[idx / Hv];
     const uint4 v = x[idx];
     const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
@@ -145,7 +148,8 @@ PtrTable table_from(const std::vector<int64_t>& ptrs) {
 
 // src_ptrs / scale_ptrs: device addresses of the per-rank [T, H] bf16 buffers and [T * k] fp32 scales (0 = none).
 Tensor moe_gather(const std::vector<int64_t>& src_ptrs, const std::vector<int64_t>& scale_ptrs, const Tensor& src_entry,
-                  int64_t H, int64_t entries_per_rank, int64_t k, const Tensor& like) {
+                  int64_t H, int64_t entries_per_rank, int64_t k, const Tensor& like, const c10::optional<Tensor>& tile_owner,
+                  int64_t owners) {
   TORCH_CHECK(src_entry.is_cuda() && src_entry.scalar_type() == torch::kInt32 && src_entry.is_contiguous(), "src_entry: int32");
   TORCH_CHECK(H % 8 == 0, "hidden size must be a multiple of 8");
   const c10::cuda::CUDAGuard guard(src_entry.device());
@@ -157,7 +161,8 @@ Tensor moe_gather(const std::vector<int64_t>& src_ptrs, const std::vector<int64_
   const long long blocks = (rows * 32 + threads - 1) / threads;
   moe_gather_kernel<<<(unsigned)blocks, threads, 0, cur_stream()>>>(table_from(src_ptrs), scale, src_entry.data_ptr<int>(),
                                                                     reinterpret_cast<uint4*>(out.data_ptr()), (int)rows,
-                                                                    (int)(H / 8), (int)entries_per_rank, (int)k);
+                                                                    (int)(H / 8), (int)entries_per_rank, (int)k,
+                                                                    tile_owner.has_value() ? tile_owner->data_ptr<int>() : nullptr, (int)owners);
   count_launch();
   check_cuda(cudaGetLastError(), "moe_gather launch");
   return out;
@@ -208,7 +213,7 @@ Tensor moe_rowdot(const Tensor& a, const Tensor& b, const Tensor& dest_row) {
   return out;
 }
 
-void scale_rows_(Tensor& x, const Tensor& w) {
+void scale_rows_(Tensor& x, const Tensor& w, const c10::optional<Tensor>& tile_owner, int64_t owners) {
   TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.size(1) % 8 == 0, "bf16 rows");
   TORCH_CHECK(w.scalar_type() == torch::kFloat32 && w.numel() == x.size(0), "one fp32 factor per row");
   const c10::cuda::CUDAGuard guard(x.device());
@@ -218,13 +223,16 @@ void scale_rows_(Tensor& x, const Tensor& w) {
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   scale_rows_kernel<<<(unsigned)blocks, 256, 0, cur_stream()>>>(reinterpret_cast<uint4*>(x.data_ptr()), w.data_ptr<float>(),
-                                                                x.size(0), (int)(x.size(1) / 8));
+                                                                x.size(0), (int)(x.size(1) / 8),
+                                                                tile_owner.has_value() ? tile_owner->data_ptr<int>() : nullptr, (int)owners);
   count_launch();
   check_cuda(cudaGetLastError(), "scale_rows launch");
 }
 
 // out[rows, N] = a[rows, K] * op(W[tile expert]); w: [E, N, K] (w_mn = false) or [E, K, N] (w_mn = true)
-Tensor grouped_rows(const Tensor& a, const Tensor& w, const Tensor& tile_expert, bool w_mn, const c10::optional<Tensor>& status) {
+// `out` (optional): a contiguous [rows, N] bf16 buffer to write into (for instance a view of symmetric memory).
+Tensor grouped_rows(const Tensor& a, const Tensor& w, const Tensor& tile_expert, bool w_mn, const c10::optional<Tensor>& status,
+                    const c10::optional<Tensor>& out_buffer) {
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && a.is_contiguous() && w.is_contiguous(), "bf16 contiguous");
   TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.size(0) % 128 == 0, "a: [128 * tiles, K], w: 3-D");
   const int64_t K = a.size(1);
@@ -234,7 +242,14 @@ Tensor grouped_rows(const Tensor& a, const Tensor& w, const Tensor& tile_expert,
   const int64_t tiles = a.size(0) / 128;
   TORCH_CHECK(tile_expert.scalar_type() == torch::kInt32 && tile_expert.numel() >= tiles, "tile_expert: int32, one per tile");
   const c10::cuda::CUDAGuard guard(a.device());
-  Tensor out = torch::empty({a.size(0), N}, a.options());
+  Tensor out;
+  if (out_buffer.has_value()) {
+    out = *out_buffer;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == N,
+                "out: contiguous bf16 [rows, N]");
+  } else {
+    out = torch::empty({a.size(0), N}, a.options());
+  }
   grouped_rows_gemm(a.data_ptr(), K, w.data_ptr(), out.data_ptr(), N, tile_expert.data_ptr<int>(), (int)tiles, (int)w.size(0),
                     (int)N, (int)K, w_mn, status_of(status), cur_stream());
   return out;
@@ -255,11 +270,14 @@ void grouped_wgrad(const Tensor& dy, const Tensor& x, Tensor& dw, const Tensor& 
 }  // namespace
 
 void register_moe(pybind11::module_& m) {
-  m.def("moe_gather", &moe_gather);
+  m.def("moe_gather", &moe_gather, pybind11::arg("src_ptrs"), pybind11::arg("scale_ptrs"), pybind11::arg("src_entry"), pybind11::arg("H"),
+        pybind11::arg("entries_per_rank"), pybind11::arg("k"), pybind11::arg("like"), pybind11::arg("tile_owner") = pybind11::none(),
+        pybind11::arg("owners") = 0);
   m.def("moe_combine", &moe_combine);
   m.def("moe_rowdot", &moe_rowdot);
-  m.def("scale_rows_", &scale_rows_);
-  m.def("grouped_rows", &grouped_rows);
+  m.def("scale_rows_", &scale_rows_, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("tile_owner") = pybind11::none(), pybind11::arg("owners") = 0);
+  m.def("grouped_rows", &grouped_rows, pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("tile_expert"), pybind11::arg("w_mn"),
+        pybind11::arg("status"), pybind11::arg("out") = pybind11::none());
   m.def("grouped_wgrad", &grouped_wgrad);
 }
 

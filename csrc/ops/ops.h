@@ -24,8 +24,10 @@ void rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd
                  float* partial, float* dw, bool accumulate_dw, int T, int H, cudaStream_t stream);
 
 // ---- ops/elementwise.cu
-void swiglu_fwd(const void* x, void* y, long long T, int I, cudaStream_t stream);
-void swiglu_bwd(const void* dy, const void* x, void* dx, void* y_recompute, long long T, int I, cudaStream_t stream);
+// tile_owner / owners (optional): rows of 128-row tiles whose owner entry is >= owners are skipped.
+void swiglu_fwd(const void* x, void* y, long long T, int I, cudaStream_t stream, const int* tile_owner = nullptr, int owners = 0);
+void swiglu_bwd(const void* dy, const void* x, void* dx, void* y_recompute, long long T, int I, cudaStream_t stream,
+                const int* tile_owner = nullptr, int owners = 0);
 void rope_inplace(void* qkv, const float* cos_t, const float* sin_t, const int* position_ids, int T, long long row_stride,
                   int num_kv_groups, int q_per_group, int head_dim, int rope_dim, bool inverse, cudaStream_t stream);
 void embedding_fwd(const void* weight, const long long* ids, void* out, int T, int H, float scale, cudaStream_t stream);

@@ -95,10 +95,11 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         st = status_word(x.device)
         T, H = x.shape
         layout = build_grouped_layout(selected_experts.reshape(-1), num_experts)
-        xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * top_k, top_k, x)
+        te = layout.tile_expert  # tiles past the used rows carry num_experts and are skipped by every kernel below
+        xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * top_k, top_k, x, te, num_experts)
         fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
         del xg
-        act = C.swiglu_fwd(fc)
+        act = C.swiglu_fwd(fc, te, num_experts)
         y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
         del act
         weights32 = router_weights.reshape(-1).float().contiguous()
@@ -118,22 +119,22 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         entries = T * top_k
 
         # dY of the second GEMM without the routing weight, and the activation recomputed from the saved c_fc output
-        dyg = C.moe_gather([dout.data_ptr()], [], src_entry, H, entries, top_k, x)
+        dyg = C.moe_gather([dout.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
         dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)  # [rows, I] = dyg @ w_proj[e]
-        act = C.swiglu_fwd(fc)
+        act = C.swiglu_fwd(fc, tile_expert, num_experts)
         # d(router weight) = <dout[token], expert output row> = <dact_row, act_row>
         d_weights = C.moe_rowdot(dact, act, dest_row).view(w_shape).to(w_dtype)
         # per-row routing weight (0 for padding rows)
         row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
         row_weight[torch.where(dest_row >= 0, dest_row, torch.full_like(dest_row, rows)).long()] = weights32
         row_weight = row_weight[:rows].contiguous()
-        C.scale_rows_(act, row_weight)
+        C.scale_rows_(act, row_weight, tile_expert, num_experts)
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
         del dyg, act
-        C.scale_rows_(dact, row_weight)
-        dfc = C.swiglu_bwd(dact, fc, False)[0]
+        C.scale_rows_(dact, row_weight, tile_expert, num_experts)
+        dfc = C.swiglu_bwd(dact, fc, False, tile_expert, num_experts)[0]
         del dact
-        xg = C.moe_gather([x.data_ptr()], [], src_entry, H, entries, top_k, x)
+        xg = C.moe_gather([x.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
         g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
         del xg
         dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)  # [rows, H] = dfc @ w_fc[e]

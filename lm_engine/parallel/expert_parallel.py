@@ -164,14 +164,13 @@ class _ExpertParallelFn(torch.autograd.Function):
         peer.barrier()  # the previous users of the buffers are done everywhere
         tokens.tensor[: T * H].view(T, H).copy_(x)
         peer.barrier()  # every rank's tokens are readable
-        xg = C.moe_gather(tokens.ptrs, [], layout.src_entry, H, entries, top_k, x)  # dispatch: pull rows from their owners
+        te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
+        xg = C.moe_gather(tokens.ptrs, [], layout.src_entry, H, entries, top_k, x, te, local)  # dispatch: pull rows from their owners
         fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
         del xg
-        act = C.swiglu_fwd(fc)
-        y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
+        act = C.swiglu_fwd(fc, te, local)
+        C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
         del act
-        out_rows.tensor[: rows * H].view(rows, H).copy_(y)
-        del y
         global_row = _exchange_rows(layout.dest_row, entries, rows)
         peer.barrier()  # every rank's expert outputs are readable
         weights32 = router_weights.reshape(-1).float().contiguous()
@@ -198,9 +197,10 @@ class _ExpertParallelFn(torch.autograd.Function):
         peer.barrier()
         tokens.tensor[: T * H].view(T, H).copy_(dout)
         peer.barrier()
-        dyg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x)  # output gradients of the rows computed here
+        local = w_fc.shape[0]
+        dyg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x, tile_expert, local)  # output gradients of the rows computed here
         dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)
-        act = C.swiglu_fwd(fc)
+        act = C.swiglu_fwd(fc, tile_expert, local)
         # gradient of the routing weight of every entry served here, sent back to the token owners
         served = dest_row >= 0
         per_entry = C.moe_rowdot(dact, act, dest_row).reshape(-1).float()  # one value per global entry, 0 where not served here
@@ -209,22 +209,20 @@ class _ExpertParallelFn(torch.autograd.Function):
         row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
         row_weight[torch.where(served, dest_row, torch.full_like(dest_row, rows)).long()] = weights_all
         row_weight = row_weight[:rows].contiguous()
-        C.scale_rows_(act, row_weight)
+        C.scale_rows_(act, row_weight, tile_expert, local)
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
         del dyg, act
-        C.scale_rows_(dact, row_weight)
-        dfc = C.swiglu_bwd(dact, fc, False)[0]
+        C.scale_rows_(dact, row_weight, tile_expert, local)
+        dfc = C.swiglu_bwd(dact, fc, False, tile_expert, local)[0]
         del dact
 
         peer.barrier()  # all ranks have pulled the output gradients; the token buffer can take the activations again
         tokens.tensor[: T * H].view(T, H).copy_(x)
         peer.barrier()
-        xg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x)
+        xg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x, tile_expert, local)
         g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
         del xg
-        dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)
-        out_rows.tensor[: rows * H].view(rows, H).copy_(dxg)
-        del dxg
+        C.grouped_rows(dfc, w_fc, tile_expert, True, st, out_rows.tensor[: rows * H].view(rows, H))
         peer.barrier()
         dx = C.moe_combine(out_rows.ptrs, global_row, None, T, H, top_k, rows, x)
         return dx, g_fc, g_proj, d_weights, None, None, None
