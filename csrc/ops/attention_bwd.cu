@@ -3,7 +3,7 @@
 // One CTA owns 128 keys of one document and one key/value head. K and V stay resident in shared memory;
 // the CTA walks the query heads of the group and, for each, the query tiles that can see these keys:
 //   S^T  = K Q^T,  dP^T = V dO^T                      (tcgen05, fp32 in TMEM)
-//   P^T  = exp2(S^T * scale*log2e - lse*log2e),  dS^T = P^T o (dP^T - delta) * scale   (128 threads, row = key)
+//   P^T  = exp2(S^T * scale*log2e - lse*log2e),  dS^T = P^T o (dP^T - delta) * scale   (256 threads: row = key, two warps share a row and split its columns)
 //   dV  += P^T dO,  dK += dS^T Q,  dQ_tile = dS K       (tcgen05; dQ goes out through fp32 vector atomics)
 // The tiles of dS^T / Q / dO / K are each loaded or written once and reused through a second descriptor with
 // the other major-ness (e.g. dS^T is the K-major A operand of dK and the MN-major A operand of dQ).
@@ -18,7 +18,8 @@ namespace b200 {
 namespace {
 
 constexpr int BT = 128;  // tile edge for both queries and keys
-constexpr int BWD_THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;  // two warps per TMEM lane quarter, each taking half of the columns
+constexpr int BWD_THREADS = 64 + SOFTMAX_WARPS * 32;
 
 template <int D>
 struct BwdSmem {
@@ -30,7 +31,7 @@ struct BwdSmem {
   static constexpr int OFF_DO = OFF_Q + TILE_D;
   static constexpr int OFF_P = OFF_DO + TILE_D;
   static constexpr int OFF_DS = OFF_P + TILE_S;
-  static constexpr int OFF_ROW = OFF_DS + TILE_S;       // per softmax warp: lse[128], delta[128] floats
+  static constexpr int OFF_ROW = OFF_DS + TILE_S;       // per softmax warp: lse[64], delta[64] floats
   static constexpr int OFF_BAR = OFF_ROW + 8 * BT * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   uint8_t* sDO = smem + L::OFF_DO;
   uint8_t* sP = smem + L::OFF_P;
   uint8_t* sDS = smem + L::OFF_DS;
-  float* s_rows = reinterpret_cast<float*>(smem + L::OFF_ROW);  // [4 warps][lse 128 | delta 128]
+  float* s_rows = reinterpret_cast<float*>(smem + L::OFF_ROW);  // [8 warps][lse 64 | delta 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -60,13 +61,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int grp = blockIdx.y;  // key/value head
+  const int grp = blockIdx.x;  // key/value head (fastest grid index: the long key tiles of every head are scheduled first)
   const int k_col = (grp * (qpg + 2) + qpg) * D;
   const int v_col = k_col + D;
   const int hq_total = groups * qpg;
 
   if (threadIdx.x == 0) {
-    const int want = blockIdx.x;  // early key tiles see the most queries: hand them out first
+    const int want = blockIdx.y;  // early key tiles see the most queries: hand them out first
     int acc = 0, found = -1, start = 0, len = -1, kt = 0;
     for (int b = 0; b < num_docs; ++b) {
       const int s = cu_seqlens[b], e = cu_seqlens[b + 1];
@@ -87,9 +88,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     mbar_init(&bars[B_QDO_FULL], 1);
     mbar_init(&bars[B_QDO_EMPTY], 1);
     mbar_init(&bars[B_SDP_FULL], 1);
-    mbar_init(&bars[B_PDS_READY], 128);
+    mbar_init(&bars[B_PDS_READY], SOFTMAX_WARPS * 32);
     mbar_init(&bars[B_MMA2_DONE], 1);
-    mbar_init(&bars[B_DQ_DRAINED], 128);
+    mbar_init(&bars[B_DQ_DRAINED], SOFTMAX_WARPS * 32);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -210,7 +211,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- P / dS producers, dQ drain, final dK / dV
-    const int q4 = warp & 3;
+    const int q4 = warp & 3;            // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the columns (of S^T / dP^T, dQ, dK, dV) this warp takes
     const int r = q4 * 32 + lane;  // key row inside the tile (S^T, dV, dK) / query row inside the tile (dQ)
     const int kv_local = kv0 + r;
     const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
@@ -222,13 +224,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const int head = grp * qpg + qh;
       const int q0 = qt * BT;
       // Each warp stages the per-query statistics of this tile for itself (no cross-warp barrier needed).
-      float* w_lse = s_rows + q4 * (2 * BT);
-      float* w_delta = w_lse + BT;
+      float* w_lse = s_rows + (half * 4 + q4) * BT;
+      float* w_delta = w_lse + BT / 2;
       __syncwarp();
 #pragma unroll
-      for (int i = 0; i < BT / 32; ++i) {
-        const int col = i * 32 + lane;
-        const int ql = q0 + col;
+      for (int i = 0; i < BT / 64; ++i) {
+        const int col = i * 32 + lane;  // relative to this warp's first column
+        const int ql = q0 + half * (BT / 2) + col;
         const bool v = ql < doc_len;
         w_lse[col] = v ? lse[(long long)head * T + doc_start + ql] * 1.4426950408889634f : INFINITY;
         w_delta[col] = v ? delta[(long long)head * T + doc_start + ql] : 0.f;
@@ -238,7 +240,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tc_fence_after_sync();
       const bool needs_mask = causal && (q0 < kv0 + BT - 1);  // only the diagonal tile
 #pragma unroll 1
-      for (int c = 0; c < BT / 32; ++c) {
+      for (int cc = 0; cc < BT / 64; ++cc) {
+        const int c = half * (BT / 64) + cc;
         uint32_t sv[32], dpv[32];
         B200_TMEM_LD_32(sv, tmem_S + lane_addr + c * 32);
         B200_TMEM_LD_32(dpv, tmem_dP + lane_addr + c * 32);
@@ -250,10 +253,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int col = c * 32 + e + u;  // query column inside the tile
-            float p = exp2f(__uint_as_float(sv[e + u]) * scale_log2 - w_lse[col]);
+            float p = exp2f(__uint_as_float(sv[e + u]) * scale_log2 - w_lse[cc * 32 + e + u]);
             if (!kv_valid || (needs_mask && kv_local > q0 + col)) p = 0.f;
             pv[u] = p;
-            dv[u] = p * (__uint_as_float(dpv[e + u]) - w_delta[col]) * scale;
+            dv[u] = p * (__uint_as_float(dpv[e + u]) - w_delta[cc * 32 + e + u]) * scale;
           }
           pp[e / 2] = pack_bf16x2(pv[0], pv[1]);
           dd[e / 2] = pack_bf16x2(dv[0], dv[1]);
@@ -280,7 +283,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int ql = q0 + r;
         float* dst = dq_accum + (long long)(doc_start + ql) * ((long long)hq_total * D) + (long long)head * D;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;
           uint32_t o[32];
           B200_TMEM_LD_32(o, tmem_S + lane_addr + c * 32);
           tmem_ld_wait();
@@ -305,7 +309,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       __nv_bfloat16* krow = dqkv + (long long)(doc_start + kv_local) * dqkv_stride + k_col;
       __nv_bfloat16* vrow = krow + D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;
         uint32_t a[32], b[32];
         B200_TMEM_LD_32(a, tmem_dK + lane_addr + c * 32);
         B200_TMEM_LD_32(b, tmem_dV + lane_addr + c * 32);
@@ -384,7 +389,7 @@ void launch_bwd(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do, const float
     configured = true;
   }
   const int tiles_upper = (T + BT - 1) / BT + num_docs;
-  dim3 grid(tiles_upper, groups);
+  dim3 grid(groups, tiles_upper);
   kernel<<<grid, BWD_THREADS, BwdSmem<D>::TOTAL, stream>>>(tm_qkv, tm_do, lse, delta, dq_accum,
                                                            reinterpret_cast<__nv_bfloat16*>(dqkv), dqkv_stride, cu_seqlens,
                                                            num_docs, T, groups, qpg, scale, scale * 1.4426950408889634f,

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y;  // query head
+  const int head = blockIdx.x;  // query head (fastest grid index: the long tiles of every head are scheduled first)
   const int grp = head / qpg;
   const int q_col = (grp * (qpg + 2) + (head - grp * qpg)) * D;
   const int k_col = (grp * (qpg + 2) + qpg) * D;
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   if (threadIdx.x == 0) {
     // Map this CTA to (document, query tile); heavy (late) tiles of each document are handed out first.
-    const int want = gridDim.x - 1 - blockIdx.x;
+    const int want = gridDim.y - 1 - blockIdx.y;
     int acc = 0, found = -1, start = 0, len = -1, qt = 0;
     for (int b = 0; b < num_docs; ++b) {
       const int s = cu_seqlens[b], e = cu_seqlens[b + 1];
@@ -331,7 +331,7 @@ void launch_fwd(const CUtensorMap& tm, void* out, float* lse, const int* cu_seql
     configured = true;
   }
   const int tiles_upper = (T + BLOCK_M - 1) / BLOCK_M + num_docs;
-  dim3 grid(tiles_upper, groups * qpg);
+  dim3 grid(groups * qpg, tiles_upper);
   kernel<<<grid, FWD_THREADS, FwdSmem<D>::TOTAL, stream>>>(tm, reinterpret_cast<__nv_bfloat16*>(out), lse, cu_seqlens,
                                                            num_docs, T, groups, qpg, out_stride,
                                                            scale * 1.4426950408889634f, causal ? 1 : 0, status);

@@ -134,6 +134,48 @@ __global__ void scale_rows_kernel(uint4* __restrict__ x, const float* __restrict
   }
 }
 
+// Backward of the weighted expert activation, one warp per expert row r with routing weight w = row_weight[r]:
+//   act_w[r] = w * up * silu(gate)                      (the operand of the second GEMM's weight gradient)
+//   dfc[r]   = [w * dact * silu(gate) | w * dact * up * dsilu(gate)]
+//   dot[r]   = <dact[r], up * silu(gate)>               (gradient of the routing weight)
+// from fc[r] = [up | gate] and dact[r], each read once. Rows of unused tiles are skipped.
+__global__ void moe_swiglu_bwd_kernel(const uint4* __restrict__ fc, const uint4* __restrict__ dact, const float* __restrict__ row_weight,
+                                      uint4* __restrict__ act_w, uint4* __restrict__ dfc, float* __restrict__ dot, long long rows,
+                                      int Iv, const int* __restrict__ tile_owner, int owners) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  if (tile_owner != nullptr && tile_owner[row >> 7] >= owners) return;
+  const float w = row_weight[row];
+  const uint4* up = fc + row * 2 * Iv;
+  const uint4* gate = up + Iv;
+  const uint4* dy = dact + row * Iv;
+  float s = 0.f;
+  for (int i = lane; i < Iv; i += 32) {
+    const uint4 u = up[i], g = gate[i], d = dy[i];
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w}, gg[4] = {g.x, g.y, g.z, g.w}, dd[4] = {d.x, d.y, d.z, d.w};
+    uint32_t du[4], dg[4], yy[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = unpack_bf16x2(uu[e]), b = unpack_bf16x2(gg[e]), q = unpack_bf16x2(dd[e]);
+      const float s0 = 1.f / (1.f + __expf(-b.x)), s1 = 1.f / (1.f + __expf(-b.y));
+      const float silu0 = b.x * s0, silu1 = b.y * s1;
+      const float ds0 = s0 * (1.f + b.x * (1.f - s0)), ds1 = s1 * (1.f + b.y * (1.f - s1));
+      const float y0 = a.x * silu0, y1 = a.y * silu1;
+      s += q.x * y0 + q.y * y1;
+      const float q0 = q.x * w, q1 = q.y * w;
+      du[e] = pack_bf16x2(q0 * silu0, q1 * silu1);
+      dg[e] = pack_bf16x2(q0 * a.x * ds0, q1 * a.y * ds1);
+      yy[e] = pack_bf16x2(y0 * w, y1 * w);
+    }
+    act_w[row * Iv + i] = make_uint4(yy[0], yy[1], yy[2], yy[3]);
+    dfc[row * 2 * Iv + i] = make_uint4(du[0], du[1], du[2], du[3]);
+    dfc[row * 2 * Iv + Iv + i] = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+  }
+  s = warp_sum(s);
+  if (lane == 0) dot[row] = s;
+}
+
 using torch::Tensor;
 
 inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
@@ -229,6 +271,32 @@ void scale_rows_(Tensor& x, const Tensor& w, const c10::optional<Tensor>& tile_o
   check_cuda(cudaGetLastError(), "scale_rows launch");
 }
 
+// (act_w [rows, I], dfc [rows, 2I], dot [rows] fp32) from fc [rows, 2I], dact [rows, I], row_weight [rows] fp32.
+// Rows of skipped tiles are left unwritten in act_w / dfc; dot is zero there.
+std::vector<Tensor> moe_swiglu_bwd(const Tensor& fc, const Tensor& dact, const Tensor& row_weight,
+                                   const c10::optional<Tensor>& tile_owner, int64_t owners) {
+  TORCH_CHECK(fc.scalar_type() == torch::kBFloat16 && dact.scalar_type() == torch::kBFloat16 && fc.is_contiguous() && dact.is_contiguous(), "bf16 rows");
+  TORCH_CHECK(fc.dim() == 2 && dact.dim() == 2 && fc.size(0) == dact.size(0) && fc.size(1) == 2 * dact.size(1) && dact.size(1) % 8 == 0, "fc: [rows, 2I], dact: [rows, I]");
+  TORCH_CHECK(row_weight.scalar_type() == torch::kFloat32 && row_weight.numel() == fc.size(0) && row_weight.is_contiguous(), "one fp32 weight per row");
+  const int64_t rows = fc.size(0);
+  if (tile_owner.has_value())
+    TORCH_CHECK(tile_owner->scalar_type() == torch::kInt32 && tile_owner->numel() * 128 >= rows, "tile_owner: int32, one per 128 rows");
+  const c10::cuda::CUDAGuard guard(fc.device());
+  Tensor act_w = torch::empty_like(dact);
+  Tensor dfc = torch::empty_like(fc);
+  Tensor dot = torch::zeros({rows}, fc.options().dtype(torch::kFloat32));
+  if (rows == 0) return {act_w, dfc, dot};
+  const int threads = 256;
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  moe_swiglu_bwd_kernel<<<(unsigned)blocks, threads, 0, cur_stream()>>>(
+      reinterpret_cast<const uint4*>(fc.data_ptr()), reinterpret_cast<const uint4*>(dact.data_ptr()), row_weight.data_ptr<float>(),
+      reinterpret_cast<uint4*>(act_w.data_ptr()), reinterpret_cast<uint4*>(dfc.data_ptr()), dot.data_ptr<float>(), rows,
+      (int)(dact.size(1) / 8), tile_owner.has_value() ? tile_owner->data_ptr<int>() : nullptr, (int)owners);
+  count_launch();
+  check_cuda(cudaGetLastError(), "moe_swiglu_bwd launch");
+  return {act_w, dfc, dot};
+}
+
 // out[rows, N] = a[rows, K] * op(W[tile expert]); w: [E, N, K] (w_mn = false) or [E, K, N] (w_mn = true)
 // `out` (optional): a contiguous [rows, N] bf16 buffer to write into (for instance a view of symmetric memory).
 Tensor grouped_rows(const Tensor& a, const Tensor& w, const Tensor& tile_expert, bool w_mn, const c10::optional<Tensor>& status,
@@ -276,6 +344,8 @@ void register_moe(pybind11::module_& m) {
   m.def("moe_combine", &moe_combine);
   m.def("moe_rowdot", &moe_rowdot);
   m.def("scale_rows_", &scale_rows_, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("tile_owner") = pybind11::none(), pybind11::arg("owners") = 0);
+  m.def("moe_swiglu_bwd", &moe_swiglu_bwd, pybind11::arg("fc"), pybind11::arg("dact"), pybind11::arg("row_weight"),
+        pybind11::arg("tile_owner") = pybind11::none(), pybind11::arg("owners") = 0);
   m.def("grouped_rows", &grouped_rows, pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("tile_expert"), pybind11::arg("w_mn"),
         pybind11::arg("status"), pybind11::arg("out") = pybind11::none());
   m.def("grouped_wgrad", &grouped_wgrad);

@@ -88,6 +88,19 @@ def _wgrad(C, dy, x, weight, padded_offsets, st):
     return dw.to(weight.dtype)
 
 
+def weighted_swiglu_backward(C, fc, dact, dest_row, entry_weights, rows: int, tile_expert, owners: int):
+    """One pass over the expert rows: the routing-weighted activation ``w * swiglu(fc)`` (operand of the second
+    weight gradient), ``dfc`` (gradient of the first GEMM's output, routing weight folded in) and, per routed entry,
+    ``<dact_row, swiglu(fc)_row>`` = the gradient of its routing weight (0 for entries without a row here)."""
+    served = dest_row >= 0
+    safe = torch.where(served, dest_row, torch.full_like(dest_row, rows)).long()
+    row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=fc.device)
+    row_weight[safe] = entry_weights
+    act_w, dfc, dot = C.moe_swiglu_bwd(fc, dact, row_weight[:rows], tile_expert, owners)
+    per_entry = torch.cat([dot, dot.new_zeros(1)])[safe]
+    return act_w, dfc, per_entry
+
+
 class _ScatteredExpertsFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, num_experts, top_k):
@@ -121,19 +134,11 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         # dY of the second GEMM without the routing weight, and the activation recomputed from the saved c_fc output
         dyg = C.moe_gather([dout.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
         dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)  # [rows, I] = dyg @ w_proj[e]
-        act = C.swiglu_fwd(fc, tile_expert, num_experts)
-        # d(router weight) = <dout[token], expert output row> = <dact_row, act_row>
-        d_weights = C.moe_rowdot(dact, act, dest_row).view(w_shape).to(w_dtype)
-        # per-row routing weight (0 for padding rows)
-        row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
-        row_weight[torch.where(dest_row >= 0, dest_row, torch.full_like(dest_row, rows)).long()] = weights32
-        row_weight = row_weight[:rows].contiguous()
-        C.scale_rows_(act, row_weight, tile_expert, num_experts)
+        act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights32, rows, tile_expert, num_experts)
+        del dact
+        d_weights = per_entry.view(w_shape).to(w_dtype)
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
         del dyg, act
-        C.scale_rows_(dact, row_weight, tile_expert, num_experts)
-        dfc = C.swiglu_bwd(dact, fc, False, tile_expert, num_experts)[0]
-        del dact
         xg = C.moe_gather([x.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
         g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
         del xg

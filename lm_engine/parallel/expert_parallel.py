@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
-from ..ops.moe import TILE, _wgrad, build_grouped_layout
+from ..ops.moe import TILE, _wgrad, build_grouped_layout, weighted_swiglu_backward
 from ..utils import ProcessGroupManager
 from .symmetric import PeerBuffer, PeerGroup, get_peer_group
 
@@ -200,21 +200,12 @@ class _ExpertParallelFn(torch.autograd.Function):
         local = w_fc.shape[0]
         dyg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x, tile_expert, local)  # output gradients of the rows computed here
         dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)
-        act = C.swiglu_fwd(fc, tile_expert, local)
-        # gradient of the routing weight of every entry served here, sent back to the token owners
-        served = dest_row >= 0
-        per_entry = C.moe_rowdot(dact, act, dest_row).reshape(-1).float()  # one value per global entry, 0 where not served here
+        # gradient of the routing weight of every entry served here (0 elsewhere), sent back to the token owners
+        act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights_all, rows, tile_expert, local)
+        del dact
         d_weights = _exchange_values(per_entry, entries).view(w_shape).to(w_dtype)
-
-        row_weight = torch.zeros(rows + 1, dtype=torch.float32, device=x.device)
-        row_weight[torch.where(served, dest_row, torch.full_like(dest_row, rows)).long()] = weights_all
-        row_weight = row_weight[:rows].contiguous()
-        C.scale_rows_(act, row_weight, tile_expert, local)
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
         del dyg, act
-        C.scale_rows_(dact, row_weight, tile_expert, local)
-        dfc = C.swiglu_bwd(dact, fc, False, tile_expert, local)[0]
-        del dact
 
         peer.barrier()  # all ranks have pulled the output gradients; the token buffer can take the activations again
         tokens.tensor[: T * H].view(T, H).copy_(x)
