@@ -134,6 +134,31 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* desc, const void
                : "memory");
 }
 
+// Element-wise add of a shared-memory tile into global memory (element type taken from the tensor map).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* desc, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+
+// Barrier `id` (1..15) over `nthreads` threads of the CTA that also returns the OR of `pred` over them: every
+// participant learns whether any of them gave up a bounded wait, so that all of them leave a loop together.
+__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 p, %3, 0;\n"
+      "bar.red.or.pred q, %1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int N>

@@ -67,6 +67,23 @@ inline CUtensorMap make_tensor_map_2d_u8(const void* base, uint64_t inner, uint6
   return m;
 }
 
+// 2-D tensor map over a row-major fp32 matrix (sizes and stride in elements; box_inner * 4 bytes <= 128 when swizzled).
+inline CUtensorMap make_tensor_map_2d_f32(const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride, uint32_t box_inner,
+                                          uint32_t box_outer, bool swizzle128 = true) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) throw std::runtime_error("TMA base must be 16-byte aligned");
+  if ((row_stride * 4) % 16 != 0) throw std::runtime_error("TMA row stride must be a multiple of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride * 4};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (f32) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
 // 3-D variant: [outer2][outer][inner] with explicit strides (elements) for the two outer dims.
 inline CUtensorMap make_tensor_map_3d_b16(const void* base, uint64_t inner, uint64_t outer, uint64_t outer2,
                                           uint64_t stride_outer, uint64_t stride_outer2, uint32_t box_inner,

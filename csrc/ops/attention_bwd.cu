@@ -4,7 +4,7 @@
 // the CTA walks the query heads of the group and, for each, the query tiles that can see these keys:
 //   S^T  = K Q^T,  dP^T = V dO^T                      (tcgen05, fp32 in TMEM)
 //   P^T  = exp2(S^T * scale*log2e - lse*log2e),  dS^T = P^T o (dP^T - delta) * scale   (256 threads: row = key, two warps share a row and split its columns)
-//   dV  += P^T dO,  dK += dS^T Q,  dQ_tile = dS K       (tcgen05; dQ goes out through fp32 vector atomics)
+//   dV  += P^T dO,  dK += dS^T Q,  dQ_tile = dS K       (tcgen05; dQ is added to an fp32 buffer by bulk tensor reductions)
 // The tiles of dS^T / Q / dO / K are each loaded or written once and reused through a second descriptor with
 // the other major-ness (e.g. dS^T is the K-major A operand of dK and the MN-major A operand of dQ).
 // Two small kernels bracket it: delta = rowsum(dO o O) before, fp32 dQ -> bf16 into the fused gradient after.
@@ -41,7 +41,7 @@ enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 2, B_SDP_FULL = 3, B_PDS_READY = 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                    const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dq_accum,
+                    const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse, const float* __restrict__ delta,
                     __nv_bfloat16* __restrict__ dqkv, long long dqkv_stride, const int* __restrict__ cu_seqlens,
                     int num_docs, int T, int groups, int qpg, float scale, float scale_log2, int causal, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -64,7 +64,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const int grp = blockIdx.x;  // key/value head (fastest grid index: the long key tiles of every head are scheduled first)
   const int k_col = (grp * (qpg + 2) + qpg) * D;
   const int v_col = k_col + D;
-  const int hq_total = groups * qpg;
 
   if (threadIdx.x == 0) {
     const int want = blockIdx.y;  // early key tiles see the most queries: hand them out first
@@ -213,6 +212,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     // ---------------------------------------------------------------- P / dS producers, dQ drain, final dK / dV
     const int q4 = warp & 3;            // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;   // which half of the columns (of S^T / dP^T, dQ, dK, dV) this warp takes
+    const bool is_issuer = warp == 2 && lane == 0;  // issues the bulk reductions of dQ
     const int r = q4 * 32 + lane;  // key row inside the tile (S^T, dV, dK) / query row inside the tile (dQ)
     const int kv_local = kv0 + r;
     const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
@@ -236,7 +236,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         w_delta[col] = v ? delta[(long long)head * T + doc_start + ql] : 0.f;
       }
       __syncwarp();
-      if (!mbar_wait(&bars[B_SDP_FULL], it & 1, abort_flag)) { ok = false; break; }
+      bool got = mbar_wait(&bars[B_SDP_FULL], it & 1, abort_flag);
+      // the P / dS tiles double as the staging buffer of the previous dQ tile: its bulk reduction must have read them
+      if (is_issuer) tma_store_wait_read<0>();
+      if (named_barrier_or(1, SOFTMAX_WARPS * 32, !got)) { ok = false; break; }
       tc_fence_after_sync();
       const bool needs_mask = causal && (q0 < kv0 + BT - 1);  // only the diagonal tile
 #pragma unroll 1
@@ -276,31 +279,36 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tc_fence_before_sync();
       mbar_arrive(&bars[B_PDS_READY]);
 
-      if (!mbar_wait(&bars[B_MMA2_DONE], it & 1, abort_flag)) { ok = false; break; }
+      got = mbar_wait(&bars[B_MMA2_DONE], it & 1, abort_flag);
       tc_fence_after_sync();
-      {
-        // dQ rows of this query tile: lane r <-> query row r
-        const int ql = q0 + r;
-        float* dst = dq_accum + (long long)(doc_start + ql) * ((long long)hq_total * D) + (long long)head * D;
+      if (got) {
+        // dQ tile -> fp32 staging in shared memory (one 128-byte-swizzled [128 x 32] box per 32 columns, over the P / dS
+        // tiles the MMAs have finished with), then one bulk add per box into the fp32 accumulator: full lines at L2
+        // instead of scattered 16-byte atomics. Query rows past the document are exact zeros (their P is 0).
 #pragma unroll
         for (int cc = 0; cc < D / 64; ++cc) {
           const int c = half * (D / 64) + cc;
           uint32_t o[32];
           B200_TMEM_LD_32(o, tmem_S + lane_addr + c * 32);
           tmem_ld_wait();
-          if (ql < doc_len) {
+          uint8_t* row = sP + c * (BT * 128) + r * 128;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              atomicAdd(reinterpret_cast<float4*>(dst + c * 32) + e,
-                        make_float4(__uint_as_float(o[4 * e]), __uint_as_float(o[4 * e + 1]), __uint_as_float(o[4 * e + 2]),
-                                    __uint_as_float(o[4 * e + 3])));
-            }
-          }
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) = make_uint4(o[4 * ch], o[4 * ch + 1], o[4 * ch + 2], o[4 * ch + 3]);
         }
+        tc_fence_before_sync();
+        mbar_arrive(&bars[B_DQ_DRAINED]);  // the S / dQ columns of TMEM can take the next tile
+        fence_proxy_async_smem();
       }
-      tc_fence_before_sync();
-      mbar_arrive(&bars[B_DQ_DRAINED]);
+      if (named_barrier_or(2, SOFTMAX_WARPS * 32, !got)) { ok = false; break; }
+      if (is_issuer) {
+        const int row0 = doc_start + q0;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tma_reduce_add_2d(&tm_dq, sP + c * (BT * 128), head * D + c * 32, row0);
+        tma_store_commit();
+      }
     }
+    if (is_issuer) tma_store_wait<0>();
     if (!ok) {
       raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
     } else {
@@ -379,7 +387,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_accum, __nv_
 }
 
 template <int D>
-void launch_bwd(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do, const float* lse, const float* delta, float* dq_accum,
+void launch_bwd(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do, const CUtensorMap& tm_dq, const float* lse, const float* delta,
                 void* dqkv, long long dqkv_stride, const int* cu_seqlens, int num_docs, int T, int groups, int qpg,
                 float scale, bool causal, int* status, cudaStream_t stream) {
   auto kernel = attn_bwd_kernel<D>;
@@ -390,7 +398,7 @@ void launch_bwd(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do, const float
   }
   const int tiles_upper = (T + BT - 1) / BT + num_docs;
   dim3 grid(groups, tiles_upper);
-  kernel<<<grid, BWD_THREADS, BwdSmem<D>::TOTAL, stream>>>(tm_qkv, tm_do, lse, delta, dq_accum,
+  kernel<<<grid, BWD_THREADS, BwdSmem<D>::TOTAL, stream>>>(tm_qkv, tm_do, tm_dq, lse, delta,
                                                            reinterpret_cast<__nv_bfloat16*>(dqkv), dqkv_stride, cu_seqlens,
                                                            num_docs, T, groups, qpg, scale, scale * 1.4426950408889634f,
                                                            causal ? 1 : 0, status);
@@ -417,8 +425,9 @@ void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, co
   check_cuda(cudaMemsetAsync(dq_accum, 0, (size_t)T * hq * head_dim * sizeof(float), stream), "dq_accum memset");
   const CUtensorMap tm_qkv = make_tensor_map_2d_b16(qkv, width, T, qkv_stride, 64, BT);
   const CUtensorMap tm_do = make_tensor_map_2d_b16(dout, (long long)hq * head_dim, T, out_stride, 64, BT);
-  if (head_dim == 128) launch_bwd<128>(tm_qkv, tm_do, lse, delta, dq_accum, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
-  else if (head_dim == 64) launch_bwd<64>(tm_qkv, tm_do, lse, delta, dq_accum, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
+  const CUtensorMap tm_dq = make_tensor_map_2d_f32(dq_accum, (long long)hq * head_dim, T, (long long)hq * head_dim, 32, BT);
+  if (head_dim == 128) launch_bwd<128>(tm_qkv, tm_do, tm_dq, lse, delta, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
+  else if (head_dim == 64) launch_bwd<64>(tm_qkv, tm_do, tm_dq, lse, delta, dqkv, dqkv_stride, cu_seqlens, num_docs, T, groups, qpg, scale, causal, status, stream);
   else throw std::runtime_error("attn_varlen_bwd: head_dim must be 64 or 128");
   {
     const long long total = (long long)T * hq * head_dim / 4;
