@@ -103,6 +103,13 @@ __device__ __forceinline__ void raise_status(int* status, int code, volatile int
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// 2^x on the special-function unit: one instruction, no range fix-ups (denormal results flush to zero).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ----------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies). Loads complete on an mbarrier of this CTA.
 // ----------------------------------------------------------------------------

@@ -36,7 +36,7 @@ struct BwdSmem {
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 2, B_SDP_FULL = 3, B_PDS_READY = 4, B_MMA2_DONE = 5, B_DQ_DRAINED = 6, B_COUNT = 7 };
+enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 2, B_SDP_FULL = 3, B_PDS_READY = 4, B_MMA2_DONE = 5, B_DQ_DRAINED = 6, B_PDS_FIRST = 7, B_COUNT = 8 };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     mbar_init(&bars[B_QDO_EMPTY], 1);
     mbar_init(&bars[B_SDP_FULL], 1);
     mbar_init(&bars[B_PDS_READY], SOFTMAX_WARPS * 32);
+    mbar_init(&bars[B_PDS_FIRST], SOFTMAX_WARPS * 32);
     mbar_init(&bars[B_MMA2_DONE], 1);
     mbar_init(&bars[B_DQ_DRAINED], SOFTMAX_WARPS * 32);
     *abort_flag = 0;
@@ -179,30 +180,38 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         umma_commit(&bars[B_SDP_FULL]);
 
-        if (!mbar_wait(&bars[B_PDS_READY], ph, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
+        // Every softmax warp produces its first 32 query columns, then its second 32: the dV / dK steps over the first
+        // columns (queries 0..31 and 64..95) run while the second ones are still being computed.
         const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;  // K-major A: 16 query columns per step
-          const uint32_t b_off = k * 16 * 128;                          // MN-major B: 16 query rows per step
-          umma_f16_ss(tmem_dV, umma_smem_desc_sw128(p_base + a_off, 16, 1024),
-                      umma_smem_desc_sw128(do_base + b_off, BT * 128, 1024), idesc_kv, (acc | (k != 0)) ? 1u : 0u);
-        }
+        for (int part = 0; part < 2; ++part) {
+          if (!mbar_wait(&bars[part == 0 ? B_PDS_FIRST : B_PDS_READY], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;
-          const uint32_t b_off = k * 16 * 128;
-          umma_f16_ss(tmem_dK, umma_smem_desc_sw128(ds_base + a_off, 16, 1024),
-                      umma_smem_desc_sw128(q_base + b_off, BT * 128, 1024), idesc_kv, (acc | (k != 0)) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {
+            const int k = (kk >> 1) * 4 + part * 2 + (kk & 1);
+            const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;  // K-major A: 16 query columns per step
+            const uint32_t b_off = k * 16 * 128;                          // MN-major B: 16 query rows per step
+            umma_f16_ss(tmem_dV, umma_smem_desc_sw128(p_base + a_off, 16, 1024),
+                        umma_smem_desc_sw128(do_base + b_off, BT * 128, 1024), idesc_kv, (acc | (part | kk) != 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const int k = (kk >> 1) * 4 + part * 2 + (kk & 1);
+            const uint32_t a_off = (k / 4) * (BT * 128) + (k % 4) * 32;
+            const uint32_t b_off = k * 16 * 128;
+            umma_f16_ss(tmem_dK, umma_smem_desc_sw128(ds_base + a_off, 16, 1024),
+                        umma_smem_desc_sw128(q_base + b_off, BT * 128, 1024), idesc_kv, (acc | (part | kk) != 0) ? 1u : 0u);
+          }
         }
+        if (!ok) break;
+        umma_commit(&bars[B_QDO_EMPTY]);  // Q and dO are free once dV and dK have retired: the next tiles load under dQ
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t off = k * 16 * 128;  // 16 key rows per step for both operands
           umma_f16_ss(tmem_S, umma_smem_desc_sw128(ds_base + off, BT * 128, 1024),
                       umma_smem_desc_sw128(k_base + off, BT * 128, 1024), idesc_dq, k != 0 ? 1u : 0u);
         }
-        umma_commit(&bars[B_QDO_EMPTY]);
         umma_commit(&bars[B_MMA2_DONE]);
       }
       if (!ok) raise_status(status, kStatusWaitTimeoutMma, abort_flag);
@@ -232,16 +241,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int col = i * 32 + lane;  // relative to this warp's first column
         const int ql = q0 + half * (BT / 2) + col;
         const bool v = ql < doc_len;
-        w_lse[col] = v ? lse[(long long)head * T + doc_start + ql] * 1.4426950408889634f : INFINITY;
-        w_delta[col] = v ? delta[(long long)head * T + doc_start + ql] : 0.f;
+        // stored negated (and delta pre-multiplied by the softmax scale) so that each element below is one fused multiply-add
+        w_lse[col] = v ? lse[(long long)head * T + doc_start + ql] * -1.4426950408889634f : -INFINITY;
+        w_delta[col] = v ? delta[(long long)head * T + doc_start + ql] * -scale : 0.f;
       }
       __syncwarp();
       bool got = mbar_wait(&bars[B_SDP_FULL], it & 1, abort_flag);
-      // the P / dS tiles double as the staging buffer of the previous dQ tile: its bulk reduction must have read them
-      if (is_issuer) tma_store_wait_read<0>();
-      if (named_barrier_or(1, SOFTMAX_WARPS * 32, !got)) { ok = false; break; }
       tc_fence_after_sync();
-      const bool needs_mask = causal && (q0 < kv0 + BT - 1);  // only the diagonal tile
+      // Only the diagonal tile and the last key tile of a document mask anything: every other tile takes the short path.
+      const bool masked = !kv_valid || (causal && (q0 < kv0 + BT - 1));
+      const int first_visible = kv_valid ? (causal ? kv_local - q0 : 0) : BT;  // query columns below this see nothing of this key
+      const float2 scale_log2_2 = make_float2(scale_log2, scale_log2), scale_2 = make_float2(scale, scale);
 #pragma unroll 1
       for (int cc = 0; cc < BT / 64; ++cc) {
         const int c = half * (BT / 64) + cc;
@@ -250,19 +260,35 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         B200_TMEM_LD_32(dpv, tmem_dP + lane_addr + c * 32);
         tmem_ld_wait();
         uint32_t pp[16], dd[16];
+        const float4* nl4 = reinterpret_cast<const float4*>(w_lse + cc * 32);
+        const float4* nd4 = reinterpret_cast<const float4*>(w_delta + cc * 32);
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;  // query column inside the tile
-            float p = exp2f(__uint_as_float(sv[e + u]) * scale_log2 - w_lse[cc * 32 + e + u]);
-            if (!kv_valid || (needs_mask && kv_local > q0 + col)) p = 0.f;
-            pv[u] = p;
-            dv[u] = p * (__uint_as_float(dpv[e + u]) - w_delta[cc * 32 + e + u]) * scale;
+        for (int e = 0; e < 32; e += 4) {
+          const float4 nl = nl4[e / 4], nd = nd4[e / 4];
+          // packed fp32 pairs: t = s * scale*log2e - lse*log2e, g = dP * scale - delta * scale
+          const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), scale_log2_2, make_float2(nl.x, nl.y));
+          const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3])), scale_log2_2, make_float2(nl.z, nl.w));
+          const float2 g0 = __ffma2_rn(make_float2(__uint_as_float(dpv[e]), __uint_as_float(dpv[e + 1])), scale_2, make_float2(nd.x, nd.y));
+          const float2 g1 = __ffma2_rn(make_float2(__uint_as_float(dpv[e + 2]), __uint_as_float(dpv[e + 3])), scale_2, make_float2(nd.z, nd.w));
+          float2 p0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+          float2 p1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+          if (masked) {
+            const int col = c * 32 + e;  // query column inside the tile
+            if (col < first_visible) p0.x = 0.f;
+            if (col + 1 < first_visible) p0.y = 0.f;
+            if (col + 2 < first_visible) p1.x = 0.f;
+            if (col + 3 < first_visible) p1.y = 0.f;
           }
-          pp[e / 2] = pack_bf16x2(pv[0], pv[1]);
-          dd[e / 2] = pack_bf16x2(dv[0], dv[1]);
+          const float2 d0 = __fmul2_rn(p0, g0), d1 = __fmul2_rn(p1, g1);
+          pp[e / 2] = pack_bf16x2(p0.x, p0.y);
+          pp[e / 2 + 1] = pack_bf16x2(p1.x, p1.y);
+          dd[e / 2] = pack_bf16x2(d0.x, d0.y);
+          dd[e / 2 + 1] = pack_bf16x2(d1.x, d1.y);
+        }
+        if (cc == 0) {
+          // the P / dS tiles double as the staging buffer of the previous dQ tile: its bulk reduction must have read them
+          if (is_issuer) tma_store_wait_read<0>();
+          if (named_barrier_or(1, SOFTMAX_WARPS * 32, !got)) { ok = false; break; }
         }
         // 32 columns = half of a 64-column K block: four 16-byte chunks of this thread's row
         const int kb = c >> 1;
@@ -274,7 +300,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
           *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
         }
+        if (cc == 0) {
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          mbar_arrive(&bars[B_PDS_FIRST]);
+        }
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars[B_PDS_READY]);
