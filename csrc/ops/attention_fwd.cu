@@ -5,9 +5,9 @@
 // through one strided TMA tensor map; nothing is split or copied beforehand.
 //
 // One CTA owns 128 consecutive query rows of one document and one query head:
-//   warp 0      TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 0      TMA producer: Q once, then K tiles and V tiles of 128 keys through two separate 2-stage rings
 //   warp 1      MMA issuer : S = Q K^T into one of two TMEM buffers, O += P V into a third
-//   warps 2..5  128 softmax threads, thread r <-> TMEM lane r <-> query row r: online softmax with lazy
+//   warps 2..9  256 softmax threads, two per query row (TMEM lane), each owning half of the key columns: online softmax with lazy
 //               rescaling of O (only when the running maximum grew by more than 2^8), P written as bf16
 //               into 128B-swizzled shared memory where the second MMA reads it, final O / l and lse
 // All waits are bounded; a timeout raises the status word and the CTA unwinds.
@@ -23,7 +23,8 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 128;
 constexpr int KV_STAGES = 2;
-constexpr int FWD_THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;  // two warps per TMEM lane quarter: each thread owns half of the columns of its row
+constexpr int FWD_THREADS = 64 + SOFTMAX_WARPS * 32;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
 template <int D>
@@ -37,11 +38,12 @@ struct FwdSmem {
   static constexpr int OFF_V = OFF_K + KV_STAGES * K_BYTES;
   static constexpr int OFF_P = OFF_V + KV_STAGES * V_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_X = OFF_BAR + 256;  // row statistics exchanged between the two threads of a row: [2][2][128] floats
+  static constexpr int TOTAL = OFF_X + 2 * 2 * BLOCK_M * 4 + 1024;
 };
 
 // barrier indices
-enum { B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = 3, B_S_FULL = 5, B_S_EMPTY = 7, B_P_READY = 9, B_PV_DONE = 10, B_COUNT = 11 };
+enum { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_S_EMPTY = 11, B_P_READY = 13, B_PV_DONE = 14, B_COUNT = 15 };
 
 template <int D>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -59,6 +61,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_tile = reinterpret_cast<int*>(tmem_slot + 2);  // [doc_start, doc_len, q_tile] or doc_len = -1
+  float* s_x = reinterpret_cast<float*>(smem + L::OFF_X);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -89,12 +92,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     s_tile[2] = qt;
     mbar_init(&bars[B_Q], 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&bars[B_KV_FULL + s], 1);
-      mbar_init(&bars[B_KV_EMPTY + s], 1);
+      mbar_init(&bars[B_K_FULL + s], 1);
+      mbar_init(&bars[B_K_EMPTY + s], 1);
+      mbar_init(&bars[B_V_FULL + s], 1);
+      mbar_init(&bars[B_V_EMPTY + s], 1);
       mbar_init(&bars[B_S_FULL + s], 1);
-      mbar_init(&bars[B_S_EMPTY + s], 128);
+      mbar_init(&bars[B_S_EMPTY + s], SOFTMAX_WARPS * 32);
     }
-    mbar_init(&bars[B_P_READY], 128);
+    mbar_init(&bars[B_P_READY], SOFTMAX_WARPS * 32);
     mbar_init(&bars[B_PV_DONE], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -127,21 +132,26 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_arrive_expect_tx(&bars[B_Q], L::Q_BYTES);
 #pragma unroll
       for (int kb = 0; kb < D / 64; ++kb) tma_load_2d(sQ + kb * (BLOCK_M * 128), &tm_qkv, &bars[B_Q], q_col + kb * 64, doc_start + q0);
-      for (int j = 0; j < n_tiles; ++j) {
+      // K and V tiles travel through separate 2-stage rings: a K stage is free as soon as its S = Q K^T has retired,
+      // long before the V stage of the same tile, so the next-but-one K tile is in flight while this one's softmax runs.
+      auto load_tile = [&](int j, bool is_k) -> bool {
         const int st = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait(&bars[B_KV_EMPTY + st], ph ^ 1, abort_flag)) {
-          raise_status(status, kStatusWaitTimeoutProducer, abort_flag);
-          break;
-        }
-        mbar_arrive_expect_tx(&bars[B_KV_FULL + st], L::K_BYTES + L::V_BYTES);
+        uint64_t* full = &bars[(is_k ? B_K_FULL : B_V_FULL) + st];
+        if (!mbar_wait(&bars[(is_k ? B_K_EMPTY : B_V_EMPTY) + st], ph ^ 1, abort_flag)) return false;
+        mbar_arrive_expect_tx(full, L::K_BYTES);
         const int row = doc_start + j * BLOCK_N;
+        uint8_t* dst = is_k ? sK + st * L::K_BYTES : sV + st * L::V_BYTES;
 #pragma unroll
-        for (int kb = 0; kb < D / 64; ++kb) {
-          tma_load_2d(sK + st * L::K_BYTES + kb * (BLOCK_N * 128), &tm_qkv, &bars[B_KV_FULL + st], k_col + kb * 64, row);
-          tma_load_2d(sV + st * L::V_BYTES + kb * (BLOCK_N * 128), &tm_qkv, &bars[B_KV_FULL + st], v_col + kb * 64, row);
-        }
+        for (int kb = 0; kb < D / 64; ++kb) tma_load_2d(dst + kb * (BLOCK_N * 128), &tm_qkv, full, (is_k ? k_col : v_col) + kb * 64, row);
+        return true;
+      };
+      bool ok = load_tile(0, true);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = load_tile(j + 1, true);
+        if (ok) ok = load_tile(j, false);
       }
+      if (!ok) raise_status(status, kStatusWaitTimeoutProducer, abort_flag);
       if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
@@ -157,7 +167,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       bool ok = mbar_wait(&bars[B_Q], 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
         const int st = j % KV_STAGES;
-        if (!mbar_wait(&bars[B_KV_FULL + st], (j / KV_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars[B_K_FULL + st], (j / KV_STAGES) & 1, abort_flag)) return false;
         if (!mbar_wait(&bars[B_S_EMPTY + st], ((j / 2) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
         const uint32_t k_base = smem_u32(sK + st * L::K_BYTES);
@@ -167,6 +177,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           umma_f16_ss(tmem_S0 + st * BLOCK_N, umma_smem_desc_sw128(q_base + off, 16, 1024),
                       umma_smem_desc_sw128(k_base + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
         }
+        umma_commit(&bars[B_K_EMPTY + st]);
         umma_commit(&bars[B_S_FULL + st]);
         return true;
       };
@@ -178,8 +189,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           ok = false;
           break;
         }
-        tc_fence_after_sync();
         const int st = j % KV_STAGES;
+        if (!mbar_wait(&bars[B_V_FULL + st], (j / KV_STAGES) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
         const uint32_t v_base = smem_u32(sV + st * L::V_BYTES);
 #pragma unroll
         for (int k = 0; k < BLOCK_N / 16; ++k) {
@@ -187,7 +202,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           const uint64_t db = umma_smem_desc_sw128(v_base + k * 16 * 128, BLOCK_N * 128, 1024);
           umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
-        umma_commit(&bars[B_KV_EMPTY + st]);
+        umma_commit(&bars[B_V_EMPTY + st]);
         umma_commit(&bars[B_PV_DONE]);
       }
       if (!ok) raise_status(status, kStatusWaitTimeoutMma, abort_flag);
@@ -195,71 +210,91 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax / correction / epilogue
+    constexpr int HALF_N = BLOCK_N / 2;
     const int q = warp & 3;              // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;    // which half of the key columns (and of the output columns) this thread owns
     const int r = q * 32 + lane;         // row inside the tile
     const int q_local = q0 + r;          // row inside the document
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    float m_used = -INFINITY, l_sum = 0.f;
+    const int pair_bar = 1 + q;          // named barrier of the two warps that share these rows
+    float m_used = -INFINITY, l_sum = 0.f;  // l_sum: this thread's columns only
     bool ok = true;
+    bool failed = false;  // a bounded wait ran out: carried to the next pair barrier so that both warps of a pair leave together
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j % KV_STAGES;
-      if (!mbar_wait(&bars[B_S_FULL + st], (j / 2) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
+      const bool got = !failed && mbar_wait(&bars[B_S_FULL + st], (j / 2) & 1, abort_flag);
       tc_fence_after_sync();
-      uint32_t s[BLOCK_N];
+      uint32_t s[HALF_N];
 #pragma unroll
-      for (int c = 0; c < BLOCK_N / 32; ++c) B200_TMEM_LD_32((s + c * 32), tmem_S0 + lane_addr + st * BLOCK_N + c * 32);
+      for (int c = 0; c < HALF_N / 32; ++c) B200_TMEM_LD_32((s + c * 32), tmem_S0 + lane_addr + st * BLOCK_N + half * HALF_N + c * 32);
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[B_S_EMPTY + st]);
 
-      // scale, mask, running maximum
-      const int kv0 = j * BLOCK_N;
-      const bool needs_mask = (kv0 + BLOCK_N > doc_len) || (causal && kv0 + BLOCK_N - 1 > q0);
-      float m_tile = -INFINITY;
+      const int kv0 = j * BLOCK_N + half * HALF_N;
+      const bool needs_mask = (j * BLOCK_N + BLOCK_N > doc_len) || (causal && j * BLOCK_N + BLOCK_N - 1 > q0);
+      if (needs_mask) {
 #pragma unroll
-      for (int c = 0; c < BLOCK_N; ++c) {
-        float v = __uint_as_float(s[c]) * scale_log2;
-        if (needs_mask) {
+        for (int c = 0; c < HALF_N; ++c) {
           const int kv = kv0 + c;
-          if (kv >= doc_len || (causal && kv > q_local)) v = -INFINITY;
+          if (kv >= doc_len || (causal && kv > q_local)) s[c] = __float_as_uint(-INFINITY);
         }
-        s[c] = __float_as_uint(v);
-        m_tile = fmaxf(m_tile, v);
       }
+      // maximum of the raw scores (the scale is positive, so it commutes with the maximum), then across the two halves
+      float m_raw[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < HALF_N; c += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          m_raw[u] = fmaxf(m_raw[u], fmaxf(__uint_as_float(s[c + 2 * u]), __uint_as_float(s[c + 2 * u + 1])));
+      }
+      float* x_mine = s_x + ((j & 1) * 2 + half) * BLOCK_M;
+      const float* x_other = s_x + ((j & 1) * 2 + (half ^ 1)) * BLOCK_M;
+      const float m_half = fmaxf(fmaxf(m_raw[0], m_raw[1]), fmaxf(m_raw[2], m_raw[3]));
+      x_mine[r] = m_half;
+      // the barrier also carries the outcome of the bounded wait above, so that both warps of a pair leave together
+      if (named_barrier_or(pair_bar, 64, !got)) { ok = false; break; }
+      const float m_tile = fmaxf(m_half, x_other[r]) * scale_log2;
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0) {
         m_used = m_tile;
       } else if (m_tile > m_used + RESCALE_THRESHOLD) {
-        alpha = exp2f(m_used - m_tile);
+        alpha = fast_exp2(m_used - m_tile);
         m_used = m_tile;
         rescale = true;
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      float row_sum = 0.f;
-      uint32_t p[BLOCK_N / 2];
+      // p = 2^(s * scale*log2e - m): one packed multiply-add per pair, one special-function instruction per element
+      const float2 scale2 = make_float2(scale_log2, scale_log2), neg_m2 = make_float2(-m_sub, -m_sub);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      uint32_t p[HALF_N / 2];
 #pragma unroll
-      for (int c = 0; c < BLOCK_N; c += 2) {
-        const float a = exp2f(__uint_as_float(s[c]) - m_sub);
-        const float b = exp2f(__uint_as_float(s[c + 1]) - m_sub);
-        row_sum += a + b;
-        p[c / 2] = pack_bf16x2(a, b);
+      for (int c = 0; c < HALF_N; c += 4) {
+        const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, neg_m2);
+        const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), scale2, neg_m2);
+        const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+        const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+        sum2[0] = __fadd2_rn(sum2[0], e0);
+        sum2[1] = __fadd2_rn(sum2[1], e1);
+        p[c / 2] = pack_bf16x2(e0.x, e0.y);
+        p[c / 2 + 1] = pack_bf16x2(e1.x, e1.y);
       }
+      const float row_sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       l_sum = l_sum * alpha + row_sum;
 
       if (j > 0) {
         // P buffer free again and O stable: PV of the previous tile retired
         if (!mbar_wait(&bars[B_PV_DONE], (j - 1) & 1, abort_flag)) {
-          ok = false;
-          break;
+          failed = true;
+          *abort_flag = 1;
+          continue;
         }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int cc = 0; cc < D / 64; ++cc) {
+            const int c = half * (D / 64) + cc;
             uint32_t o[32];
             B200_TMEM_LD_32(o, tmem_O + lane_addr + c * 32);
             tmem_ld_wait();
@@ -270,30 +305,35 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           tmem_st_wait();
         }
       }
-      // P (bf16) -> shared memory, K-major with the 128-byte swizzle the MMA expects
+      // P (bf16) -> shared memory, K-major with the 128-byte swizzle the MMA expects; this thread's 64 keys = one K block
+      {
+        uint8_t* row_base = sP + half * (BLOCK_M * 128) + r * 128;
 #pragma unroll
-      for (int kb = 0; kb < BLOCK_N / 64; ++kb) {
-        uint8_t* row_base = sP + kb * (BLOCK_M * 128) + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const int pi = kb * 32 + ch * 4;
-          *reinterpret_cast<uint4*>(row_base + ((ch ^ (r & 7)) * 16)) = make_uint4(p[pi], p[pi + 1], p[pi + 2], p[pi + 3]);
-        }
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(row_base + ((ch ^ (r & 7)) * 16)) = make_uint4(p[ch * 4], p[ch * 4 + 1], p[ch * 4 + 2], p[ch * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars[B_P_READY]);
     }
+    ok = ok && !failed;
     if (ok && n_tiles > 0) ok = mbar_wait(&bars[B_PV_DONE], (n_tiles - 1) & 1, abort_flag);
+    // total of the two halves of every row (also the point where a pair agrees on having finished)
+    float* x_mine = s_x + ((n_tiles & 1) * 2 + half) * BLOCK_M;
+    const float* x_other = s_x + ((n_tiles & 1) * 2 + (half ^ 1)) * BLOCK_M;
+    x_mine[r] = l_sum;
+    if (named_barrier_or(pair_bar, 64, !ok)) ok = false;
     if (!ok) {
       raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
     } else {
       tc_fence_after_sync();
-      const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const float l_row = l_sum + x_other[r];
+      const float inv_l = l_row > 0.f ? 1.f / l_row : 0.f;
       const bool valid = q_local < doc_len;
       __nv_bfloat16* orow = out + (long long)(doc_start + q_local) * out_stride + (long long)head * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;
         uint32_t o[32];
         B200_TMEM_LD_32(o, tmem_O + lane_addr + c * 32);
         tmem_ld_wait();
@@ -309,7 +349,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
         }
       }
-      if (valid) lse[(long long)head * T + doc_start + q_local] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
+      if (valid && half == 0) lse[(long long)head * T + doc_start + q_local] = (m_used + log2f(l_row)) * 0.6931471805599453f;
     }
   }
 
