@@ -16,6 +16,7 @@ import math
 import torch
 import torch.nn as nn
 
+from ...enums import Kernel
 from ...utils import divide_if_divisible
 from ..context import SequenceContext
 from ..parameter import mark_parameter_as_mup_learning_rate, mark_parameter_as_no_weight_decay
@@ -98,6 +99,42 @@ class _RecurrentBase(nn.Module):
     def reset_parameters(self) -> None:
         nn.init.normal_(self.state_weight, std=self.state_weight_std)
 
+    kernel_name = None  # the switch that turns on the native scan for this mixer
+
+    def _kernel_ok(self, x: torch.Tensor) -> bool:
+        from ...kernels import is_kernel_allowed
+        from ...ops.recurrent import recurrent_kernel_ok
+
+        return is_kernel_allowed(self.kernel_name) and recurrent_kernel_ok(x, self.state_head_dim)
+
+    def _masked_input_and_state(self, x: torch.Tensor, ctx: SequenceContext, past_key_values):
+        if ctx.attention_mask is not None and past_key_values is None and not bool(torch.all(ctx.attention_mask == 1)):
+            # left padding: a zero input keeps tanh(0) = 0 state contributions out of real positions
+            x = x * ctx.attention_mask[:, -x.shape[1]:, None].to(x.dtype)
+        state = None if past_key_values is None else past_key_values.get_cache(self.layer_idx)
+        return x, state
+
+    def _store_state(self, h: torch.Tensor, num_tokens: int, past_key_values) -> None:
+        if past_key_values is not None:
+            past_key_values.update(state=h[:, -1].reshape(h.shape[0], self.num_heads, self.state_head_dim),
+                                   num_tokens_added=num_tokens, layer_idx=self.layer_idx)
+
+    def _native_scan(self, x: torch.Tensor, ctx: SequenceContext, past_key_values) -> torch.Tensor:
+        """The scan kernel over the packed token rows (a padded batch is ``batch`` documents of equal length)."""
+        from ...ops.recurrent import recurrent_scan
+
+        weight = self.state_weight * self.factor
+        gru = self.gates == 3
+        if ctx.packed:
+            return recurrent_scan(x, weight, ctx.cu_seqlens_int32(), self.num_heads, self.state_head_dim, gru, self.gradient_clipping)
+        x, state = self._masked_input_and_state(x, ctx, past_key_values)
+        b, s, width = x.shape
+        cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=x.device)
+        h = recurrent_scan(x.reshape(b * s, width), weight, cu, self.num_heads, self.state_head_dim, gru, self.gradient_clipping, h0=state)
+        h = h.view(b, s, self.num_heads, self.state_head_dim)
+        self._store_state(h, s, past_key_values)
+        return h
+
     def _scan(self, x: torch.Tensor, state: torch.Tensor | None) -> torch.Tensor:
         raise NotImplementedError
 
@@ -107,19 +144,16 @@ class _RecurrentBase(nn.Module):
         if self.is_gated_normalization:
             x, gate = x.split((self.gates * self.state_size, self.state_size), dim=-1)
         x = x * self.factor
-        if ctx.packed:
+        if self._kernel_ok(x):
+            h = self._native_scan(x, ctx, past_key_values)
+        elif ctx.packed:
             bounds = ctx.cu_seqlens.tolist()
             pieces = [self._scan(x[s:e].unsqueeze(0), None).squeeze(0) for s, e in zip(bounds[:-1], bounds[1:]) if e > s]
             h = torch.cat(pieces, dim=0)
         else:
-            if ctx.attention_mask is not None and past_key_values is None and not bool(torch.all(ctx.attention_mask == 1)):
-                # left padding: a zero input keeps tanh(0) = 0 state contributions out of real positions
-                x = x * ctx.attention_mask[:, -x.shape[1]:, None].to(x.dtype)
-            state = None if past_key_values is None else past_key_values.get_cache(self.layer_idx)
+            x, state = self._masked_input_and_state(x, ctx, past_key_values)
             h = self._scan(x, state)
-            if past_key_values is not None:
-                past_key_values.update(state=h[:, -1].reshape(h.shape[0], self.num_heads, self.state_head_dim),
-                                       num_tokens_added=x.shape[1], layer_idx=self.layer_idx)
+            self._store_state(h, x.shape[1], past_key_values)
         h = h.reshape(*h.shape[:-2], self.state_size)
         h = self.norm(h, gate) if self.is_gated_normalization else self.norm(h)
         return self.output_projection(h)
@@ -130,6 +164,7 @@ class _RecurrentBase(nn.Module):
 
 class RNN(_RecurrentBase):
     gates = 1
+    kernel_name = Kernel.rnn_cute
 
     def _scan(self, x, state):
         x = x.reshape(*x.shape[:-1], self.num_heads, self.state_head_dim)
@@ -138,6 +173,7 @@ class RNN(_RecurrentBase):
 
 class GRU(_RecurrentBase):
     gates = 3
+    kernel_name = Kernel.gru_cute
 
     def _scan(self, x, state):
         xi, xf, xr = (t.reshape(*t.shape[:-1], self.num_heads, self.state_head_dim) for t in x.chunk(3, dim=-1))

@@ -376,6 +376,7 @@ class MoE_TP(MoE):
                  initializer_range: float, m_width: float | None, num_layers: int, use_padding_free_transformer: bool,
                  sequence_parallel: bool = False) -> None:
         nn.Module.__init__(self)
+        self.expert_parallel = False  # experts are split over the tensor-parallel group here
         self.num_experts, self.top_k = num_experts, num_experts_per_tok
         self.hidden_size = hidden_size
         self.intermediate_size = divide_if_divisible(intermediate_size, tp.tp_world(), "")

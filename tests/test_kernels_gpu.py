@@ -330,3 +330,48 @@ def test_stickbreaking_attention_forward_matches_dense_formulation(head_dim, gro
     torch.testing.assert_close(rem, ref_rem, atol=2e-2, rtol=2e-2)
     (out.float().square().sum() + rem.sum()).backward()
     assert torch.isfinite(qkv.grad).all() and float(qkv.grad.abs().sum()) > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("gru", [False, True])
+@pytest.mark.parametrize("head_dim,clip", [(16, None), (64, 0.05), (128, None)])
+def test_recurrent_scan_matches_the_step_by_step_loops(gru, head_dim, clip):
+    """RNN / GRU scan kernels (forward, input / weight / initial-state gradients, clamped state gradient) against the
+    PyTorch loops in fp32, over documents of different lengths."""
+    from lm_engine.hf_models.layers.recurrent import gru_scan, rnn_scan
+    from lm_engine.ops.recurrent import recurrent_scan
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    n, d, gates = 3, head_dim, (3 if gru else 1)
+    lengths = [37, 5, 64]
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
+    total = sum(lengths)
+    x = (torch.randn(total, gates * n * d, device=dev) * 0.5).requires_grad_(True)
+    w = (torch.randn(gates * n, d, d, device=dev) / d**0.5).requires_grad_(True)
+    h0 = (torch.randn(len(lengths), n, d, device=dev) * 0.3).requires_grad_(True)
+    dout = torch.randn(total, n, d, device=dev)
+
+    out = recurrent_scan(x, w, cu, n, d, gru, clip, h0=h0)
+    out.backward(dout)
+    got = (out.detach().clone(), x.grad.clone(), w.grad.clone(), h0.grad.clone())
+    x.grad = w.grad = h0.grad = None
+
+    pieces = []
+    start = 0
+    for i, length in enumerate(lengths):
+        xs = x[start:start + length].unsqueeze(0)
+        state = h0[i:i + 1]
+        if gru:
+            xi, xf, xr = (t.reshape(1, length, n, d) for t in xs.chunk(3, dim=-1))
+            wi, wf, wr = w.chunk(3, dim=0)
+            pieces.append(gru_scan(xi, wi, xf, wf, xr, wr, state, clip).squeeze(0))
+        else:
+            pieces.append(rnn_scan(xs.reshape(1, length, n, d), w, state, clip).squeeze(0))
+        start += length
+    ref = torch.cat(pieces, dim=0)
+    ref.backward(dout)
+    for name, a, b in zip(("out", "dx", "dw", "dh0"), got, (ref.detach(), x.grad, w.grad, h0.grad)):
+        err = (a - b).abs().max().item()
+        scale = b.abs().max().item() + 1e-6
+        assert err <= 2e-3 * scale + 1e-5, f"{name}: max abs error {err} against magnitude {scale}"
