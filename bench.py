@@ -176,7 +176,9 @@ def run_native(cli) -> dict:
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
     expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
-    extra = {"expert_parallel_world_size": expert_parallel} if expert_parallel > 1 else None
+    # expert row buffers: twice a rank's balanced share instead of the worst case (every entry of the group on one rank);
+    # the number of entries this bound dropped is reported and must be 0 for the run to count as dropless
+    extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": 2.0} if expert_parallel > 1 else None
     args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
 
     init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel)
@@ -276,6 +278,13 @@ def run_native(cli) -> dict:
         "clocks": clocks, "gpu_launches": launches, "loss_after_warmup": loss_after_warmup,
         "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
     }
+    if expert_parallel > 1:
+        from lm_engine.parallel.expert_parallel import dropped_entries
+
+        dropped = torch.tensor([dropped_entries(device)], dtype=torch.int64, device=device)
+        torch.distributed.all_reduce(dropped)
+        result["config"]["expert_capacity_factor"] = 2.0
+        result["config"]["expert_entries_dropped"] = int(dropped.item())
     if e2e is not None:
         result["e2e"] = e2e
     ProcessGroupManager.destroy_process_groups()

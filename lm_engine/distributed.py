@@ -39,6 +39,10 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
         for name, p in wrapper.named_parameters():
             if name.startswith(frozen):
                 p.requires_grad_(False)
+        if dist_args.expert_parallel_world_size > 1:
+            from .parallel.expert_parallel import set_expert_capacity_factor
+
+            set_expert_capacity_factor(dist_args.expert_capacity_factor)
         engine = ShardedTrainingEngine(
             wrapper,
             compute_dtype=dtype,

@@ -32,18 +32,33 @@ class GroupedLayout:
     tile_expert: torch.Tensor  # int32 [rows / 128]: expert of each tile (>= num_experts: unused tile)
     padded_offsets: torch.Tensor  # int32 [num_experts + 1]
     rows: int  # static upper bound, multiple of 128
+    dropped: torch.Tensor | None = None  # int32 [1]: entries that did not fit under a capacity bound (device counter)
+
+
+def worst_case_rows(entries: int, num_local_experts: int) -> int:
+    return ((entries + num_local_experts * (TILE - 1)) + TILE - 1) // TILE * TILE
 
 
 def build_grouped_layout(expert_of_entry: torch.Tensor, num_experts: int, first_expert: int = 0,
-                         num_local_experts: int | None = None) -> GroupedLayout:
-    """Stable counting sort of entries by expert with tile-aligned expert ranges, using device ops only.
+                         num_local_experts: int | None = None, capacity_rows: int | None = None) -> GroupedLayout:
+    """Stable counting sort of entries by expert with tile-aligned expert ranges, on the device (no host sync).
 
     ``expert_of_entry``: int [entries]. Entries whose expert is outside ``[first_expert, first_expert + local)`` are not
     placed (their ``dest_row`` is -1), which is how one rank of an expert parallel group selects its share.
+    ``capacity_rows`` bounds the row buffer below the worst case (all entries on this rank); entries that do not fit are
+    dropped and counted in ``dropped``. On a GPU the layout comes from three small kernels (``csrc/ops/moe_layout.cu``);
+    the torch formulation below is the reference and the CPU path, and gives the same result element for element.
     """
     local = num_experts if num_local_experts is None else num_local_experts
     entries = expert_of_entry.numel()
     device = expert_of_entry.device
+    rows = worst_case_rows(entries, local)
+    if capacity_rows is not None:
+        rows = min(rows, max(TILE, (capacity_rows + TILE - 1) // TILE * TILE))
+    if expert_of_entry.is_cuda and local <= 256 and native_available() and hasattr(native(), "moe_layout"):
+        flat = expert_of_entry.reshape(-1).to(torch.int32).contiguous()
+        dest_row, src_entry, tile_expert, padded_offsets, dropped = native().moe_layout(flat, first_expert, local, rows)
+        return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows, dropped)
     e = expert_of_entry.reshape(-1).to(torch.int64) - first_expert
     mine = (e >= 0) & (e < local)
     key = torch.where(mine, e, torch.full_like(e, local))  # foreign entries sort last
@@ -54,12 +69,17 @@ def build_grouped_layout(expert_of_entry: torch.Tensor, num_experts: int, first_
     padded_start = padded_end - padded
     start = torch.cumsum(counts, 0) - counts
 
-    rows = ((entries + local * (TILE - 1)) + TILE - 1) // TILE * TILE
     sorted_key = key[order]
     placed = sorted_key < local
     safe_key = sorted_key.clamp(max=local - 1)
     position = torch.arange(entries, device=device) - start[safe_key]
     row_sorted = torch.where(placed, padded_start[safe_key] + position, torch.full_like(position, -1))
+    fits = row_sorted < rows
+    dropped = (placed & ~fits).sum().to(torch.int32).reshape(1)
+    placed = placed & fits
+    row_sorted = torch.where(placed, row_sorted, torch.full_like(row_sorted, -1))
+    padded_start = padded_start.clamp(max=rows)
+    padded_end = padded_end.clamp(max=rows)
 
     dest_row = torch.empty(entries, dtype=torch.int32, device=device)
     dest_row[order] = row_sorted.to(torch.int32)
@@ -70,7 +90,7 @@ def build_grouped_layout(expert_of_entry: torch.Tensor, num_experts: int, first_
     tile_start = torch.arange(rows // TILE, device=device) * TILE
     tile_expert = torch.searchsorted(padded_end, tile_start, right=True).to(torch.int32)  # == local for unused tiles
     padded_offsets = torch.cat([padded_start.new_zeros(1), padded_end]).to(torch.int32)
-    return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows)
+    return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows, dropped)
 
 
 def native_moe_ok(x: torch.Tensor, activation_function: str) -> bool:

@@ -31,6 +31,39 @@ from .symmetric import PeerBuffer, PeerGroup, get_peer_group
 
 _WORKSPACES: dict[int, "_Workspace"] = {}
 
+# Row buffers of a rank hold at most ``capacity_factor x (its balanced share of the routed entries)`` rows (plus tile
+# padding); None sizes them for the worst case, in which every entry of the group lands on one rank. Entries beyond the
+# bound are dropped (they contribute nothing to their token) and counted on the device in ``_DROPPED``.
+_CAPACITY_FACTOR: float | None = None
+_DROPPED: dict[torch.device, torch.Tensor] = {}
+
+
+def set_expert_capacity_factor(factor: float | None) -> None:
+    global _CAPACITY_FACTOR
+    assert factor is None or factor >= 1.0, "expert_capacity_factor must be at least 1"
+    _CAPACITY_FACTOR = factor
+
+
+def dropped_entries(device: torch.device) -> int:
+    """Entries dropped on this rank since the start of the run (synchronises with the device)."""
+    counter = _DROPPED.get(device)
+    return 0 if counter is None else int(counter.item())
+
+
+def _capacity_rows(entries_per_rank: int, local_experts: int) -> int | None:
+    if _CAPACITY_FACTOR is None:
+        return None
+    return int(_CAPACITY_FACTOR * entries_per_rank + 0.5) + local_experts * (TILE - 1)
+
+
+def _count_dropped(layout) -> None:
+    if _CAPACITY_FACTOR is None or layout.dropped is None:
+        return
+    device = layout.dropped.device
+    if device not in _DROPPED:
+        _DROPPED[device] = torch.zeros(1, dtype=torch.int64, device=device)
+    _DROPPED[device] += layout.dropped
+
 
 def ep_world() -> int:
     return ProcessGroupManager.get_expert_parallel_world_size() if ProcessGroupManager.is_initialized() else 1
@@ -132,7 +165,8 @@ def _exchange_rows(dest_row: torch.Tensor, entries: int, rows: int) -> torch.Ten
     received = received.view(world, entries)
     owner = received.argmax(dim=0)  # exactly one owner reports a row >= 0
     local = received.max(dim=0).values
-    return (owner.to(torch.int32) * rows + local).to(torch.int32).contiguous()
+    # an entry that its owner had to drop (capacity bound) has no row anywhere: -1, which the combine kernel skips
+    return torch.where(local >= 0, owner.to(torch.int32) * rows + local, torch.full_like(local, -1)).to(torch.int32).contiguous()
 
 
 def _exchange_values(per_entry: torch.Tensor, entries: int) -> torch.Tensor:
@@ -156,7 +190,9 @@ class _ExpertParallelFn(torch.autograd.Function):
 
         selected_all = torch.cat(_all_gather_plain(selected_experts.reshape(-1).to(torch.int32)))
         weights_all = torch.cat(_all_gather_plain(router_weights.reshape(-1).float()))
-        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local)
+        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
+                                      capacity_rows=_capacity_rows(entries, local))
+        _count_dropped(layout)
         rows = layout.rows
 
         tokens = ws.buffer("tokens", T * H)
@@ -167,7 +203,6 @@ class _ExpertParallelFn(torch.autograd.Function):
         te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
         xg = C.moe_gather(tokens.ptrs, [], layout.src_entry, H, entries, top_k, x, te, local)  # dispatch: pull rows from their owners
         fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
-        del xg
         act = C.swiglu_fwd(fc, te, local)
         C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
         del act
@@ -176,14 +211,15 @@ class _ExpertParallelFn(torch.autograd.Function):
         weights32 = router_weights.reshape(-1).float().contiguous()
         out = C.moe_combine(out_rows.ptrs, global_row, weights32, T, H, top_k, rows, x)  # combine: pull the k results per token
 
+        # the gathered rows are kept for the weight gradient: pulling them from the peers a second time costs more than the memory
         ctx.save_for_backward(x, w_fc, w_proj, weights_all, fc, layout.dest_row, layout.src_entry, layout.tile_expert,
-                              layout.padded_offsets, global_row)
+                              layout.padded_offsets, global_row, xg)
         ctx.meta = (num_experts, top_k, rows, router_weights.dtype, router_weights.shape)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        x, w_fc, w_proj, weights_all, fc, dest_row, src_entry, tile_expert, padded_offsets, global_row = ctx.saved_tensors
+        x, w_fc, w_proj, weights_all, fc, dest_row, src_entry, tile_expert, padded_offsets, global_row, xg = ctx.saved_tensors
         num_experts, top_k, rows, w_dtype, w_shape = ctx.meta
         C = ops.native()
         st = ops.status_word(x.device)
@@ -207,12 +243,7 @@ class _ExpertParallelFn(torch.autograd.Function):
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
         del dyg, act
 
-        peer.barrier()  # all ranks have pulled the output gradients; the token buffer can take the activations again
-        tokens.tensor[: T * H].view(T, H).copy_(x)
-        peer.barrier()
-        xg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x, tile_expert, local)
         g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
-        del xg
         C.grouped_rows(dfc, w_fc, tile_expert, True, st, out_rows.tensor[: rows * H].view(rows, H))
         peer.barrier()
         dx = C.moe_combine(out_rows.ptrs, global_row, None, T, H, top_k, rows, x)

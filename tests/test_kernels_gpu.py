@@ -375,3 +375,27 @@ def test_recurrent_scan_matches_the_step_by_step_loops(gru, head_dim, clip):
         err = (a - b).abs().max().item()
         scale = b.abs().max().item() + 1e-6
         assert err <= 2e-3 * scale + 1e-5, f"{name}: max abs error {err} against magnitude {scale}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("entries,num_experts,first,local,capacity", [(5000, 40, 0, 40, None), (70001, 40, 10, 5, None),
+                                                                   (9000, 8, 4, 4, 3000), (100, 256, 0, 256, None)])
+def test_expert_layout_kernels_match_the_sort_based_layout(entries, num_experts, first, local, capacity):
+    """The counting-sort kernels give, element for element, the stable argsort layout (also under a capacity bound)."""
+    import lm_engine.ops.moe as moe
+
+    torch.manual_seed(entries)
+    experts = torch.randint(0, num_experts, (entries,), device="cuda", dtype=torch.int32)
+    got = moe.build_grouped_layout(experts, num_experts, first_expert=first, num_local_experts=local, capacity_rows=capacity)
+    assert got.dropped is not None
+    available = moe.native_available
+    moe.native_available = lambda: False  # the torch formulation of the same function
+    try:
+        ref = moe.build_grouped_layout(experts, num_experts, first_expert=first, num_local_experts=local, capacity_rows=capacity)
+    finally:
+        moe.native_available = available
+    assert got.rows == ref.rows
+    for name in ("dest_row", "src_entry", "tile_expert", "padded_offsets", "dropped"):
+        assert torch.equal(getattr(got, name).cpu(), getattr(ref, name).cpu()), name
+    if capacity is not None:
+        assert int(got.dropped.item()) > 0
