@@ -22,4 +22,11 @@ void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, co
 void sb_attn_varlen_fwd(const void* qkv, long long qkv_stride, void* out, long long out_stride, float* rem, const int* cu_seqlens,
                         int num_docs, int T, int groups, int qpg, int head_dim, float scale, int* status, cudaStream_t stream);
 
+// Stick-breaking attention backward (sb_attention_bwd.cu). rem / drem: [groups * qpg, T] fp32 (forward output and its
+// gradient); gtot: scratch [groups * qpg, T] fp32; dk_accum / dv_accum: scratch [T, groups * head_dim] fp32; dqkv: layout of qkv.
+void sb_attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, const void* out, long long out_stride, const float* rem,
+                        const float* drem, float* gtot, float* dk_accum, float* dv_accum, void* dqkv, long long dqkv_stride,
+                        const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale, int* status,
+                        cudaStream_t stream);
+
 }  // namespace b200

@@ -67,10 +67,35 @@ std::vector<Tensor> sb_attn_fwd(const Tensor& qkv, const Tensor& cu_seqlens, int
   return {out, rem};
 }
 
+// Gradient of the fused qkv buffer from (d out, d rem); out / rem are the forward results.
+Tensor sb_attn_bwd(const Tensor& dout, const Tensor& drem, const Tensor& qkv, const Tensor& out, const Tensor& rem, const Tensor& cu_seqlens,
+                   int64_t groups, int64_t qpg, int64_t d, double scale, const c10::optional<Tensor>& status) {
+  TORCH_CHECK(dout.is_cuda() && dout.scalar_type() == torch::kBFloat16 && dout.is_contiguous(), "dout: contiguous bf16");
+  TORCH_CHECK(out.is_contiguous() && out.sizes() == dout.sizes(), "out/dout mismatch");
+  TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && qkv.stride(1) == 1, "qkv: bf16 with unit inner stride");
+  TORCH_CHECK(rem.scalar_type() == torch::kFloat32 && drem.scalar_type() == torch::kFloat32 && rem.is_contiguous() && drem.is_contiguous() &&
+                  rem.sizes() == drem.sizes(), "rem / drem: contiguous fp32 [heads, T]");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int64_t T = qkv.size(0);
+  const int64_t hq = groups * qpg;
+  TORCH_CHECK(rem.numel() == hq * T, "rem: [heads, T]");
+  Tensor dqkv = torch::empty({T, groups * (qpg + 2) * d}, qkv.options());
+  auto f32 = qkv.options().dtype(torch::kFloat32);
+  Tensor gtot = torch::empty({hq, T}, f32);
+  Tensor dk_accum = torch::empty({T, groups * d}, f32);
+  Tensor dv_accum = torch::empty({T, groups * d}, f32);
+  sb_attn_varlen_bwd(dout.data_ptr(), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), rem.data_ptr<float>(),
+                     drem.data_ptr<float>(), gtot.data_ptr<float>(), dk_accum.data_ptr<float>(), dv_accum.data_ptr<float>(), dqkv.data_ptr(),
+                     dqkv.stride(0), cu_seqlens.data_ptr<int>(), (int)cu_seqlens.numel() - 1, (int)T, (int)groups, (int)qpg, (int)d,
+                     (float)scale, status_of(status), at::cuda::getCurrentCUDAStream().stream());
+  return dqkv;
+}
+
 }  // namespace
 
 void register_attention(pybind11::module_& m) {
   m.def("sb_attn_fwd", &sb_attn_fwd);
+  m.def("sb_attn_bwd", &sb_attn_bwd);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
 }

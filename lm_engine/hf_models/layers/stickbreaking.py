@@ -40,37 +40,29 @@ def stickbreaking_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
 
 
 class _FusedStickBreaking(torch.autograd.Function):
-    """Forward: the sm_100a kernel on the fused qkv buffer of a packed batch. Backward: the dense fp32 formulation above,
-    recomputed document by document under autograd (a backward kernel does not exist yet)."""
+    """The sm_100a kernels on the fused qkv buffer of a packed batch (``csrc/ops/sb_attention_{fwd,bwd}.cu``): forward
+    walks the key tiles from the diagonal to the start of the document, backward does the same walk per query tile and
+    reduces the key / value gradients across query tiles in fp32."""
 
     @staticmethod
     def forward(ctx, qkv, cu_seqlens, groups, group_size, head_dim, scale):
         from ... import ops
 
         out, rem = ops.native().sb_attn_fwd(qkv, cu_seqlens, groups, group_size, head_dim, scale, ops.status_word(qkv.device))
-        ctx.save_for_backward(qkv, cu_seqlens)
+        ctx.save_for_backward(qkv, cu_seqlens, out, rem)
         ctx.meta = (groups, group_size, head_dim, scale)
         return out, rem
 
     @staticmethod
     def backward(ctx, d_out, d_rem):
-        qkv, cu_seqlens = ctx.saved_tensors
+        from ... import ops
+
+        qkv, cu_seqlens, out, rem = ctx.saved_tensors
         groups, g, d, scale = ctx.meta
-        d_qkv = torch.zeros_like(qkv)
-        bounds = cu_seqlens.tolist()
-        for s, e in zip(bounds[:-1], bounds[1:]):
-            if e <= s:
-                continue
-            with torch.enable_grad():
-                piece = qkv[s:e].detach().requires_grad_(True)
-                v4 = piece.view(e - s, groups, g + 2, d)
-                q = v4[:, :, :g].reshape(e - s, groups * g, d).transpose(0, 1)
-                k = v4[:, :, g].repeat_interleave(g, dim=1).transpose(0, 1)
-                v = v4[:, :, g + 1].repeat_interleave(g, dim=1).transpose(0, 1)
-                out, rem = stickbreaking_attention(q, k, v, scale)  # [h, n, d], [h, n]
-                out = out.transpose(0, 1).reshape(e - s, groups * g * d)
-                torch.autograd.backward([out, rem], [d_out[s:e].to(out.dtype), d_rem[:, s:e].to(rem.dtype)])
-            d_qkv[s:e] = piece.grad
+        if d_rem is None:
+            d_rem = torch.zeros_like(rem)
+        d_qkv = ops.native().sb_attn_bwd(d_out.contiguous(), d_rem.float().contiguous(), qkv, out, rem, cu_seqlens, groups, g, d, scale,
+                                         ops.status_word(qkv.device))
         return d_qkv, None, None, None, None, None
 
 

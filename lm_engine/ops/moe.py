@@ -7,7 +7,7 @@ routing outcome (no host synchronisation). One layer is
 
     gather rows -> grouped GEMM (c_fc) -> SwiGLU -> grouped GEMM (c_proj) -> weighted combine per token
 
-with an explicit backward that recomputes the gathered input and the activation instead of saving them. Under
+with an explicit backward that recomputes the activation from the saved c_fc output instead of saving it. Under
 expert parallelism the same kernels read token rows / expert outputs directly from the peers' buffers (see
 :mod:`lm_engine.parallel.expert_parallel`).
 """
@@ -131,19 +131,19 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         te = layout.tile_expert  # tiles past the used rows carry num_experts and are skipped by every kernel below
         xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * top_k, top_k, x, te, num_experts)
         fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
-        del xg
         act = C.swiglu_fwd(fc, te, num_experts)
         y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
         del act
         weights32 = router_weights.reshape(-1).float().contiguous()
         out = C.moe_combine([y.data_ptr()], layout.dest_row, weights32, T, H, top_k, layout.rows, x)
-        ctx.save_for_backward(x, w_fc, w_proj, weights32, fc, layout.dest_row, layout.src_entry, layout.tile_expert, layout.padded_offsets)
+        # the gathered rows are kept for the weight gradient of c_fc (one [rows, H] buffer per layer instead of a second gather)
+        ctx.save_for_backward(x, w_fc, w_proj, weights32, fc, layout.dest_row, layout.src_entry, layout.tile_expert, layout.padded_offsets, xg)
         ctx.meta = (num_experts, top_k, layout.rows, router_weights.dtype, router_weights.shape)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        x, w_fc, w_proj, weights32, fc, dest_row, src_entry, tile_expert, padded_offsets = ctx.saved_tensors
+        x, w_fc, w_proj, weights32, fc, dest_row, src_entry, tile_expert, padded_offsets, xg = ctx.saved_tensors
         num_experts, top_k, rows, w_dtype, w_shape = ctx.meta
         C = native()
         st = status_word(x.device)
@@ -159,9 +159,7 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         d_weights = per_entry.view(w_shape).to(w_dtype)
         g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
         del dyg, act
-        xg = C.moe_gather([x.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
         g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
-        del xg
         dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)  # [rows, H] = dfc @ w_fc[e]
         dx = C.moe_combine([dxg.data_ptr()], dest_row, None, T, H, top_k, rows, x)
         return dx, g_fc, g_proj, d_weights, None, None, None
