@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(SB_BWD_THREADS, 1)
             const int kv = kv0 + c * 32 + e + u;
             const bool valid = row_valid && kv < q_local;
             const float ez = fast_exp2(fminf(__uint_as_float(sv[e + u]) * scale_log2, 86.f));  // exp(z), z clamped at 60
-            const float inv = __frcp_rn(1.f + ez);                                             // 1 - sigma
+            const float inv = fast_rcp(1.f + ez);                                             // 1 - sigma
             const float sig = ez * inv;
             const float a = valid ? sig * prod : 0.f;
             const float g = a * (__uint_as_float(dpv[e + u]) - d_rem);

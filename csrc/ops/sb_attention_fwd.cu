@@ -7,8 +7,8 @@
 // one strided TMA map, one CTA per 128 query rows of one document and one head, warp 0 = TMA, warp 1 = tcgen05 MMA
 // (S = Q K^T into two TMEM buffers, O += A V into a third), warps 2-5 = one thread per query row. The differences:
 //   * key tiles are visited from the diagonal towards the start of the document, because the weight of key j depends on
-//     all keys between j and i: every row keeps c = sum of softplus(z_ik) over the keys seen so far, and
-//     A[i, j] = exp(z_ij - softplus(z_ij) - c) before c grows by softplus(z_ij);
+//     all keys between j and i: every row keeps the product of (1 - sigma(z_ik)) over the keys seen so far, and
+//     A[i, j] = sigma(z_ij) * product before the product shrinks by (1 - sigma(z_ij));
 //   * the weights are absolute (no normalisation), so O is never rescaled and accumulates across all tiles;
 //   * the kernel returns rem (fp32 [heads, T]) instead of a log-sum-exp.
 #include "../common/launch.h"
@@ -198,7 +198,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     const int r = q * 32 + lane;         // row inside the tile
     const int q_local = q0 + r;          // row inside the document
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    float c_run = 0.f;    // sum of softplus(z) over the keys already visited (those between the current key and the query)
+    float keep = 1.f;     // product of (1 - sigmoid(z)) over the keys already visited (those between the current key and the query)
+    const float scale_log2 = scale * 1.4426950408889634f;
     float a_total = 0.f;  // sum of the weights
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -224,11 +225,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
         for (int h = 1; h >= 0; --h) {  // the later key first
           const int kv = kv0 + c + h;
-          const float z = __uint_as_float(s[c + h]) * scale;
           if (kv < q_local && kv < doc_len) {
-            const float sp = z > 15.f ? z : __logf(1.f + __expf(z));  // softplus
-            w[h] = __expf(z - sp - c_run);
-            c_run += sp;
+            // sigma = e^z / (1 + e^z), 1 - sigma = 1 / (1 + e^z): one exponential and one reciprocal per element; the
+            // product of (1 - sigma) over the keys already visited is carried in the linear domain (z clamped at 60)
+            const float ez = fast_exp2(fminf(__uint_as_float(s[c + h]) * scale_log2, 86.f));
+            const float inv = fast_rcp(1.f + ez);
+            w[h] = ez * inv * keep;
+            keep *= inv;
           } else {
             w[h] = 0.f;
           }

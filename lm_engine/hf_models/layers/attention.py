@@ -114,7 +114,41 @@ class Attention(nn.Module):
         return wait_for_ACT(out, wait_in_forward=False, wait_in_backward=True)
 
     # -------------------------------------------------------------- padded: [b, s, *]
+    def _padded_on_varlen_kernels(self, qkv: torch.Tensor, ctx: SequenceContext) -> torch.Tensor | None:
+        """A padded batch without a KV cache on the packed-sequence kernels: rotate the fused buffer in place of splitting
+        it, drop the padding rows (``pack_sequence``), run the variable-length attention kernels, and put the rows back
+        (the role of unpad -> flash_attn_varlen -> pad in lm_engine/hf_models/modeling_utils/sequence_mixer_blocks/
+        attention.py of the reference). Returns None when the batch does not qualify."""
+        from ...ops.attention import _native_attention_ok
+        from ...ops.sequence import compute_cu_seqlens_and_max_seqlen_from_attention_mask, pack_sequence, unpack_sequence
+
+        b, s, width = qkv.shape
+        g, hkv, d = self.group_size, self.num_key_value_heads, self.head_dim
+        if not (self.causal and self._use_flash() and _native_attention_ok(qkv, d)):
+            return None
+        if self.training and self.softmax_dropout_p > 0:
+            return None
+        flat = qkv.reshape(b * s, width)
+        if self.position_embedding_type == "rope":
+            cos_h, sin_h = ctx.rope_half_tables
+            position_ids = ctx.position_ids.expand(b, s).reshape(-1)
+            flat = ops.rope_fused_qkv(flat, cos_h, sin_h, position_ids, hkv, g, d, cos_h.shape[-1] * 2)
+        mask = ctx.attention_mask
+        if mask is None:
+            cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=qkv.device)
+            out = attention_fused_qkv(flat, cu, s, hkv, g, d, self.softmax_scale, True, 0.0)
+            return out.view(b, s, hkv * g * d)
+        cu, max_seqlen = compute_cu_seqlens_and_max_seqlen_from_attention_mask(mask)
+        side = "left" if bool(mask[:, -1].all()) else "right"  # a batch is padded on one side as a whole
+        packed = pack_sequence(flat.view(b, s, width), cu, side)
+        out = attention_fused_qkv(packed, cu, max_seqlen, hkv, g, d, self.softmax_scale, True, 0.0)
+        return unpack_sequence(out, cu, (b, s, hkv * g * d), side)
+
     def _forward_padded(self, qkv: torch.Tensor, ctx: SequenceContext, past_key_values) -> torch.Tensor:
+        if past_key_values is None and qkv.is_cuda:
+            out = self._padded_on_varlen_kernels(qkv, ctx)
+            if out is not None:
+                return out
         b, s, _ = qkv.shape
         g, hkv, d = self.group_size, self.num_key_value_heads, self.head_dim
         v5 = qkv.view(b, s, hkv, g + 2, d)

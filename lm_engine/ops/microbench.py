@@ -100,6 +100,14 @@ def bench_attention(args) -> None:
                 record["flash_attn2_bwd_ms"], record["flash_attn2_bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
             except ImportError:
                 pass
+        if hasattr(C, "sb_attn_bwd") and not args.profile:
+            # stick-breaking attention on the same buffer (strictly causal, same matrix products as the softmax kernels)
+            sb_out, sb_rem = C.sb_attn_fwd(qkv, cu, groups, qpg, d, d**-0.5, st)
+            d_rem = torch.randn_like(sb_rem)
+            ms = _time(lambda: C.sb_attn_fwd(qkv, cu, groups, qpg, d, d**-0.5, st), args.iters, args.warmup, flush)
+            record["stickbreaking_fwd_ms"], record["stickbreaking_fwd_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+            ms = _time(lambda: C.sb_attn_bwd(dout, d_rem, qkv, sb_out, sb_rem, cu, groups, qpg, d, d**-0.5, st), args.iters, args.warmup, flush)
+            record["stickbreaking_bwd_ms"], record["stickbreaking_bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
         record["status"] = int(st.item())
         _emit(record)
 

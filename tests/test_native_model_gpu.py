@@ -104,3 +104,35 @@ def test_native_training_curve_tracks_fp32_reference():
     for a, b in zip(curve, ref_curve):
         assert abs(a - b) < 3e-2 * abs(b), (curve, ref_curve)
     assert all(abs(v) < 20 for v in curve)
+
+
+@pytest.mark.parametrize("side", ["none", "left", "right"])
+def test_padded_batches_run_on_the_varlen_kernels(side):
+    """A padded [batch, seq] batch (no mask, left padding, right padding) through pack -> variable-length attention
+    kernels -> unpack gives the logits of the masked dense attention at every real position."""
+    from lm_engine.hf_models import GPTBaseForCausalLM
+    from lm_engine.kernels import enable_kernels
+
+    torch.manual_seed(0)
+    device = torch.device("cuda", 0)
+    model = GPTBaseForCausalLM(_config(), use_padding_free_transformer=False).to(device=device, dtype=torch.bfloat16).eval()
+    batch, seq = 3, 200
+    ids = torch.randint(0, 1024, (batch, seq), device=device)
+    lengths = [200, 131, 64]
+    mask = None
+    if side != "none":
+        mask = torch.zeros(batch, seq, dtype=torch.long, device=device)
+        for i, n in enumerate(lengths):
+            if side == "left":
+                mask[i, seq - n:] = 1
+            else:
+                mask[i, :n] = 1
+    with torch.no_grad():
+        ref = model(input_ids=ids, attention_mask=mask).logits.float()
+        from lm_engine.enums import Kernel
+
+        with enable_kernels([k for k in _all_kernels() if k != Kernel.fused_linear_cross_entropy_cute]):
+            got = model(input_ids=ids, attention_mask=mask).logits.float()
+    keep = torch.ones(batch, seq, dtype=torch.bool, device=device) if mask is None else mask.bool()
+    err = (got - ref)[keep].abs().max().item()
+    assert err < 0.1 * ref[keep].abs().max().item() + 0.05, err
