@@ -176,9 +176,11 @@ def run_native(cli) -> dict:
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
     expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
-    # expert row buffers: twice a rank's balanced share instead of the worst case (every entry of the group on one rank);
-    # the number of entries this bound dropped is reported and must be 0 for the run to count as dropless
-    extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": 2.0} if expert_parallel > 1 else None
+    # expert row buffers: up to four times a rank's balanced share (the worst case, every entry of the group on one rank,
+    # for 2 and 4 ranks; half of it for 8); the number of entries this bound dropped is reported and must be 0 for the
+    # run to count as dropless
+    capacity = float(min(expert_parallel, 4))
+    extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else None
     args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
 
     init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel)
@@ -283,7 +285,7 @@ def run_native(cli) -> dict:
 
         dropped = torch.tensor([dropped_entries(device)], dtype=torch.int64, device=device)
         torch.distributed.all_reduce(dropped)
-        result["config"]["expert_capacity_factor"] = 2.0
+        result["config"]["expert_capacity_factor"] = capacity
         result["config"]["expert_entries_dropped"] = int(dropped.item())
     if e2e is not None:
         result["e2e"] = e2e
