@@ -121,28 +121,166 @@ __device__ __forceinline__ void store_row(uint32_t t_row, void* Cv, long long ro
 
 // ----------------------------------------------------------------------------------------------------------------
 // C[rows, N] = A[rows, K] * op(W[expert])
-template <int B_MN>
+// With DISPATCH the A rows do not exist yet when the kernel starts: the first `copy_ctas` CTAs gather them, 128-row tile by
+// tile, from the token buffers of all ranks (peer pointers; bulk copies peer -> shared-memory ring -> this GPU's A buffer)
+// and publish one ready flag per tile; the GEMM CTAs visit the tiles in the same order and wait for the flag of a tile
+// before their first TMA load of it, so the transfer of tile t + 1 runs under the MMAs of tile t. All CTAs are resident
+// (one per SM), every wait is bounded.
+struct DispatchArgs {
+  const void* src[16];     // per rank: [tokens, K] bf16 token rows
+  const int* src_entry;    // per row: global entry (rank * entries_per_rank + token * k + slot) or -1 for a padding row
+  void* a_rows;            // [max_m_tiles * 128, K] bf16: the gathered rows (kept by the caller for the weight gradient)
+  int* ready;              // one flag per tile, zero at launch
+  int entries_per_rank, k, copy_ctas, epoch;
+};
+
+constexpr uint32_t kReadySpinLimit = 1u << 24;  // x ~100 ns sleep: a couple of seconds
+constexpr int RING_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+
+__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_store_row(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+// One warp of a gather CTA. Lane l owns two row slots of the shared-memory ring and its own mbarriers, and runs its own
+// two-deep pipeline over the rows l, l + rb, l + 2 rb, ... of every tile this CTA gathers: the load of its next row is in
+// flight while the current one is stored, so about 2 * rb rows per CTA are in flight at any time.
+__device__ void gather_tiles(uint8_t* ring, volatile int* abort_flag, const DispatchArgs& da, const int* tile_expert, int max_m_tiles,
+                             int num_experts, int K, int* status) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t row_bytes = (uint32_t)K * 2;
+  const int rb = min(32, (int)((RING_BYTES - row_bytes - 512) / 2 / row_bytes));  // lanes that take rows
+  uint8_t* zero = ring + (size_t)2 * rb * row_bytes;  // one row of zeros: the source of the padding rows
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zero + row_bytes);  // [2][rb]
+  const bool active = lane < rb;
+  if (active) {
+    mbar_init(&bars[lane], 1);
+    mbar_init(&bars[rb + lane], 1);
+  }
+  if (lane == 0) *abort_flag = 0;
+  fence_barrier_init();
+  for (uint32_t i = lane * 16; i < row_bytes; i += 32 * 16) *reinterpret_cast<uint4*>(zero + i) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  __syncwarp();
+  uint32_t parity[2] = {0, 0};
+  uint32_t slot = 0;     // slot of the row whose load is in flight (or that is a padding row)
+  bool ok = true;
+  const int per_lane = (BM - lane + rb - 1) / rb;  // rows of a tile that fall to this lane
+
+  // first used tile at or after `mt` in this CTA's sequence (max_m_tiles if none)
+  auto next_tile = [&](int mt) -> int {
+    for (; mt < max_m_tiles; mt += da.copy_ctas) {
+      const int te = tile_expert[mt];
+      if (te >= 0 && te < num_experts) break;
+    }
+    return mt;
+  };
+  // start the load of row (mt, r) into `s`; returns the entry (-1: padding row, nothing to load)
+  auto start_row = [&](int mt, int r, uint32_t s) -> int {
+    const int e = da.src_entry[mt * BM + r];
+    if (e >= 0) {
+      tma_store_wait_read<0>();  // the store that last used this slot (the previous row of this lane) has left shared memory
+      const int rank = e / da.entries_per_rank;
+      const int token = (e - rank * da.entries_per_rank) / da.k;
+      uint64_t* bar = &bars[s * rb + lane];
+      mbar_arrive_expect_tx(bar, row_bytes);
+      bulk_load_row(ring + (size_t)(s * rb + lane) * row_bytes, reinterpret_cast<const uint8_t*>(da.src[rank]) + (size_t)token * row_bytes, row_bytes, bar);
+    }
+    return e;
+  };
+
+  int mt = next_tile(blockIdx.x);
+  int e_cur = -1;
+  if (mt < max_m_tiles && active) e_cur = start_row(mt, lane, slot);
+  while (mt < max_m_tiles) {
+    const int mt_next = next_tile(mt + da.copy_ctas);
+    uint8_t* dst_tile = reinterpret_cast<uint8_t*>(da.a_rows) + (size_t)mt * BM * row_bytes;
+    if (active) {
+      for (int jrow = 0; jrow < per_lane; ++jrow) {
+        const int r = lane + jrow * rb;
+        // the next row of this lane: in this tile, or the first one of the next tile
+        int e_next = -1;
+        const bool more = jrow + 1 < per_lane;
+        if (more) e_next = start_row(mt, r + rb, slot ^ 1);
+        else if (mt_next < max_m_tiles) e_next = start_row(mt_next, lane, slot ^ 1);
+        if (e_cur >= 0) {
+          if (ok && !mbar_wait(&bars[slot * rb + lane], parity[slot], abort_flag)) ok = false;
+          parity[slot] ^= 1;
+        }
+        if (ok) bulk_store_row(dst_tile + (size_t)r * row_bytes, e_cur >= 0 ? ring + (size_t)(slot * rb + lane) * row_bytes : zero, row_bytes);
+        tma_store_commit();
+        e_cur = e_next;
+        slot ^= 1;
+      }
+      tma_store_wait<0>();  // this lane's rows of the tile are in this GPU's memory (its next load stays in flight)
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    if (lane == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(da.ready + mt), "r"(da.epoch) : "memory");
+    }
+    mt = mt_next;
+  }
+  if (!ok) {
+    if (lane == 0) raise_status(status, kStatusWaitTimeoutPeer, abort_flag);
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // bounded grace for copies still in flight
+    tma_store_wait<0>();
+  }
+}
+
+template <int B_MN, bool DISPATCH>
 __global__ void __launch_bounds__(THREADS, 1)
     grouped_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         __nv_bfloat16* __restrict__ C, const int* __restrict__ tile_expert, int max_m_tiles,
-                        int num_experts, int N, int K, long long ldc, int* status) {
+                        int num_experts, int N, int K, long long ldc, int* status, const __grid_constant__ DispatchArgs da) {
   extern __shared__ uint8_t smem_raw[];
   const Smem s = carve(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int copy_ctas = DISPATCH ? da.copy_ctas : 0;
+  if (DISPATCH && (int)blockIdx.x < copy_ctas) {
+    if (warp == 0) gather_tiles(s.sA, s.abort_flag, da, tile_expert, max_m_tiles, num_experts, K, status);
+    return;
+  }
   init_common(s, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   const int n_tiles = (N + BN - 1) / BN;
   const int k_blocks = (K + BK - 1) / BK;
   const int total = max_m_tiles * n_tiles;
+  const int first_tile = (int)blockIdx.x - copy_ctas, tile_step = (int)gridDim.x - copy_ctas;
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      int ready_mt = -1;
+      for (int tile = first_tile; tile < total && ok; tile += tile_step) {
         const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
         const int e = tile_expert[mt];
         if (e < 0 || e >= num_experts) continue;
+        if (DISPATCH && mt != ready_mt) {
+          // the rows of this tile are being gathered by another CTA: wait for its flag, bounded
+          uint32_t spins = 0;
+          int seen;
+          do {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(da.ready + mt) : "memory");
+            if (seen == da.epoch) break;
+            __nanosleep(100);
+          } while (++spins < kReadySpinLimit && !*s.abort_flag);
+          if (seen != da.epoch) {
+            raise_status(status, kStatusWaitTimeoutPeer, s.abort_flag);
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");  // the TMA loads below must see the rows written by bulk copies
+          ready_mt = mt;
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(&s.empty[st], ph ^ 1, s.abort_flag)) {
@@ -169,7 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, B_MN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < total && ok; tile += tile_step) {
         const int mt = tile / n_tiles;
         const int e = tile_expert[mt];
         if (e < 0 || e >= num_experts) continue;
@@ -206,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   } else {
     const int q = warp & 3;
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    for (int tile = first_tile; tile < total; tile += tile_step) {
       const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
       const int e = tile_expert[mt];
       if (e < 0 || e >= num_experts) continue;
@@ -364,19 +502,61 @@ void grouped_rows_gemm(const void* A, long long lda, const void* W, void* C, lon
   if (w_mn) {
     // W[e] is [K, N] row-major: N contiguous -> MN-major B operand
     const CUtensorMap tmB = make_tensor_map_3d_b16(W, N, K, num_experts, N, (uint64_t)N * K, 64, BK, 1);
-    static bool once = (configure(grouped_rows_kernel<1>), true);
+    static bool once = (configure(grouped_rows_kernel<1, false>), true);
     (void)once;
-    grouped_rows_kernel<1><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
-                                                                  max_m_tiles, num_experts, N, K, ldc, status);
+    grouped_rows_kernel<1, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
+                                                                         max_m_tiles, num_experts, N, K, ldc, status, DispatchArgs{});
   } else {
     const CUtensorMap tmB = make_tensor_map_3d_b16(W, K, N, num_experts, K, (uint64_t)N * K, BK, BN, 1);
-    static bool once = (configure(grouped_rows_kernel<0>), true);
+    static bool once = (configure(grouped_rows_kernel<0, false>), true);
     (void)once;
-    grouped_rows_kernel<0><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
-                                                                  max_m_tiles, num_experts, N, K, ldc, status);
+    grouped_rows_kernel<0, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
+                                                                         max_m_tiles, num_experts, N, K, ldc, status, DispatchArgs{});
   }
   count_launch();
   check_cuda(cudaGetLastError(), "grouped_rows_gemm launch");
+}
+
+// The same product with the A rows gathered inside the kernel (see DispatchArgs): `src_ptrs[r]` is rank r's [tokens, K]
+// bf16 token buffer (this GPU's own buffer or a peer mapping), `src_entry` names the (rank, token) of every row, `a_rows`
+// receives the gathered rows, `ready` is an int32 buffer of max_m_tiles zeros.
+void grouped_rows_dispatch_gemm(const void* const* src_ptrs, int num_ranks, const int* src_entry, int entries_per_rank, int k, void* a_rows,
+                                int* ready, int copy_ctas, const void* W, void* C, long long ldc, const int* tile_expert, int max_m_tiles,
+                                int num_experts, int N, int K, bool w_mn, int* status, cudaStream_t stream) {
+  if (max_m_tiles <= 0 || N <= 0 || K <= 0) return;
+  if (num_ranks < 1 || num_ranks > 16) throw std::runtime_error("grouped_rows_dispatch: between 1 and 16 source buffers");
+  if ((K * 2) % 16 != 0 || K * 2 > 16384) throw std::runtime_error("grouped_rows_dispatch: row size must be a multiple of 16 bytes, at most 16 KB");
+  const CUtensorMap tmA = make_tensor_map_2d_b16(a_rows, K, (uint64_t)max_m_tiles * BM, K, BK, BM);
+  const int total = max_m_tiles * ((N + BN - 1) / BN);
+  const int sms = sm_count();
+  if (copy_ctas < 1) copy_ctas = 1;
+  if (copy_ctas > sms / 2) copy_ctas = sms / 2;
+  int grid = sms;  // every CTA must be resident: gather and GEMM CTAs wait on one another
+  if (total + copy_ctas < grid) grid = total + copy_ctas;
+  DispatchArgs da = {};
+  for (int r = 0; r < num_ranks; ++r) da.src[r] = src_ptrs[r];
+  da.src_entry = src_entry;
+  da.a_rows = a_rows;
+  da.ready = ready;
+  da.entries_per_rank = entries_per_rank;
+  da.k = k;
+  da.copy_ctas = copy_ctas;
+  da.epoch = 1;
+  if (w_mn) {
+    const CUtensorMap tmB = make_tensor_map_3d_b16(W, N, K, num_experts, N, (uint64_t)N * K, 64, BK, 1);
+    static bool once = (configure(grouped_rows_kernel<1, true>), true);
+    (void)once;
+    grouped_rows_kernel<1, true><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
+                                                                        max_m_tiles, num_experts, N, K, ldc, status, da);
+  } else {
+    const CUtensorMap tmB = make_tensor_map_3d_b16(W, K, N, num_experts, K, (uint64_t)N * K, BK, BN, 1);
+    static bool once = (configure(grouped_rows_kernel<0, true>), true);
+    (void)once;
+    grouped_rows_kernel<0, true><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(C), tile_expert,
+                                                                        max_m_tiles, num_experts, N, K, ldc, status, da);
+  }
+  count_launch();
+  check_cuda(cudaGetLastError(), "grouped_rows_dispatch_gemm launch");
 }
 
 // dY: [rows, Nw] bf16, X: [rows, Kw] bf16 (both contiguous grouped buffers), dW: [E, Nw, Kw] fp32.

@@ -17,6 +17,9 @@ namespace b200 {
 
 void grouped_rows_gemm(const void* A, long long lda, const void* W, void* C, long long ldc, const int* tile_expert,
                        int max_m_tiles, int num_experts, int N, int K, bool w_mn, int* status, cudaStream_t stream);
+void grouped_rows_dispatch_gemm(const void* const* src_ptrs, int num_ranks, const int* src_entry, int entries_per_rank, int k, void* a_rows,
+                                int* ready, int copy_ctas, const void* W, void* C, long long ldc, const int* tile_expert, int max_m_tiles,
+                                int num_experts, int N, int K, bool w_mn, int* status, cudaStream_t stream);
 void grouped_wgrad_gemm(const void* dY, const void* X, float* dW, const int* padded_offsets, long long total_rows,
                         int num_experts, int Nw, int Kw, bool accumulate, int* status, cudaStream_t stream);
 
@@ -323,6 +326,40 @@ Tensor grouped_rows(const Tensor& a, const Tensor& w, const Tensor& tile_expert,
   return out;
 }
 
+// Dispatch fused into the grouped GEMM: the rows named by `src_entry` are pulled from the per-rank token buffers by gather CTAs
+// of the GEMM kernel itself, tile by tile, while the other CTAs multiply the tiles that have arrived.
+// -> (gathered rows [rows, K], out [rows, N]); `out` may be given (for instance a view of symmetric memory).
+std::vector<Tensor> grouped_rows_dispatch(const std::vector<int64_t>& src_ptrs, const Tensor& src_entry, int64_t entries_per_rank, int64_t k,
+                                          const Tensor& w, const Tensor& tile_expert, bool w_mn, const c10::optional<Tensor>& status,
+                                          int64_t copy_ctas, const c10::optional<Tensor>& out_buffer) {
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 3, "w: contiguous bf16 [E, ., .]");
+  TORCH_CHECK(src_entry.is_cuda() && src_entry.scalar_type() == torch::kInt32 && src_entry.is_contiguous() && src_entry.numel() % 128 == 0, "src_entry: int32, one per row, 128-row tiles");
+  TORCH_CHECK(src_ptrs.size() >= 1 && src_ptrs.size() <= MAX_RANKS, "between 1 and 16 source buffers");
+  const int64_t rows = src_entry.numel();
+  const int64_t K = w_mn ? w.size(1) : w.size(2);
+  const int64_t N = w_mn ? w.size(2) : w.size(1);
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0 && K * 2 <= 16384, "sizes must be multiples of 8, rows at most 16 KB");
+  const int64_t tiles = rows / 128;
+  TORCH_CHECK(tile_expert.scalar_type() == torch::kInt32 && tile_expert.numel() >= tiles, "tile_expert: int32, one per tile");
+  const c10::cuda::CUDAGuard guard(w.device());
+  Tensor a_rows = torch::empty({rows, K}, w.options());
+  Tensor out;
+  if (out_buffer.has_value()) {
+    out = *out_buffer;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.dim() == 2 && out.size(0) == rows && out.size(1) == N,
+                "out: contiguous bf16 [rows, N]");
+  } else {
+    out = torch::empty({rows, N}, w.options());
+  }
+  Tensor ready = torch::zeros({tiles}, src_entry.options());
+  const void* ptrs[MAX_RANKS];
+  for (size_t i = 0; i < src_ptrs.size(); ++i) ptrs[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+  grouped_rows_dispatch_gemm(ptrs, (int)src_ptrs.size(), src_entry.data_ptr<int>(), (int)entries_per_rank, (int)k, a_rows.data_ptr(),
+                             ready.data_ptr<int>(), (int)copy_ctas, w.data_ptr(), out.data_ptr(), N, tile_expert.data_ptr<int>(), (int)tiles,
+                             (int)w.size(0), (int)N, (int)K, w_mn, status_of(status), cur_stream());
+  return {a_rows, out};
+}
+
 // dw[E, Nw, Kw] (+)= dy[rows, Nw]^T x[rows, Kw] per expert row range
 void grouped_wgrad(const Tensor& dy, const Tensor& x, Tensor& dw, const Tensor& padded_offsets, bool accumulate,
                    const c10::optional<Tensor>& status) {
@@ -348,6 +385,9 @@ void register_moe(pybind11::module_& m) {
         pybind11::arg("tile_owner") = pybind11::none(), pybind11::arg("owners") = 0);
   m.def("grouped_rows", &grouped_rows, pybind11::arg("a"), pybind11::arg("w"), pybind11::arg("tile_expert"), pybind11::arg("w_mn"),
         pybind11::arg("status"), pybind11::arg("out") = pybind11::none());
+  m.def("grouped_rows_dispatch", &grouped_rows_dispatch, pybind11::arg("src_ptrs"), pybind11::arg("src_entry"), pybind11::arg("entries_per_rank"),
+        pybind11::arg("k"), pybind11::arg("w"), pybind11::arg("tile_expert"), pybind11::arg("w_mn"), pybind11::arg("status"),
+        pybind11::arg("copy_ctas") = 16, pybind11::arg("out") = pybind11::none());
   m.def("grouped_wgrad", &grouped_wgrad);
 }
 

@@ -98,6 +98,25 @@ def native_moe_ok(x: torch.Tensor, activation_function: str) -> bool:
             and x.shape[-1] % 8 == 0 and hasattr(native(), "grouped_rows"))
 
 
+def fused_dispatch_enabled(C) -> bool:
+    """Gather inside the grouped GEMM kernel (on unless ``LM_ENGINE_MOE_FUSED_DISPATCH=0``)."""
+    import os
+
+    return hasattr(C, "grouped_rows_dispatch") and os.environ.get("LM_ENGINE_MOE_FUSED_DISPATCH", "1") != "0"
+
+
+def gather_then_grouped_rows(C, src_ptrs, src_entry, hidden, entries_per_rank, top_k, like, tile_expert, owners, weight, w_mn, st,
+                             copy_ctas: int = 8, out=None):
+    """``rows = gather(src)[src_entry]; out = rows @ op(weight[expert of the tile])`` -> ``(rows, out)``. One kernel when
+    the fused dispatch is available (gather CTAs feed the GEMM CTAs tile by tile), otherwise the gather kernel followed by
+    the grouped GEMM."""
+    # worth it when rows cross NVLink (the transfer hides under the MMAs); a local gather runs at memory bandwidth on its own
+    if len(src_ptrs) > 1 and fused_dispatch_enabled(C) and hidden * 2 <= 16384:
+        return C.grouped_rows_dispatch(src_ptrs, src_entry, entries_per_rank, top_k, weight, tile_expert, w_mn, st, copy_ctas, out)
+    rows = C.moe_gather(src_ptrs, [], src_entry, hidden, entries_per_rank, top_k, like, tile_expert, owners)
+    return rows, C.grouped_rows(rows, weight, tile_expert, w_mn, st, out)
+
+
 def _wgrad(C, dy, x, weight, padded_offsets, st):
     target = _weight_grad_target(weight)
     if target is not None:
@@ -129,8 +148,7 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         T, H = x.shape
         layout = build_grouped_layout(selected_experts.reshape(-1), num_experts)
         te = layout.tile_expert  # tiles past the used rows carry num_experts and are skipped by every kernel below
-        xg = C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * top_k, top_k, x, te, num_experts)
-        fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
+        xg, fc = gather_then_grouped_rows(C, [x.data_ptr()], layout.src_entry, H, T * top_k, top_k, x, te, num_experts, w_fc, False, st)
         act = C.swiglu_fwd(fc, te, num_experts)
         y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
         del act
@@ -152,8 +170,7 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         entries = T * top_k
 
         # dY of the second GEMM without the routing weight, and the activation recomputed from the saved c_fc output
-        dyg = C.moe_gather([dout.data_ptr()], [], src_entry, H, entries, top_k, x, tile_expert, num_experts)
-        dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)  # [rows, I] = dyg @ w_proj[e]
+        dyg, dact = gather_then_grouped_rows(C, [dout.data_ptr()], src_entry, H, entries, top_k, x, tile_expert, num_experts, w_proj, True, st)  # [rows, I] = dyg @ w_proj[e]
         act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights32, rows, tile_expert, num_experts)
         del dact
         d_weights = per_entry.view(w_shape).to(w_dtype)

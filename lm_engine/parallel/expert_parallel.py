@@ -21,11 +21,13 @@ local experts -> reduce-scatter over the group with the same results, which is w
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
 from .. import ops
-from ..ops.moe import TILE, _wgrad, build_grouped_layout, weighted_swiglu_backward
+from ..ops.moe import TILE, _wgrad, build_grouped_layout, gather_then_grouped_rows, weighted_swiglu_backward
 from ..utils import ProcessGroupManager
 from .symmetric import PeerBuffer, PeerGroup, get_peer_group
 
@@ -35,6 +37,8 @@ _WORKSPACES: dict[int, "_Workspace"] = {}
 # padding); None sizes them for the worst case, in which every entry of the group lands on one rank. Entries beyond the
 # bound are dropped (they contribute nothing to their token) and counted on the device in ``_DROPPED``.
 _CAPACITY_FACTOR: float | None = None
+# CTAs of the fused dispatch + GEMM kernel that pull rows from the peers (each keeps about 190 KB in flight)
+_GATHER_CTAS = int(os.environ.get("LM_ENGINE_MOE_GATHER_CTAS", "32"))
 _DROPPED: dict[torch.device, torch.Tensor] = {}
 
 
@@ -201,8 +205,8 @@ class _ExpertParallelFn(torch.autograd.Function):
         tokens.tensor[: T * H].view(T, H).copy_(x)
         peer.barrier()  # every rank's tokens are readable
         te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
-        xg = C.moe_gather(tokens.ptrs, [], layout.src_entry, H, entries, top_k, x, te, local)  # dispatch: pull rows from their owners
-        fc = C.grouped_rows(xg, w_fc, layout.tile_expert, False, st)
+        # dispatch: rows are pulled from their owners by gather CTAs inside the c_fc GEMM kernel
+        xg, fc = gather_then_grouped_rows(C, tokens.ptrs, layout.src_entry, H, entries, top_k, x, te, local, w_fc, False, st, copy_ctas=_GATHER_CTAS)
         act = C.swiglu_fwd(fc, te, local)
         C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
         del act
@@ -234,8 +238,8 @@ class _ExpertParallelFn(torch.autograd.Function):
         tokens.tensor[: T * H].view(T, H).copy_(dout)
         peer.barrier()
         local = w_fc.shape[0]
-        dyg = C.moe_gather(tokens.ptrs, [], src_entry, H, entries, top_k, x, tile_expert, local)  # output gradients of the rows computed here
-        dact = C.grouped_rows(dyg, w_proj, tile_expert, True, st)
+        # output gradients of the rows computed here, pulled inside the GEMM kernel as in the forward pass
+        dyg, dact = gather_then_grouped_rows(C, tokens.ptrs, src_entry, H, entries, top_k, x, tile_expert, local, w_proj, True, st, copy_ctas=_GATHER_CTAS)
         # gradient of the routing weight of every entry served here (0 elsewhere), sent back to the token owners
         act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights_all, rows, tile_expert, local)
         del dact

@@ -408,3 +408,32 @@ def test_expert_layout_kernels_match_the_sort_based_layout(entries, num_experts,
         assert torch.equal(getattr(got, name).cpu(), getattr(ref, name).cpu()), name
     if capacity is not None:
         assert int(got.dropped.item()) > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("w_mn", [False, True])
+def test_dispatch_fused_into_the_grouped_gemm_matches_gather_then_gemm(w_mn):
+    """Gather CTAs inside the grouped GEMM kernel (two source buffers standing in for two ranks) against the separate
+    gather kernel followed by the grouped GEMM: identical gathered rows, identical products."""
+    from lm_engine import ops
+    from lm_engine.ops.moe import build_grouped_layout
+
+    C = ops.native()
+    st = ops.status_word(torch.device("cuda"))
+    torch.manual_seed(5)
+    tokens, hidden, inter, experts, k = 700, 512, 384, 6, 2
+    bufs = [torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    selected = torch.randint(0, experts, (2 * tokens * k,), device="cuda", dtype=torch.int32)  # entries of both "ranks"
+    layout = build_grouped_layout(selected, experts)
+    w = torch.randn(experts, hidden, inter, device="cuda", dtype=torch.bfloat16) * 0.05 if w_mn else \
+        torch.randn(experts, inter, hidden, device="cuda", dtype=torch.bfloat16) * 0.05
+    ptrs = [b.data_ptr() for b in bufs]
+    rows_ref = C.moe_gather(ptrs, [], layout.src_entry, hidden, tokens * k, k, bufs[0], layout.tile_expert, experts)
+    out_ref = C.grouped_rows(rows_ref, w, layout.tile_expert, w_mn, st)
+    for copy_ctas in (1, 7):
+        rows, out = C.grouped_rows_dispatch(ptrs, layout.src_entry, tokens * k, k, w, layout.tile_expert, w_mn, st, copy_ctas)
+        torch.cuda.synchronize()
+        ops.check_status()
+        used = int(layout.padded_offsets[-1].item())
+        assert torch.equal(rows[:used], rows_ref[:used])
+        assert torch.equal(out[:used], out_ref[:used])
