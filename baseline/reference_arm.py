@@ -30,7 +30,7 @@ def _unavailable(why: str) -> dict:
 def run_reference(cli, spec: dict, repo_root: str):
     ref_root = os.path.join(repo_root, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "lm_engine")):
-        return _unavailable("baseline/_ref is missing: the reference has not been installed (see DESIGN.md section 4)")
+        return _unavailable("baseline/_ref is missing: the reference has not been installed (pip install --no-index --target baseline/_ref of the reference tree)")
     # make sure `import lm_engine` resolves to the reference, never to this repository's package
     sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != os.path.abspath(repo_root)]
     sys.path.insert(0, ref_root)

@@ -33,7 +33,7 @@ DENSE_8B = dict(
     intermediate_size=14336, rope_theta=500000, sequence_length=4096, micro_batch_size=2, gradient_accumulation_steps=16,
 )
 
-# BASELINE config 5: scattered-MoE decoder, 40 experts top-8; experts spread over the GPUs (expert parallel = world size)
+# scattered-MoE decoder, 40 experts top-8; experts spread over the GPUs (expert parallel = world size)
 MOE_40E = dict(
     name="moe-40e-top8-gpt_base",
     vocab_size=49152, hidden_size=1536, num_layers=32, num_attention_heads=24, num_key_value_heads=8,
