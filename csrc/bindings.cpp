@@ -25,6 +25,7 @@ void register_sequence(pybind11::module_& m);
 void register_fp8(pybind11::module_& m);
 void register_recurrent(pybind11::module_& m);
 void register_moe_layout(pybind11::module_& m);
+void register_ssd(pybind11::module_& m);
 }  // namespace b200
 
 namespace {
@@ -336,5 +337,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   b200::register_fp8(m);
   b200::register_recurrent(m);
   b200::register_moe_layout(m);
+  b200::register_ssd(m);
   b200::register_data_helpers(m);
 }

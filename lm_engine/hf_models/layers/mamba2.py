@@ -107,12 +107,19 @@ class Mamba2(nn.Module):
     def _split(self, projected: torch.Tensor):
         return projected.split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)
 
-    def _ssm_inputs(self, xbc: torch.Tensor, dt: torch.Tensor):
+    def _scan_kernel_ok(self, xbc: torch.Tensor) -> bool:
+        from ...enums import Kernel
+        from ...kernels import is_kernel_allowed
+        from ...ops.ssd import ssd_kernel_ok
+
+        return is_kernel_allowed(Kernel.mamba2_ssm) and ssd_kernel_ok(xbc.new_empty(0, self.head_dim), self.ssm_state_size)
+
+    def _ssm_inputs(self, xbc: torch.Tensor, dt: torch.Tensor, repeat_groups: bool = True):
         gn = self.n_groups * self.ssm_state_size
         x, b, c = xbc.split([self.intermediate_size, gn, gn], dim=-1)
         lead = x.shape[:-1]
         x = x.reshape(*lead, self.num_heads, self.head_dim)
-        rep = self.num_heads // self.n_groups
+        rep = self.num_heads // self.n_groups if repeat_groups else 1
         b = b.reshape(*lead, self.n_groups, self.ssm_state_size).repeat_interleave(rep, dim=-2)
         c = c.reshape(*lead, self.n_groups, self.ssm_state_size).repeat_interleave(rep, dim=-2)
         dt = F.softplus(dt.float() + self.dt_bias.float())
@@ -140,9 +147,16 @@ class Mamba2(nn.Module):
             xbc_act = self.activation(conv_out.transpose(1, 2))
         if mask is not None:
             xbc_act = xbc_act * mask[..., None].to(xbc_act.dtype)
-        x, b, c, dt = self._ssm_inputs(xbc_act, dt)
         A = -torch.exp(self.A_log.float())
-        y, final_state = ssd_chunk_scan(x.float() * dt[..., None], A * dt, b.float(), c.float(), self.chunk_size)
+        if self._scan_kernel_ok(xbc_act):
+            from ...ops.ssd import ssd_scan
+
+            # b and c stay per group: the scan kernel maps heads to groups itself
+            x, b, c, dt = self._ssm_inputs(xbc_act, dt, repeat_groups=False)
+            y, final_state = ssd_scan(x.float() * dt[..., None], A * dt, b, c)
+        else:
+            x, b, c, dt = self._ssm_inputs(xbc_act, dt)
+            y, final_state = ssd_chunk_scan(x.float() * dt[..., None], A * dt, b.float(), c.float(), self.chunk_size)
         y = y + x.float() * self.D.float()[:, None]
         if cache is not None:
             k = self.conv_kernel_size

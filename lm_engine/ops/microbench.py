@@ -166,9 +166,53 @@ def bench_elementwise(args) -> None:
     _emit(dict(op="adamw_step", elements=n, ms=round(ms, 4), gbs=round(n * (4 * 4 + 4 * 4 + 2) / ms / 1e6, 1)))
 
 
+def bench_scans(args) -> None:
+    """State-resident scans: Mamba-2 SSD (against the chunked PyTorch formulation) and the GRU scan."""
+    from ..hf_models.layers.mamba2 import ssd_chunk_scan
+    from .recurrent import recurrent_scan
+    from .ssd import ssd_scan
+
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    B, L, H, G, P, N = 4, 4096, 32, 1, 64, 128
+    x = torch.randn(B, L, H, P, device="cuda", requires_grad=True)
+    a = (-torch.rand(B, L, H, device="cuda") * 0.2).requires_grad_(True)
+    b = (torch.randn(B, L, G, N, device="cuda") * 0.3).requires_grad_(True)
+    c = (torch.randn(B, L, G, N, device="cuda") * 0.3).requires_grad_(True)
+    dy = torch.randn(B, L, H, P, device="cuda")
+
+    def native_step():
+        y, _ = ssd_scan(x, a, b, c)
+        y.backward(dy)
+
+    def torch_step():
+        y, _ = ssd_chunk_scan(x, a, b.repeat_interleave(H // G, dim=2), c.repeat_interleave(H // G, dim=2), 256)
+        y.backward(dy)
+
+    record = dict(op="ssd_scan", batch=B, seq_len=L, heads=H, head_dim=P, state=N)
+    record["fwd_ms"] = round(_time(lambda: ssd_scan(x.detach(), a.detach(), b.detach(), c.detach()), args.iters, args.warmup, flush), 4)
+    record["fwd_bwd_ms"] = round(_time(native_step, args.iters, args.warmup, flush), 4)
+    record["torch_chunked_fwd_bwd_ms"] = round(_time(torch_step, max(2, args.iters // 4), 1, flush), 4)
+    _emit(record)
+
+    n, d = 16, 64
+    tokens = 4 * 4096
+    cu = torch.arange(0, tokens + 1, 4096, dtype=torch.int32, device="cuda")
+    xr = (torch.randn(tokens, 3 * n * d, device="cuda", dtype=torch.bfloat16) * 0.5).requires_grad_(True)
+    wr = (torch.randn(3 * n, d, d, device="cuda") / d**0.5).requires_grad_(True)
+    dout = torch.randn(tokens, n, d, device="cuda", dtype=torch.bfloat16)
+
+    def gru_step():
+        recurrent_scan(xr, wr, cu, n, d, True, None).backward(dout)
+
+    record = dict(op="gru_scan", sequences=4, seq_len=4096, heads=n, head_dim=d)
+    record["fwd_ms"] = round(_time(lambda: recurrent_scan(xr.detach(), wr.detach(), cu, n, d, True, None), args.iters, args.warmup, flush), 4)
+    record["fwd_bwd_ms"] = round(_time(gru_step, args.iters, args.warmup, flush), 4)
+    _emit(record)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("op", choices=["gemm", "attention", "moe", "elementwise"])
+    parser.add_argument("op", choices=["gemm", "attention", "moe", "elementwise", "scans"])
     parser.add_argument("--shapes", nargs="*", help="gemm: MxNxK ...; attention: SEQUENCESxLENGTH ...")
     parser.add_argument("--layouts", nargs="*", default=["nt"], help="gemm: nt (y = x w^T), nn (dgrad), tn (wgrad)")
     parser.add_argument("--variant", default="all", choices=["all", "cta1", "cta_pair"])
@@ -186,7 +230,7 @@ def main() -> None:
     parser.add_argument("--top-k", type=int, default=8)
     parser.add_argument("--vocab", type=int, default=128256)
     args = parser.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "moe": bench_moe, "elementwise": bench_elementwise}[args.op](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "moe": bench_moe, "elementwise": bench_elementwise, "scans": bench_scans}[args.op](args)
 
 
 if __name__ == "__main__":

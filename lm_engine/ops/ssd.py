@@ -1,0 +1,83 @@
+"""Mamba-2 selective state-space recurrence on the state-resident scan kernel of ``csrc/ops/ssd_scan.cu``
+(the role of ``mamba_chunk_scan_combined`` for the reference, lm_engine/hf_models/modeling_utils/sequence_mixer_blocks/
+mamba2.py:461-504 there). ``lm_engine.hf_models.layers.mamba2.ssd_chunk_scan`` is the PyTorch formulation of the same
+function and the fallback.
+
+    h_t = exp(a_t) h_{t-1} + x_t b_t^T,   y_t = h_t c_t        x: [B, L, H, P], a: [B, L, H], b / c: [B, L, G, N]
+
+Forward is one scan; backward is three more scans of the same kernel (the transposed state for dc, the adjoint state
+backwards in time for dx and db) and a reversed cumulative sum for da: ``da_t = <dy_t, y_t> - <x_t, dx_t> + da_{t+1}``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import native, native_available
+
+
+def ssd_kernel_ok(x: torch.Tensor, state_size: int) -> bool:
+    if not (x.is_cuda and native_available() and hasattr(native(), "ssd_scan")):
+        return False
+    p = x.shape[-1]
+    return p % 4 == 0 and state_size % 4 == 0 and p <= 256 and state_size <= 256
+
+
+_SIDE_STREAMS: dict[torch.device, tuple[torch.cuda.Stream, torch.cuda.Stream]] = {}
+
+
+def _side_streams(device: torch.device):
+    if device not in _SIDE_STREAMS:
+        _SIDE_STREAMS[device] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    return _SIDE_STREAMS[device]
+
+
+class _SSDScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, a, b, c, h0):
+        C = native()
+        y, final = C.ssd_scan(x, b, c, a, h0, False)
+        ctx.save_for_backward(x, a, b, c, y, final, h0 if h0 is not None else x.new_empty(0))
+        ctx.has_h0 = h0 is not None
+        return y, final
+
+    @staticmethod
+    def backward(ctx, dy, dfinal):
+        x, a, b, c, y, final, h0 = ctx.saved_tensors
+        C = native()
+        B, L, H, P = x.shape
+        G, N = b.shape[2], b.shape[3]
+        dy = dy.contiguous() if dy is not None else torch.zeros_like(y)
+        h0 = h0 if ctx.has_h0 else None
+        dfinal = None if dfinal is None else dfinal.contiguous()
+        transposed = lambda s: None if s is None else s.transpose(-1, -2).contiguous()
+        # three independent scans of one CTA per (batch, head) each: side streams let them share the SMs
+        main = torch.cuda.current_stream(x.device)
+        side = _side_streams(x.device)
+        h0_t, dfinal_t = transposed(h0), transposed(dfinal)
+        for stream in side:
+            stream.wait_stream(main)
+        with torch.cuda.stream(side[0]):
+            dc_heads, _ = C.ssd_scan(b, x, dy, a, h0_t, False)
+        with torch.cuda.stream(side[1]):
+            db_heads, _ = C.ssd_scan(c, dy, x, a, dfinal_t, True)
+        dx, adjoint0 = C.ssd_scan(dy, c, b, a, dfinal, True)
+        for stream, result in zip(side, (dc_heads, db_heads)):
+            main.wait_stream(stream)
+            result.record_stream(main)
+        r = (dy * y).sum(-1) - (x * dx).sum(-1)
+        da = torch.flip(torch.cumsum(torch.flip(r, dims=[1]), dim=1), dims=[1])
+        if dfinal is not None:
+            da = da + (dfinal * final).sum(dim=(-1, -2))[:, None, :]
+        db = db_heads.view(B, L, G, H // G, N).sum(3)
+        dc = dc_heads.view(B, L, G, H // G, N).sum(3)
+        dh0 = torch.exp(a[:, 0])[..., None, None] * adjoint0 if ctx.has_h0 else None
+        return dx, da, db, dc, dh0
+
+
+def ssd_scan(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+             initial_state: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``x [B, L, H, P]`` (already multiplied by dt), ``a [B, L, H]`` (= A * dt), ``b`` / ``c`` ``[B, L, G, N]`` with
+    ``G`` dividing ``H``. Returns ``(y [B, L, H, P], final_state [B, H, P, N])``, all fp32."""
+    f32 = lambda t: None if t is None else t.float().contiguous()
+    return _SSDScan.apply(f32(x), f32(a), f32(b), f32(c), f32(initial_state))

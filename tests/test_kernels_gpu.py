@@ -437,3 +437,35 @@ def test_dispatch_fused_into_the_grouped_gemm_matches_gather_then_gemm(w_mn):
         used = int(layout.padded_offsets[-1].item())
         assert torch.equal(rows[:used], rows_ref[:used])
         assert torch.equal(out[:used], out_ref[:used])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,groups,head_dim,state", [(4, 1, 64, 128), (6, 2, 32, 16), (2, 2, 64, 64)])
+def test_ssd_scan_matches_the_chunked_formulation(heads, groups, head_dim, state):
+    """The state-resident scan kernel against the chunked PyTorch formulation: outputs, final state and every gradient
+    (x, a, b, c, initial state), with a gradient flowing into the final state as well."""
+    from lm_engine.hf_models.layers.mamba2 import ssd_chunk_scan
+    from lm_engine.ops.ssd import ssd_scan
+
+    torch.manual_seed(1)
+    dev = "cuda"
+    B, L = 2, 150
+    x = torch.randn(B, L, heads, head_dim, device=dev, requires_grad=True)
+    a = (-torch.rand(B, L, heads, device=dev) * 0.5).requires_grad_(True)
+    b = (torch.randn(B, L, groups, state, device=dev) * 0.3).requires_grad_(True)
+    c = (torch.randn(B, L, groups, state, device=dev) * 0.3).requires_grad_(True)
+    h0 = (torch.randn(B, heads, head_dim, state, device=dev) * 0.2).requires_grad_(True)
+    dy = torch.randn(B, L, heads, head_dim, device=dev)
+    dfinal = torch.randn(B, heads, head_dim, state, device=dev) * 0.1
+
+    y, final = ssd_scan(x, a, b, c, h0)
+    torch.autograd.backward([y, final], [dy, dfinal])
+    got = [t.detach().clone() for t in (y, final, x.grad, a.grad, b.grad, c.grad, h0.grad)]
+    for t in (x, a, b, c, h0):
+        t.grad = None
+    rep = heads // groups
+    y_ref, final_ref = ssd_chunk_scan(x, a, b.repeat_interleave(rep, dim=2), c.repeat_interleave(rep, dim=2), 64, initial_state=h0)
+    torch.autograd.backward([y_ref, final_ref], [dy, dfinal])
+    ref = [y_ref.detach(), final_ref.detach(), x.grad, a.grad, b.grad, c.grad, h0.grad]
+    for name, g, r in zip(("y", "final", "dx", "da", "db", "dc", "dh0"), got, ref):
+        assert _rel_err(g, r) < 2e-4, (name, _rel_err(g, r))

@@ -136,3 +136,42 @@ def test_padded_batches_run_on_the_varlen_kernels(side):
     keep = torch.ones(batch, seq, dtype=torch.bool, device=device) if mask is None else mask.bool()
     err = (got - ref)[keep].abs().max().item()
     assert err < 0.1 * ref[keep].abs().max().item() + 0.05, err
+
+
+def test_recurrent_and_state_space_mixers_on_their_scan_kernels():
+    """A model with Mamba-2, GRU and RNN mixers gives the same logits and parameter gradients with the scan kernels
+    (SSD scan, depthwise convolution, GRU / RNN scans) as with the PyTorch formulations of the same layers."""
+    from lm_engine.enums import Kernel
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+    from lm_engine.kernels import enable_kernels
+
+    torch.manual_seed(0)
+    device = torch.device("cuda", 0)
+    mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=256, add_bias=False)
+    config = GPTBaseConfig(
+        vocab_size=512, hidden_size=128, num_layers=3, max_position_embeddings=512, position_embedding_type="nope",
+        normalization_function="rmsnorm",
+        sequence_mixer_blocks=[
+            dict(sequence_mixer_type="mamba2", state_size=64, intermediate_size=256, num_heads=4, conv_kernel_size=4, num_groups=2, chunk_size=64),
+            dict(sequence_mixer_type="gru", state_size=128, num_heads=4, add_bias=False),
+            dict(sequence_mixer_type="rnn", state_size=128, num_heads=2, add_bias=False),
+        ],
+        mlp_blocks=[dict(mlp)] * 3,
+    )
+    model = GPTBaseForCausalLM(config, use_padding_free_transformer=False).to(device)
+    ids = torch.randint(0, 512, (2, 96), device=device)
+
+    def run(kernels):
+        model.zero_grad(set_to_none=True)
+        with enable_kernels(kernels):
+            out = model(input_ids=ids, labels=ids)
+        out.loss.backward()
+        return out.logits.detach().float(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters() if p.grad is not None}
+
+    ref_logits, ref_grads = run([])
+    logits, grads = run([Kernel.mamba2_ssm, Kernel.gru_cute, Kernel.rnn_cute, Kernel.causal_conv1d])
+    assert (logits - ref_logits).abs().max().item() < 2e-3 * ref_logits.abs().max().item() + 1e-4
+    assert set(grads) == set(ref_grads)
+    for name, g in grads.items():
+        r = ref_grads[name]
+        assert (g - r).norm().item() <= 2e-3 * r.norm().item() + 1e-6, name
