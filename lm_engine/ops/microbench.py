@@ -136,6 +136,23 @@ def bench_moe(args) -> None:
     record["wgrad_fc_ms"], record["wgrad_fc_tflops_useful"] = round(ms, 4), round(2.0 * T * k * 2 * I * H / ms / 1e9, 1)
     ms = _time(lambda: C.moe_gather([x.data_ptr()], [], layout.src_entry, H, T * k, k, x), args.iters, args.warmup, flush)
     record["gather_ms"], record["gather_gbs"] = round(ms, 4), round(2.0 * layout.rows * H * 2 / ms / 1e6, 1)
+    if hasattr(C, "grouped_rows_dispatch") and H * 2 <= 16384:
+        # dispatch fused into the c_fc GEMM, with two buffers of this GPU standing in for the token buffers of two ranks
+        # (on one GPU this shows the cost of running the gather inside the GEMM kernel, not the NVLink overlap it is for)
+        x2 = torch.randn_like(x)
+        both = torch.cat([selected.reshape(-1), selected.flip(0).reshape(-1)]).to(torch.int32)
+        layout2 = build_grouped_layout(both, E)
+        ptrs = [x.data_ptr(), x2.data_ptr()]
+
+        def separate():
+            rows = C.moe_gather(ptrs, [], layout2.src_entry, H, T * k, k, x, layout2.tile_expert, E)
+            return C.grouped_rows(rows, w_fc, layout2.tile_expert, False, st)
+
+        record["dispatch_rows"] = layout2.rows
+        record["gather_then_c_fc_ms"] = round(_time(separate, args.iters, args.warmup, flush), 4)
+        for ctas in (16, 32):
+            ms = _time(lambda: C.grouped_rows_dispatch(ptrs, layout2.src_entry, T * k, k, w_fc, layout2.tile_expert, False, st, ctas), args.iters, args.warmup, flush)
+            record[f"fused_dispatch_c_fc_ms_{ctas}_gather_ctas"] = round(ms, 4)
     record["status"] = int(st.item())
     _emit(record)
 

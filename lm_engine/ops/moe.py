@@ -106,12 +106,11 @@ def fused_dispatch_enabled(C) -> bool:
 
 
 def gather_then_grouped_rows(C, src_ptrs, src_entry, hidden, entries_per_rank, top_k, like, tile_expert, owners, weight, w_mn, st,
-                             copy_ctas: int = 8, out=None):
+                             copy_ctas: int = 32, out=None):
     """``rows = gather(src)[src_entry]; out = rows @ op(weight[expert of the tile])`` -> ``(rows, out)``. One kernel when
     the fused dispatch is available (gather CTAs feed the GEMM CTAs tile by tile), otherwise the gather kernel followed by
     the grouped GEMM."""
-    # worth it when rows cross NVLink (the transfer hides under the MMAs); a local gather runs at memory bandwidth on its own
-    if len(src_ptrs) > 1 and fused_dispatch_enabled(C) and hidden * 2 <= 16384:
+    if fused_dispatch_enabled(C) and hidden * 2 <= 16384:
         return C.grouped_rows_dispatch(src_ptrs, src_entry, entries_per_rank, top_k, weight, tile_expert, w_mn, st, copy_ctas, out)
     rows = C.moe_gather(src_ptrs, [], src_entry, hidden, entries_per_rank, top_k, like, tile_expert, owners)
     return rows, C.grouped_rows(rows, weight, tile_expert, w_mn, st, out)
