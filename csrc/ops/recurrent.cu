@@ -52,6 +52,21 @@ __device__ __forceinline__ float column_dot(const float* __restrict__ v, const f
   return (a0 + a1) + (a2 + a3);
 }
 
+// sum_k v[k] * w[k] with v in shared memory and w (one matrix column, or row of the transposed matrix) in registers
+template <int D>
+__device__ __forceinline__ float register_dot(const float* __restrict__ v, const float (&w)[D]) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int k = 0; k < D; k += 4) {
+    const float4 h = *reinterpret_cast<const float4*>(v + k);
+    a0 = fmaf(h.x, w[k + 0], a0);
+    a1 = fmaf(h.y, w[k + 1], a1);
+    a2 = fmaf(h.z, w[k + 2], a2);
+    a3 = fmaf(h.w, w[k + 3], a3);
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
 // ------------------------------------------------------------------------------------------------ forward
 // x: [T, G, n, d] through (row_stride, gate_stride = n * d); weight: [G * n, d, d] fp32; h0: [docs, n, d] fp32 or null.
 // out: [T, n, d]; gates (GRU only): [T, 3, n, d] = z, f, r of every step, kept for the backward pass.
@@ -74,27 +89,30 @@ __global__ void __launch_bounds__((GRU ? 3 : 1) * D)
   }
   if (m == 0) sH[e] = h0 != nullptr ? h0[((size_t)doc * n + head) * D + e] : 0.f;
   __syncthreads();
-  const float* w_col = sW + m * D * D + e;
+  // this thread's matrix column lives in registers for the whole scan (shared memory only stages the load)
+  float w_col[D];
+#pragma unroll
+  for (int k = 0; k < D; ++k) w_col[k] = sW[m * D * D + k * D + e];
   const size_t gate_stride = (size_t)n * D;
   int cur = 0;
   for (int t = t0; t < t1; ++t) {
     const float* h = sH + cur * D;
     const float xv = ld_f(x + (size_t)t * row_stride + m * gate_stride + (size_t)head * D + e);
     if (!GRU) {
-      const float hn = tanh_f(xv + column_dot<D>(h, w_col));
+      const float hn = tanh_f(xv + register_dot<D>(h, w_col));
       st_f(out + ((size_t)t * n + head) * D + e, hn);
       sH[(cur ^ 1) * D + e] = hn;
       __syncthreads();
     } else {
       float gate = 0.f;
       if (m != 0) {
-        gate = sigmoid_f(xv + column_dot<D>(h, w_col));
+        gate = sigmoid_f(xv + register_dot<D>(h, w_col));
         if (m == 1) sF[e] = gate; else sRH[e] = gate * h[e];
         st_f(gates + (((size_t)t * 3 + m) * n + head) * D + e, gate);
       }
       __syncthreads();
       if (m == 0) {
-        const float z = tanh_f(xv + column_dot<D>(sRH, w_col));
+        const float z = tanh_f(xv + register_dot<D>(sRH, w_col));
         const float f = sF[e];
         const float hn = f * h[e] + (1.f - f) * z;
         st_f(gates + (((size_t)t * 3) * n + head) * D + e, z);
@@ -132,6 +150,17 @@ __global__ void __launch_bounds__((GRU ? 3 : 1) * D)
   }
   __syncthreads();
   const float* wt_col = sWT + m * D * D + e;  // element j of row e of W_m at wt_col[j * D]
+  // up to d = 64 that row also fits in registers next to the weight-gradient column (2 d registers per thread)
+  constexpr bool kRowInRegisters = D <= 64;
+  float wt_reg[kRowInRegisters ? D : 1];
+  if constexpr (kRowInRegisters) {
+#pragma unroll
+    for (int j = 0; j < D; ++j) wt_reg[j] = wt_col[j * D];
+  }
+  auto row_dot = [&](const float* vec) -> float {
+    if constexpr (kRowInRegisters) return register_dot<D>(vec, wt_reg);
+    else return column_dot<D>(vec, wt_col);
+  };
   float dw[D];
 #pragma unroll
   for (int k = 0; k < D; ++k) dw[k] = 0.f;
@@ -148,7 +177,7 @@ __global__ void __launch_bounds__((GRU ? 3 : 1) * D)
       sDP[e] = dp;
       sHP[e] = hp;
       __syncthreads();
-      carry = column_dot<D>(sDP, wt_col);
+      carry = row_dot(sDP);
       if (clip > 0.f) carry = fminf(fmaxf(carry, -clip), clip);
 #pragma unroll
       for (int k = 0; k < D; k += 4) {
@@ -174,7 +203,7 @@ __global__ void __launch_bounds__((GRU ? 3 : 1) * D)
         sDP[D + e] = dpf;
       }
       __syncthreads();
-      if (m < 2) sPart[m * D + e] = column_dot<D>(sDP + m * D, wt_col);
+      if (m < 2) sPart[m * D + e] = row_dot(sDP + m * D);
       __syncthreads();
       const float drh = sPart[e];
       const float dpr = drh * hp * r * (1.f - r);
@@ -183,7 +212,7 @@ __global__ void __launch_bounds__((GRU ? 3 : 1) * D)
         sDP[2 * D + e] = dpr;
       }
       __syncthreads();
-      if (m == 2) sPart[2 * D + e] = column_dot<D>(sDP + 2 * D, wt_col);
+      if (m == 2) sPart[2 * D + e] = row_dot(sDP + 2 * D);
       // weight-gradient column of this thread: dW_m[k, e] += a[k] * dp_m[e], a = r * h for the candidate matrix, h otherwise
       {
         const float dp = m == 0 ? dpz : (m == 1 ? dpf : dpr);
