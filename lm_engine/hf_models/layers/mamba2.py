@@ -128,8 +128,8 @@ class Mamba2(nn.Module):
             dt = dt.clamp(lo, hi)
         return x, b, c, dt
 
-    def _sequence(self, u: torch.Tensor, mask: torch.Tensor | None, cache) -> torch.Tensor:
-        """u ``[B, L, hidden]``"""
+    def _sequence(self, u: torch.Tensor, mask: torch.Tensor | None, cache, cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
+        """u ``[B, L, hidden]``; with ``cu_seqlens`` (kernels only) the single row holds packed documents."""
         dtype = u.dtype
         gate, xbc, dt = self._split(self.in_proj(u))
         if mask is not None:
@@ -140,7 +140,7 @@ class Mamba2(nn.Module):
 
             # every row of the batch is one sequence: depthwise conv + SiLU in one kernel on the [tokens, channels] layout
             rows, length = xbc.shape[:2]
-            cu = torch.arange(0, rows * length + 1, length, dtype=torch.int32, device=xbc.device)
+            cu = cu_seqlens if cu_seqlens is not None else torch.arange(0, rows * length + 1, length, dtype=torch.int32, device=xbc.device)
             xbc_act = causal_conv1d_packed(xbc.reshape(rows * length, -1), self.conv1d.weight, self.conv1d.bias, cu, "silu").view_as(xbc)
         else:
             conv_out = self.conv1d(conv_in)[..., : conv_in.shape[-1]]
@@ -153,7 +153,7 @@ class Mamba2(nn.Module):
 
             # b and c stay per group: the scan kernel maps heads to groups itself
             x, b, c, dt = self._ssm_inputs(xbc_act, dt, repeat_groups=False)
-            y, final_state = ssd_scan(x.float() * dt[..., None], A * dt, b, c)
+            y, final_state = ssd_scan(x.float() * dt[..., None], A * dt, b, c, cu_seqlens=cu_seqlens)
         else:
             x, b, c, dt = self._ssm_inputs(xbc_act, dt)
             y, final_state = ssd_chunk_scan(x.float() * dt[..., None], A * dt, b.float(), c.float(), self.chunk_size)
@@ -184,6 +184,9 @@ class Mamba2(nn.Module):
         return self.out_proj(self.norm(y, gate.unsqueeze(1)))
 
     def forward(self, hidden_states: torch.Tensor, ctx: SequenceContext, past_key_values=None) -> torch.Tensor:
+        if ctx.packed and hidden_states.is_cuda and self._silu_activation and self.conv_kernel_size <= 8 and self._scan_kernel_ok(hidden_states):
+            # all documents in one pass: the convolution and the scan kernels take the document boundaries from cu_seqlens
+            return self._sequence(hidden_states.unsqueeze(0), None, None, cu_seqlens=ctx.cu_seqlens_int32()).squeeze(0)
         if ctx.packed:
             bounds = ctx.cu_seqlens.tolist()
             pieces = [self._sequence(hidden_states[s:e].unsqueeze(0), None, None).squeeze(0)

@@ -34,16 +34,29 @@ def _side_streams(device: torch.device):
 
 class _SSDScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, a, b, c, h0):
+    def forward(ctx, x, a, b, c, h0, cu_seqlens):
         C = native()
+        starts = None
+        if cu_seqlens is not None:
+            # packed documents in one row: a decay of exp(-inf) = 0 at the first token of a document resets the state
+            # there (forwards) and cuts the adjoint state (backwards); no host round trip for the boundaries
+            assert x.shape[0] == 1, "packed documents come as one row of tokens"
+            L = x.shape[1]
+            starts = torch.zeros(L + 1, dtype=torch.bool, device=x.device)
+            starts[cu_seqlens[:-1].long()] = True
+            starts = starts[:L]
+            a = a.masked_fill(starts[None, :, None], float("-inf"))
         y, final = C.ssd_scan(x, b, c, a, h0, False)
-        ctx.save_for_backward(x, a, b, c, y, final, h0 if h0 is not None else x.new_empty(0))
+        empty = x.new_empty(0)
+        ctx.save_for_backward(x, a, b, c, y, final, h0 if h0 is not None else empty,
+                              cu_seqlens if cu_seqlens is not None else empty, starts if starts is not None else empty)
         ctx.has_h0 = h0 is not None
+        ctx.packed = cu_seqlens is not None
         return y, final
 
     @staticmethod
     def backward(ctx, dy, dfinal):
-        x, a, b, c, y, final, h0 = ctx.saved_tensors
+        x, a, b, c, y, final, h0, cu_seqlens, starts = ctx.saved_tensors
         C = native()
         B, L, H, P = x.shape
         G, N = b.shape[2], b.shape[3]
@@ -67,17 +80,29 @@ class _SSDScan(torch.autograd.Function):
             result.record_stream(main)
         r = (dy * y).sum(-1) - (x * dx).sum(-1)
         da = torch.flip(torch.cumsum(torch.flip(r, dims=[1]), dim=1), dims=[1])
-        if dfinal is not None:
-            da = da + (dfinal * final).sum(dim=(-1, -2))[:, None, :]
+        tail = None if dfinal is None else (dfinal * final).sum(dim=(-1, -2))[:, None, :]
+        if ctx.packed:
+            # the sum runs to the end of the token's own document: subtract what lies beyond it
+            bounds = cu_seqlens.long()
+            document = torch.bucketize(torch.arange(L, device=x.device), bounds[1:], right=True).clamp(max=bounds.numel() - 2)
+            next_start = bounds[document + 1]
+            beyond = torch.cat([da, da.new_zeros(B, 1, H)], dim=1)[:, next_start]
+            da = da - beyond
+            if tail is not None:
+                da = da + tail * (next_start == L)[None, :, None]
+            da = da.masked_fill(starts[None, :, None], 0.0)
+        elif tail is not None:
+            da = da + tail
         db = db_heads.view(B, L, G, H // G, N).sum(3)
         dc = dc_heads.view(B, L, G, H // G, N).sum(3)
         dh0 = torch.exp(a[:, 0])[..., None, None] * adjoint0 if ctx.has_h0 else None
-        return dx, da, db, dc, dh0
+        return dx, da, db, dc, dh0, None
 
 
-def ssd_scan(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
-             initial_state: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+def ssd_scan(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, initial_state: torch.Tensor | None = None,
+             cu_seqlens: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """``x [B, L, H, P]`` (already multiplied by dt), ``a [B, L, H]`` (= A * dt), ``b`` / ``c`` ``[B, L, G, N]`` with
-    ``G`` dividing ``H``. Returns ``(y [B, L, H, P], final_state [B, H, P, N])``, all fp32."""
+    ``G`` dividing ``H``. Returns ``(y [B, L, H, P], final_state [B, H, P, N])``, all fp32. With ``cu_seqlens`` the single
+    row (``B = 1``) holds packed documents and the state starts from zero at every document."""
     f32 = lambda t: None if t is None else t.float().contiguous()
-    return _SSDScan.apply(f32(x), f32(a), f32(b), f32(c), f32(initial_state))
+    return _SSDScan.apply(f32(x), f32(a), f32(b), f32(c), f32(initial_state), cu_seqlens)

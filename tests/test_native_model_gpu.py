@@ -175,3 +175,40 @@ def test_recurrent_and_state_space_mixers_on_their_scan_kernels():
     for name, g in grads.items():
         r = ref_grads[name]
         assert (g - r).norm().item() <= 2e-3 * r.norm().item() + 1e-6, name
+
+
+def test_packed_documents_through_the_scan_kernels_match_the_per_document_loops():
+    """Padding-free batches: Mamba-2 (convolution + SSD scan with the state reset at document starts), GRU and RNN take
+    the document boundaries from cu_seqlens inside the kernels; the result equals running every document on its own."""
+    from lm_engine.enums import Kernel
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+    from lm_engine.kernels import enable_kernels
+
+    torch.manual_seed(0)
+    device = torch.device("cuda", 0)
+    mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=256, add_bias=False)
+    config = GPTBaseConfig(
+        vocab_size=512, hidden_size=128, num_layers=2, max_position_embeddings=512, position_embedding_type="nope",
+        normalization_function="rmsnorm",
+        sequence_mixer_blocks=[
+            dict(sequence_mixer_type="mamba2", state_size=64, intermediate_size=256, num_heads=4, conv_kernel_size=4, num_groups=2, chunk_size=64),
+            dict(sequence_mixer_type="gru", state_size=128, num_heads=4, add_bias=False),
+        ],
+        mlp_blocks=[dict(mlp)] * 2,
+    )
+    model = GPTBaseForCausalLM(config, use_padding_free_transformer=True).to(device)
+    docs = [torch.randint(0, 512, (n,)).tolist() for n in (70, 3, 129, 40)]
+
+    def run(kernels):
+        model.zero_grad(set_to_none=True)
+        with enable_kernels(kernels):
+            out = model(input_ids=docs, labels=docs)
+        out.loss.backward()
+        return out.logits.detach().float(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters() if p.grad is not None}
+
+    ref_logits, ref_grads = run([])
+    logits, grads = run([Kernel.mamba2_ssm, Kernel.gru_cute, Kernel.causal_conv1d])
+    assert (logits - ref_logits).abs().max().item() < 2e-3 * ref_logits.abs().max().item() + 1e-4
+    for name, g in grads.items():
+        r = ref_grads[name]
+        assert (g - r).norm().item() <= 3e-3 * r.norm().item() + 1e-6, name
