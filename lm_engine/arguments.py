@@ -175,7 +175,7 @@ class MixedPrecisionArgs(BaseArgs):
     scaling_type_weight: str = "dynamic"
     scaling_type_grad_output: str = "dynamic"
     # "tensorwise" (one scale per tensor) or "mxfp8" (e4m3 payload, one UE8M0 scale per 32 elements along K)
-    fp8_recipe: str = "mxfp8"
+    fp8_recipe: str = "tensorwise"
 
     def model_post_init(self, __context: Any) -> None:
         self.dtype = normalize_dtype_string(self.dtype)

@@ -65,8 +65,8 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
     if args.mixed_precision_args.dtype == "fp8":
         from .fp8 import FP8Manager
 
-        manager = FP8Manager([w.model for w in model_container])
-        log_rank_0(logging.INFO, f"fp8: {manager.converted} linear layers run tensor-scaled e4m3/e5m2 GEMMs (compute dtype of the rest: bf16)")
+        manager = FP8Manager([w.model for w in model_container], recipe=args.mixed_precision_args.fp8_recipe)
+        log_rank_0(logging.INFO, f"fp8 ({manager.recipe}): {manager.converted} linear layers converted (compute dtype of the rest: bf16)")
 
     pipeline_schedule = None
     if dist_args.num_pipeline_stages > 1:

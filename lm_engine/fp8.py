@@ -4,7 +4,13 @@ The reference converts linears with ``torchao.float8`` (one dynamic scale per te
 this engine's own kernels: per-tensor dynamic scaling, e4m3 for activations and weights, e5m2 for output gradients,
 fp32 accumulation in the tcgen05 ``kind::f8f6f4`` GEMM (``csrc/gemm/gemm_fp8.cu``), which reads K-major and MN-major
 operands, so the forward, data-gradient and weight-gradient products use the same three quantised tensors and no
-transposed copies. Block-scaled (MX, 1x32) operands are not built yet.
+transposed copies.
+
+``fp8_recipe: mxfp8`` selects the OCP microscaling format instead: e4m3 payload with one power-of-two (E8M0) scale per 32
+consecutive elements along the contraction dimension of each product. Its operands are quantised exactly as the format
+prescribes and multiplied after dequantisation by the bf16 tcgen05 GEMM, which reproduces the numerics of MXFP8
+training; a GEMM that consumes the block scales natively (``tcgen05.mma.kind::mxf8f6f4.block_scale``) does not exist
+here yet, so this recipe has the speed of bf16 plus the quantisation passes.
 """
 
 from __future__ import annotations
@@ -28,6 +34,65 @@ def quantize(x: torch.Tensor, fmt: int = E4M3) -> tuple[torch.Tensor, torch.Tens
 def dequantize(q: torch.Tensor, scale_inv: torch.Tensor, fmt: int = E4M3) -> torch.Tensor:
     dtype = torch.float8_e4m3fn if fmt == E4M3 else torch.float8_e5m2
     return q.view(dtype).float() * scale_inv
+
+
+MX_BLOCK = 32
+_E4M3_MAX = 448.0
+_E4M3_EMAX = 8  # 2^8 is the largest power of two that e4m3 represents
+
+
+def mx_quantize(x: torch.Tensor, dim: int = -1) -> tuple[torch.Tensor, torch.Tensor]:
+    """OCP MXFP8 (e4m3) along ``dim``: ``(payload float8_e4m3fn shaped like x, scales uint8 = biased E8M0 exponents with
+    the size of ``dim`` divided by 32)``. The shared exponent of a block is ``floor(log2(amax)) - 8``; values are rounded to
+    nearest even and saturate at +-448."""
+    x = x.movedim(dim, -1)
+    assert x.shape[-1] % MX_BLOCK == 0, "the quantised dimension must be a multiple of 32"
+    blocks = x.float().reshape(*x.shape[:-1], x.shape[-1] // MX_BLOCK, MX_BLOCK)
+    amax = blocks.abs().amax(dim=-1, keepdim=True)
+    exponent = torch.floor(torch.log2(amax.clamp(min=2.0**-126))) - _E4M3_EMAX
+    exponent = exponent.clamp(-127, 127)
+    scaled = (blocks * torch.exp2(-exponent)).clamp(-_E4M3_MAX, _E4M3_MAX)
+    payload = scaled.to(torch.float8_e4m3fn).reshape(x.shape).movedim(-1, dim)
+    scales = (exponent.squeeze(-1) + 127).to(torch.uint8).movedim(-1, dim)
+    return payload, scales
+
+
+def mx_dequantize(payload: torch.Tensor, scales: torch.Tensor, dim: int = -1, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    p = payload.movedim(dim, -1).float()
+    e = scales.movedim(dim, -1).float() - 127
+    out = p.reshape(*p.shape[:-1], p.shape[-1] // MX_BLOCK, MX_BLOCK) * torch.exp2(e).unsqueeze(-1)
+    return out.reshape(p.shape).movedim(-1, dim).to(dtype)
+
+
+def _mx_round_trip(x: torch.Tensor, dim: int) -> torch.Tensor:
+    return mx_dequantize(*mx_quantize(x, dim), dim=dim, dtype=x.dtype)
+
+
+class _MXLinear(torch.autograd.Function):
+    """Linear layer with MXFP8 operands: every product quantises both operands in blocks of 32 along its own contraction
+    dimension (features for the forward product, output features for the data gradient, tokens for the weight gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.shape, ctx.has_bias = shape, bias is not None
+        y = ops.linear(_mx_round_trip(x2, 1), _mx_round_trip(weight, 1), bias)
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = _mx_round_trip(dy2, 1) @ _mx_round_trip(weight, 0)        # contraction over the output features
+        dw = _mx_round_trip(dy2, 0).t() @ _mx_round_trip(x2, 0)        # contraction over the tokens
+        db = dy2.sum(0) if ctx.has_bias else None
+        return dx.view(ctx.shape), dw.to(weight.dtype), db
+
+
+def mx_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    return _MXLinear.apply(x, weight, bias)
 
 
 class _FP8Linear(torch.autograd.Function):
@@ -82,16 +147,20 @@ class FP8Manager:
     bf16, like in the reference). The scaling-type arguments are accepted for compatibility; scaling is dynamic."""
 
     def __init__(self, model_container, enable_fsdp_fp8_all_gather: bool = False, precompute_fp8_dynamic_scale_for_fsdp: bool = False,
-                 torch_compile: bool = False, scaling_type_input=None, scaling_type_weight=None, scaling_type_grad_output=None) -> None:
-        if not ops.native_available() or not hasattr(ops.native(), "gemm_fp8"):
-            raise RuntimeError("fp8 training needs the sm_100a extension")
+                 torch_compile: bool = False, scaling_type_input=None, scaling_type_weight=None, scaling_type_grad_output=None,
+                 recipe: str = "tensorwise") -> None:
+        assert recipe in ("tensorwise", "mxfp8"), recipe
+        if recipe == "tensorwise" and (not ops.native_available() or not hasattr(ops.native(), "gemm_fp8")):
+            raise RuntimeError("tensor-scaled fp8 training needs the sm_100a extension")
+        self.recipe = recipe
+        forward = _fp8_forward if recipe == "tensorwise" else _mx_forward
         self.converted = 0
         for model in model_container:
             for name, module in model.named_modules():
                 if hasattr(module, "_fusable"):
                     module._fusable = False  # the whole-block bf16 schedule would bypass the converted linears
                 if _eligible(module) and not name.endswith(("lm_head", "output")):
-                    module.forward = _fp8_forward.__get__(module, type(module))
+                    module.forward = forward.__get__(module, type(module))
                     self.converted += 1
 
     @staticmethod
@@ -106,4 +175,11 @@ class FP8Manager:
 def _fp8_forward(self, x: torch.Tensor) -> torch.Tensor:
     if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.numel() // x.shape[-1] % 16 == 0:
         return fp8_linear(x, self.weight, self.bias)
+    return ops.linear(x, self.weight, self.bias)
+
+
+def _mx_forward(self, x: torch.Tensor) -> torch.Tensor:
+    tokens = x.numel() // x.shape[-1]
+    if tokens % MX_BLOCK == 0 and self.in_features % MX_BLOCK == 0 and self.out_features % MX_BLOCK == 0:
+        return mx_linear(x, self.weight, self.bias)
     return ops.linear(x, self.weight, self.bias)

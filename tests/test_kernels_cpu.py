@@ -20,3 +20,57 @@ def test_grouped_layout_capacity_bound_drops_the_overflow_and_counts_it():
     assert torch.equal(bound.src_entry[rows].long(), torch.nonzero(bound.dest_row >= 0).flatten())
     keep = bound.dest_row >= 0
     assert torch.equal(bound.dest_row[keep], free.dest_row[keep])
+
+
+def test_mx_quantisation_follows_the_block_format():
+    """One power-of-two scale per 32 elements, e4m3 payload: exact for values that e4m3 holds after the shift, relative
+    error below 2^-3 otherwise, saturation at the block maximum, and quantisation along any dimension."""
+    import torch
+
+    from lm_engine.fp8 import MX_BLOCK, mx_dequantize, mx_quantize
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 128) * torch.logspace(-6, 6, 6).unsqueeze(1)
+    payload, scales = mx_quantize(x)
+    assert payload.dtype == torch.float8_e4m3fn and payload.shape == x.shape
+    assert scales.dtype == torch.uint8 and scales.shape == (6, 128 // MX_BLOCK)
+    back = mx_dequantize(payload, scales)
+    blocks, back_blocks = x.view(6, 4, MX_BLOCK), back.view(6, 4, MX_BLOCK)
+    amax = blocks.abs().amax(-1, keepdim=True)
+    # elements well above the block's underflow level keep 3 mantissa bits (relative error at most 2^-4); the block
+    # maximum may saturate from just below 512 to 448, which is the worst case 2^-3
+    big = blocks.abs() > amax * 2.0**-6
+    assert ((back_blocks - blocks).abs()[big] <= blocks.abs()[big] * 2.0**-3 + 1e-30).all()
+    inside = big & (blocks.abs() * torch.exp2(127.0 - scales.float()).unsqueeze(-1) <= 448)
+    assert ((back_blocks - blocks).abs()[inside] <= blocks.abs()[inside] * 2.0**-4 + 1e-30).all()
+    # the scale is the power of two that puts the block maximum into [256, 512) before saturation at 448
+    shifted = amax.squeeze(-1) * torch.exp2(127.0 - scales.float())
+    assert ((shifted >= 256 * (1 - 1e-6)) & (shifted < 512)).all()
+    # powers of two survive exactly, and quantising along dim 0 equals quantising the transpose along dim 1
+    exact = torch.tensor([[2.0 ** (k % 15) for k in range(32)]])  # 2^0 .. 2^14: within e4m3's normal range after the shift
+    assert torch.equal(mx_dequantize(*mx_quantize(exact)), exact)
+    y = torch.randn(64, 8)
+    p0, s0 = mx_quantize(y, dim=0)
+    p1, s1 = mx_quantize(y.t().contiguous(), dim=1)
+    assert torch.equal(p0.float(), p1.float().t()) and torch.equal(s0, s1.t())
+
+
+def test_mx_linear_gradients_track_the_unquantised_layer():
+    import torch
+
+    from lm_engine.fp8 import mx_linear
+
+    torch.manual_seed(1)
+    x = torch.randn(64, 96, requires_grad=True)
+    w = (torch.randn(128, 96) * 0.1).requires_grad_(True)
+    b = torch.zeros(128, requires_grad=True)
+    dy = torch.randn(64, 128)
+    mx_linear(x, w, b).backward(dy)
+    got = [t.grad.clone() for t in (x, w, b)]
+    for t in (x, w, b):
+        t.grad = None
+    torch.nn.functional.linear(x, w, b).backward(dy)
+    for g, t in zip(got, (x, w, b)):
+        rel = (g - t.grad).norm() / t.grad.norm()
+        assert rel < 0.06, rel
+    assert torch.equal(got[2], b.grad)
