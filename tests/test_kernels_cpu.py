@@ -74,3 +74,29 @@ def test_mx_linear_gradients_track_the_unquantised_layer():
         rel = (g - t.grad).norm() / t.grad.norm()
         assert rel < 0.06, rel
     assert torch.equal(got[2], b.grad)
+
+
+def test_mxfp8_recipe_converts_the_linears_of_a_model():
+    """``FP8Manager(recipe="mxfp8")`` switches the block linears (not the LM head) to MX operands; the loss stays close to
+    the unquantised model and every parameter still receives a gradient."""
+    import torch
+
+    from lm_engine.fp8 import FP8Manager
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    torch.manual_seed(0)
+    config = GPTBaseConfig(
+        vocab_size=128, hidden_size=64, num_layers=2, max_position_embeddings=64, position_embedding_type="rope",
+        normalization_function="rmsnorm", tie_word_embeddings=False,
+        sequence_mixer_blocks=[dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)] * 2,
+        mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=False)] * 2,
+    )
+    model = GPTBaseForCausalLM(config)
+    ids = torch.randint(0, 128, (2, 32))
+    reference = float(model(input_ids=ids, labels=ids).loss)
+    manager = FP8Manager([model], recipe="mxfp8")
+    assert manager.converted == 8  # c_attn, c_proj, c_fc, c_proj of two blocks
+    out = model(input_ids=ids, labels=ids)
+    assert abs(float(out.loss) - reference) < 0.05 * reference
+    out.loss.backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
