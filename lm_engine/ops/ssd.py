@@ -23,6 +23,31 @@ def ssd_kernel_ok(x: torch.Tensor, state_size: int) -> bool:
     return p % 4 == 0 and state_size % 4 == 0 and p <= 256 and state_size <= 256
 
 
+def _scan_reference(u, v, w, a, s0, reverse: bool):
+    """The recurrence of the kernel, step by step in PyTorch (CPU path and oracle): ``s = decay * s + u_t v_t^T``,
+    ``out_t = s w_t`` with the decay of step t forwards and of step t + 1 backwards."""
+    B, L, H = a.shape
+    expand = lambda t: t if t.shape[2] == H else t.repeat_interleave(H // t.shape[2], dim=2)
+    u, v, w = expand(u), expand(v), expand(w)
+    state = u.new_zeros(B, H, u.shape[-1], v.shape[-1]) if s0 is None else s0.clone()
+    out = u.new_empty(B, L, H, u.shape[-1])
+    decay_next = a.new_ones(B, H)
+    for step in range(L):
+        t = L - 1 - step if reverse else step
+        decay_t = torch.exp(a[:, t])
+        decay = decay_next if reverse else decay_t
+        decay_next = decay_t
+        state = decay[..., None, None] * state + u[:, t, :, :, None] * v[:, t, :, None, :]
+        out[:, t] = torch.einsum("bhqr,bhr->bhq", state, w[:, t])
+    return out, state
+
+
+def _scan(u, v, w, a, s0, reverse: bool):
+    if u.is_cuda and native_available() and hasattr(native(), "ssd_scan"):
+        return native().ssd_scan(u, v, w, a, s0, reverse)
+    return _scan_reference(u, v, w, a, s0, reverse)
+
+
 _SIDE_STREAMS: dict[torch.device, tuple[torch.cuda.Stream, torch.cuda.Stream]] = {}
 
 
@@ -35,7 +60,6 @@ def _side_streams(device: torch.device):
 class _SSDScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, a, b, c, h0, cu_seqlens):
-        C = native()
         starts = None
         if cu_seqlens is not None:
             # packed documents in one row: a decay of exp(-inf) = 0 at the first token of a document resets the state
@@ -46,7 +70,7 @@ class _SSDScan(torch.autograd.Function):
             starts[cu_seqlens[:-1].long()] = True
             starts = starts[:L]
             a = a.masked_fill(starts[None, :, None], float("-inf"))
-        y, final = C.ssd_scan(x, b, c, a, h0, False)
+        y, final = _scan(x, b, c, a, h0, False)
         empty = x.new_empty(0)
         ctx.save_for_backward(x, a, b, c, y, final, h0 if h0 is not None else empty,
                               cu_seqlens if cu_seqlens is not None else empty, starts if starts is not None else empty)
@@ -57,27 +81,31 @@ class _SSDScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dfinal):
         x, a, b, c, y, final, h0, cu_seqlens, starts = ctx.saved_tensors
-        C = native()
         B, L, H, P = x.shape
         G, N = b.shape[2], b.shape[3]
         dy = dy.contiguous() if dy is not None else torch.zeros_like(y)
         h0 = h0 if ctx.has_h0 else None
         dfinal = None if dfinal is None else dfinal.contiguous()
         transposed = lambda s: None if s is None else s.transpose(-1, -2).contiguous()
-        # three independent scans of one CTA per (batch, head) each: side streams let them share the SMs
-        main = torch.cuda.current_stream(x.device)
-        side = _side_streams(x.device)
         h0_t, dfinal_t = transposed(h0), transposed(dfinal)
-        for stream in side:
-            stream.wait_stream(main)
-        with torch.cuda.stream(side[0]):
-            dc_heads, _ = C.ssd_scan(b, x, dy, a, h0_t, False)
-        with torch.cuda.stream(side[1]):
-            db_heads, _ = C.ssd_scan(c, dy, x, a, dfinal_t, True)
-        dx, adjoint0 = C.ssd_scan(dy, c, b, a, dfinal, True)
-        for stream, result in zip(side, (dc_heads, db_heads)):
-            main.wait_stream(stream)
-            result.record_stream(main)
+        if x.is_cuda:
+            # three independent scans of one CTA per (batch, head) each: side streams let them share the SMs
+            main = torch.cuda.current_stream(x.device)
+            side = _side_streams(x.device)
+            for stream in side:
+                stream.wait_stream(main)
+            with torch.cuda.stream(side[0]):
+                dc_heads, _ = _scan(b, x, dy, a, h0_t, False)
+            with torch.cuda.stream(side[1]):
+                db_heads, _ = _scan(c, dy, x, a, dfinal_t, True)
+            dx, adjoint0 = _scan(dy, c, b, a, dfinal, True)
+            for stream, result in zip(side, (dc_heads, db_heads)):
+                main.wait_stream(stream)
+                result.record_stream(main)
+        else:
+            dc_heads, _ = _scan(b, x, dy, a, h0_t, False)
+            db_heads, _ = _scan(c, dy, x, a, dfinal_t, True)
+            dx, adjoint0 = _scan(dy, c, b, a, dfinal, True)
         r = (dy * y).sum(-1) - (x * dx).sum(-1)
         da = torch.flip(torch.cumsum(torch.flip(r, dims=[1]), dim=1), dims=[1])
         tail = None if dfinal is None else (dfinal * final).sum(dim=(-1, -2))[:, None, :]

@@ -100,3 +100,64 @@ def test_mxfp8_recipe_converts_the_linears_of_a_model():
     assert abs(float(out.loss) - reference) < 0.05 * reference
     out.loss.backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+def test_ssd_scan_function_on_cpu_matches_the_chunked_formulation_packed_and_batched():
+    """The autograd function around the scan (step-by-step recurrence on CPU): batched rows with an initial state and a
+    gradient into the final state, and packed documents whose state restarts at every document."""
+    import torch
+
+    from lm_engine.hf_models.layers.mamba2 import ssd_chunk_scan
+    from lm_engine.ops.ssd import ssd_scan
+
+    torch.manual_seed(2)
+    H, G, P, N = 4, 2, 8, 16
+
+    def inputs(B, L):
+        x = torch.randn(B, L, H, P, requires_grad=True)
+        a = (-torch.rand(B, L, H) * 0.5).requires_grad_(True)
+        b = (torch.randn(B, L, G, N) * 0.3).requires_grad_(True)
+        c = (torch.randn(B, L, G, N) * 0.3).requires_grad_(True)
+        return x, a, b, c
+
+    def chunked(x, a, b, c, h0=None):
+        return ssd_chunk_scan(x, a, b.repeat_interleave(H // G, dim=2), c.repeat_interleave(H // G, dim=2), 16, initial_state=h0)
+
+    def grads(tensors):
+        out = [t.grad.clone() for t in tensors]
+        for t in tensors:
+            t.grad = None
+        return out
+
+    # batched, with initial state and final-state gradient
+    x, a, b, c = inputs(2, 40)
+    h0 = (torch.randn(2, H, P, N) * 0.2).requires_grad_(True)
+    dy, dfinal = torch.randn(2, 40, H, P), torch.randn(2, H, P, N) * 0.1
+    y, final = ssd_scan(x, a, b, c, h0)
+    torch.autograd.backward([y, final], [dy, dfinal])
+    got = [y.detach(), final.detach()] + grads([x, a, b, c, h0])
+    y_ref, final_ref = chunked(x, a, b, c, h0)
+    torch.autograd.backward([y_ref, final_ref], [dy, dfinal])
+    ref = [y_ref.detach(), final_ref.detach()] + grads([x, a, b, c, h0])
+    for g, r in zip(got, ref):
+        assert (g - r).norm() <= 1e-4 * r.norm() + 1e-6
+
+    # packed: three documents (one of a single token) in one row
+    lengths = [13, 1, 26]
+    cu = torch.tensor([0, 13, 14, 40], dtype=torch.int32)
+    x, a, b, c = inputs(1, 40)
+    dy = torch.randn(1, 40, H, P)
+    y, _ = ssd_scan(x, a, b, c, cu_seqlens=cu)
+    y.backward(dy)
+    got = [y.detach()] + grads([x, a, b, c])
+    pieces, start = [], 0
+    for n in lengths:
+        sl = slice(start, start + n)
+        pieces.append(chunked(x[:, sl], a[:, sl], b[:, sl], c[:, sl])[0])
+        start += n
+    y_ref = torch.cat(pieces, dim=1)
+    y_ref.backward(dy)
+    ref = [y_ref.detach()] + grads([x, a, b, c])
+    # the decay of a document's first token multiplies a zero state: its gradient is zero in both formulations
+    for name, g, r in zip(("y", "dx", "da", "db", "dc"), got, ref):
+        assert (g - r).norm() <= 1e-4 * r.norm() + 1e-6, name
