@@ -1,3 +1,5 @@
+"""CPU statements of device-side algorithms: the expert row layout, the MX block format and the SSD scan function
+(the kernels themselves are tested on a GPU in test_kernels_gpu.py)."""
 
 
 def test_grouped_layout_capacity_bound_drops_the_overflow_and_counts_it():
