@@ -82,6 +82,37 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
                     out.stride(0), a_mn, b_mn, epi, (float)alpha, status_ptr(status), (int)max_ctas, cur_stream());
 }
 
+// Knobs of the CTA-pair GEMM for micro-benchmarks: raster group, k skew, register-store epilogue, trace buffer
+// (int64 tensor with 8 words per CTA; pass None to switch tracing off).
+void gemm_tuning(int64_t group, int64_t k_skew, bool direct_store, const c10::optional<Tensor>& trace, int64_t split_k) {
+  auto& t = b200::pair_gemm_tuning();
+  t.split_k = (int)split_k;
+  t.group = (int)group;
+  t.k_skew = (int)k_skew;
+  t.direct_store = direct_store ? 1 : 0;
+  t.trace = nullptr;
+  if (trace.has_value()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 8 * 148, "trace must be a CUDA int64 tensor of >= 8 * 148 words");
+    t.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+  }
+}
+
+// fc = x w^T ([T, 2I], both halves kept for backward) and act = fc[:, :I] * silu(fc[:, I:]) in one launch.
+void gemm_swiglu(const Tensor& x, const Tensor& w, Tensor& fc, Tensor& act, const c10::optional<Tensor>& status) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  check_bf16(fc, "fc");
+  check_bf16(act, "act");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && fc.dim() == 2 && act.dim() == 2, "gemm_swiglu operands must be 2-D");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && fc.stride(1) == 1 && act.stride(1) == 1, "gemm_swiglu operands must have a unit inner stride");
+  const int64_t M = x.size(0), K = x.size(1), I = w.size(0) / 2;
+  TORCH_CHECK(w.size(1) == K && w.size(0) == 2 * I, "gemm_swiglu: weight must be [2I, K]");
+  TORCH_CHECK(fc.size(0) == M && fc.size(1) == 2 * I && act.size(0) == M && act.size(1) == I, "gemm_swiglu: output shape mismatch");
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::gemm_bf16_swiglu(x.data_ptr(), w.data_ptr(), fc.data_ptr(), act.data_ptr(), (int)M, (int)I, (int)K, x.stride(0), w.stride(0),
+                         fc.stride(0), act.stride(0), status_ptr(status), cur_stream());
+}
+
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, double eps,
                                 bool want_sum) {
   check_bf16(x, "x");
@@ -314,6 +345,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b_mn") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0, py::arg("status") = py::none(),
         py::arg("max_ctas") = 0, py::arg("variant") = 0);
   m.def("set_gemm_variant", &set_gemm_variant);
+  m.def("gemm_tuning", &gemm_tuning, py::arg("group") = 0, py::arg("k_skew") = 0, py::arg("direct_store") = false, py::arg("trace") = py::none(), py::arg("split_k") = 0);
+  m.def("gemm_swiglu", &gemm_swiglu, "c_fc GEMM with the SwiGLU activation in its epilogue", py::arg("x"), py::arg("w"), py::arg("fc"), py::arg("act"), py::arg("status") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("eps"),
         py::arg("want_sum") = true);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -14,11 +14,24 @@
 //   acc_empty[b] lives in the leader, 8 arrivals: the four epilogue warps of each CTA (the peer's arrive remotely)
 // All mbarrier waits are bounded; cluster-wide barriers bracket the kernel so that neither CTA touches the other's
 // shared memory before it is initialised or after it has exited.
+//
+// Epilogue: every epilogue warp owns 32 accumulator rows. It converts 128-byte row segments (64 bf16 / 32 fp32
+// columns) into a swizzled 4 KB shared-memory box and hands the box to the TMA engine: a bulk tensor store, or a bulk
+// tensor reduction (`.add`) for the accumulating variants, so that the read-modify-write of a weight-gradient tile
+// happens in L2 and never travels to the SM. Two boxes per warp alternate, the store of one overlaps the conversion
+// of the next. Outputs that a tensor map cannot describe (unaligned base / row stride) take the register -> global path.
+//
+// SwiGLU epilogue (forward of the gated MLP up-projection): the weight is [2I, K] with rows [0, I) = up and
+// [I, 2I) = gate. The even CTA of a pair loads 128 up rows and the odd CTA the 128 gate rows of the same channels, so
+// accumulator columns [0,128) and [128,256) of one tile hold up and gate of the same 128 channels; the epilogue
+// writes both halves of the projection (backward needs them) and up * silu(gate), computed from the bf16-rounded
+// values exactly as the stand-alone kernel does, without the projection making a round trip through HBM.
 #include <cuda.h>
 
 #include "../common/launch.h"
 #include "../common/ptx.cuh"
 #include "../common/tensor_map.h"
+#include "../ops/ops.h"
 
 namespace b200 {
 
@@ -32,11 +45,22 @@ constexpr int STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN_HALF * BK * 2;
 constexpr int THREADS = 192;
-constexpr int GROUP_M = 4;  // in units of 256-row tiles
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+constexpr int BOX_BYTES = 32 * 128;            // one epilogue box: 32 rows x 128 bytes
+constexpr int STAGING_BYTES = 4 * 2 * BOX_BYTES;  // two boxes for each of the four epilogue warps
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES + 1024 + 256;
+constexpr int TRACE_WORDS = 8;
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ACC = 3 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ACC = 3, EPI_SWIGLU = 4 };
+
+struct KernelOpts {
+  int group;        // > 0: panels of `group` 256-row tiles, rows fastest; < 0: panels of -group 256-column tiles, columns fastest
+  int tma_store;    // epilogue leaves through shared memory and bulk tensor stores / reductions
+  int k_skew;       // k-block at which tile (i, j) starts its walk over K is (i + j) * k_skew mod k_blocks
+  int swiglu_i;     // EPI_SWIGLU: intermediate size I (N == 2 I)
+  int split_k;      // >= 1; > 1 only with the bulk-reduction epilogues: each tile is computed as that many partial sums over K
+  long long* trace; // TRACE builds: TRACE_WORDS cycle counters per CTA
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -96,28 +120,46 @@ __device__ __forceinline__ void umma_commit_2sm(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
 struct TileCoord {
-  int m0, n0;
+  int mi, ni;  // tile indices (256-row, 256-column units)
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_tiles) {
-  const int per_group = GROUP_M * n_tiles;
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_tiles, int group) {
+  if (group > 0) {
+    const int per_group = group * n_tiles;
+    const int g = tile / per_group;
+    const int first = g * group;
+    const int gsize = min(m_tiles - first, group);
+    const int r = tile - g * per_group;
+    return {first + r % gsize, r / gsize};
+  }
+  group = -group;
+  const int per_group = group * m_tiles;
   const int g = tile / per_group;
-  const int first_m = g * GROUP_M;
-  const int gsize = min(m_tiles - first_m, GROUP_M);
+  const int first = g * group;
+  const int gsize = min(n_tiles - first, group);
   const int r = tile - g * per_group;
-  return {(first_m + r % gsize) * (2 * BM), (r / gsize) * BN};
+  return {r / gsize, first + r % gsize};
 }
 
-template <int A_MN, int B_MN, int EPI>
+// Row `lane` of a swizzled 32 x 128-byte box: 16-byte chunk `c` of the row lands at chunk `c ^ (lane & 7)`.
+__device__ __forceinline__ void box_write(uint8_t* box, int lane, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(box + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = v;
+}
+
+template <int A_MN, int B_MN, int EPI, bool TRACE>
 __global__ void __launch_bounds__(THREADS, 1)
     gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         void* __restrict__ Cv, int M, int N, int K, long long ldc, float alpha, int* status) {
+                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
+                         void* __restrict__ Cv, int M, int N, int K, long long ldc, float alpha, int* status, KernelOpts opts) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* sStage = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStage + STAGING_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* acc_full = bars + 2 * STAGES;
@@ -134,7 +176,9 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int m_tiles = (M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = (N + BN - 1) / BN;
   const int k_blocks = (K + BK - 1) / BK;
-  const int total = m_tiles * n_tiles;
+  const int split = opts.split_k;
+  const int total = m_tiles * n_tiles * split;  // work units: (tile, k range)
+  long long* trace = TRACE ? opts.trace + (long long)blockIdx.x * TRACE_WORDS : nullptr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -166,36 +210,45 @@ __global__ void __launch_bounds__(THREADS, 1)
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total && ok; tile += num_pairs) {
-        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles);
-        const int m0 = tc.m0 + (int)cta_rank * BM;
-        const int n0 = tc.n0 + (int)cta_rank * BN_HALF;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      long long waited = 0;
+      for (int unit = pair; unit < total && ok; unit += num_pairs) {
+        const TileCoord tc = tile_coord(unit / split, m_tiles, n_tiles, opts.group);
+        const int kb_begin = (int)((long long)(unit % split) * k_blocks / split);
+        const int kb_end = (int)((long long)(unit % split + 1) * k_blocks / split);
+        const int m0 = tc.mi * (2 * BM) + (int)cta_rank * BM;
+        const int n0 = EPI == EPI_SWIGLU ? tc.ni * BN_HALF + (int)cta_rank * opts.swiglu_i : tc.ni * BN + (int)cta_rank * BN_HALF;
+        const int k_len = kb_end - kb_begin;
+        int kk = kb_begin + (opts.k_skew && k_len > 0 ? (int)(((long long)(tc.mi + tc.ni) * opts.k_skew) % k_len) : 0);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          const long long t0 = TRACE ? clock64() : 0;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
             raise_status(status, kStatusWaitTimeoutProducer, abort_flag);
             ok = false;
             break;
           }
+          if (TRACE) waited += clock64() - t0;
           const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
           if (leader) mbar_arrive_expect_tx(&full[s], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
           uint8_t* b_dst = sB + s * B_STAGE_BYTES;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmA, full_leader, m0 + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmA, full_leader, m0 + j * 64, kk * BK);
           } else {
-            tma_load_2d_pair(a_dst, &tmA, full_leader, kb * BK, m0);
+            tma_load_2d_pair(a_dst, &tmA, full_leader, kk * BK, m0);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmB, full_leader, n0 + j * 64, kb * BK);
+            for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmB, full_leader, n0 + j * 64, kk * BK);
           } else {
-            tma_load_2d_pair(b_dst, &tmB, full_leader, kb * BK, n0);
+            tma_load_2d_pair(b_dst, &tmB, full_leader, kk * BK, n0);
           }
+          if (++kk == kb_end) kk = kb_begin;
         }
       }
+      if (TRACE) trace[0] = waited;
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
@@ -207,23 +260,31 @@ __global__ void __launch_bounds__(THREADS, 1)
       constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = pair; tile < total && ok; tile += num_pairs, ++tcount) {
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = TRACE ? clock64() : 0;
+      for (int unit = pair; unit < total && ok; unit += num_pairs, ++tcount) {
+        const int kb_begin = (int)((long long)(unit % split) * k_blocks / split);
+        const int kb_end = (int)((long long)(unit % split + 1) * k_blocks / split);
         const uint32_t buf = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
+        long long t0 = TRACE ? clock64() : 0;
         if (!mbar_wait(&acc_empty[buf], aph ^ 1, abort_flag)) {
           raise_status(status, kStatusWaitTimeoutMma, abort_flag);
           break;
         }
+        if (TRACE) wait_acc += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          t0 = TRACE ? clock64() : 0;
           if (!mbar_wait(&full[s], ph, abort_flag)) {
             raise_status(status, kStatusWaitTimeoutMma, abort_flag);
             ok = false;
             break;
           }
+          if (TRACE) wait_full += clock64() - t0;
           tc_fence_after_sync();
           const uint32_t a_base = smem_u32(sA + s * A_STAGE_BYTES);
           const uint32_t b_base = smem_u32(sB + s * B_STAGE_BYTES);
@@ -233,7 +294,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                                      : umma_smem_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc_sw128(b_base + k * 16 * 128, BK * 128, 1024)
                                      : umma_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_f16_ss_2sm(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_2sm(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           // release the stage in both CTAs
           const uint32_t e_local = smem_u32(&empty[s]);
@@ -246,26 +307,157 @@ __global__ void __launch_bounds__(THREADS, 1)
           umma_commit_2sm(map_to_cta(f_local, 1));
         }
       }
+      if (TRACE) {
+        trace[1] = wait_full;
+        trace[2] = wait_acc;
+        trace[3] = clock64() - t_begin;
+        trace[6] = tcount;
+      }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue: this CTA's 128 x 256 half
     const int q = warp & 3;
-    uint32_t tcount = 0;
-    for (int tile = pair; tile < total; tile += num_pairs, ++tcount) {
-      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles);
+    uint8_t* stage0 = sStage + q * (2 * BOX_BYTES);
+    uint32_t tcount = 0, nstore = 0;
+    long long wait_acc = 0, wait_store = 0;
+    const long long t_begin = TRACE ? clock64() : 0;
+    for (int unit = pair; unit < total; unit += num_pairs, ++tcount) {
+      const TileCoord tc = tile_coord(unit / split, m_tiles, n_tiles, opts.group);
       const uint32_t buf = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
+      long long t0 = TRACE ? clock64() : 0;
       if (!mbar_wait(&acc_full[buf], aph, abort_flag)) {
         raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
         break;
       }
+      if (TRACE) wait_acc += clock64() - t0;
       tc_fence_after_sync();
-      const int row = tc.m0 + (int)cta_rank * BM + q * 32 + lane;
+      const int row0 = tc.mi * (2 * BM) + (int)cta_rank * BM + q * 32;
+      const int row = row0 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+
+      if (EPI == EPI_SWIGLU) {
+        // accumulator columns [0,128) = up, [128,256) = gate of channels [ni*128, ni*128 + 128)
+        const int ch0 = tc.ni * BN_HALF;
+        uint8_t* box_u = stage0;
+        uint8_t* box_g = stage0 + BOX_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int ch = ch0 + c * 64;
+          if (ch >= opts.swiglu_i) break;
+          uint32_t actp[32];
+          if (TRACE) t0 = clock64();
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          if (TRACE) wait_store += clock64() - t0;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t vu[32], vg[32];
+            B200_TMEM_LD_32(vu, t_row + c * 64 + half * 32);
+            B200_TMEM_LD_32(vg, t_row + BN_HALF + c * 64 + half * 32);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t pu[4], pg[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                pu[e] = pack_bf16x2(__uint_as_float(vu[8 * j + 2 * e]) * alpha, __uint_as_float(vu[8 * j + 2 * e + 1]) * alpha);
+                pg[e] = pack_bf16x2(__uint_as_float(vg[8 * j + 2 * e]) * alpha, __uint_as_float(vg[8 * j + 2 * e + 1]) * alpha);
+                const float2 u = unpack_bf16x2(pu[e]), g = unpack_bf16x2(pg[e]);
+                actp[half * 16 + j * 4 + e] = pack_bf16x2(u.x * silu_f(g.x), u.y * silu_f(g.y));
+              }
+              box_write(box_u, lane, half * 4 + j, make_uint4(pu[0], pu[1], pu[2], pu[3]));
+              box_write(box_g, lane, half * 4 + j, make_uint4(pg[0], pg[1], pg[2], pg[3]));
+            }
+          }
+          if (c == 1 || ch + 64 >= opts.swiglu_i) {
+            // last read of this accumulator: hand the TMEM buffer back before the stores drain
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M) {
+            tma_store_2d(&tmC, box_u, ch, row0);
+            tma_store_2d(&tmC, box_g, opts.swiglu_i + ch, row0);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) box_write(box_u, lane, j, make_uint4(actp[4 * j], actp[4 * j + 1], actp[4 * j + 2], actp[4 * j + 3]));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M) {
+            tma_store_2d(&tmC2, box_u, ch, row0);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
+
+      if (opts.tma_store) {
+        constexpr bool kBf16 = EPI == EPI_BF16 || EPI == EPI_BF16_ACC;
+        constexpr int kColsPerBox = kBf16 ? 64 : 32;
+        constexpr int kBoxes = BN / kColsPerBox;
+#pragma unroll 1
+        for (int c = 0; c < kBoxes; ++c) {
+          const int col0 = tc.ni * BN + c * kColsPerBox;
+          if (col0 >= N) break;
+          uint8_t* box = stage0 + (nstore & 1) * BOX_BYTES;
+          if (TRACE) t0 = clock64();
+          if (lane == 0) tma_store_wait_read<1>();  // the store that used this box two boxes ago has read it
+          __syncwarp();
+          if (TRACE) wait_store += clock64() - t0;
+          if (kBf16) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v[32];
+              B200_TMEM_LD_32(v, t_row + c * 64 + half * 32);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                box_write(box, lane, half * 4 + j,
+                          make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]) * alpha, __uint_as_float(v[8 * j + 1]) * alpha),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 2]) * alpha, __uint_as_float(v[8 * j + 3]) * alpha),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 4]) * alpha, __uint_as_float(v[8 * j + 5]) * alpha),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 6]) * alpha, __uint_as_float(v[8 * j + 7]) * alpha)));
+              }
+            }
+          } else {
+            uint32_t v[32];
+            B200_TMEM_LD_32(v, t_row + c * 32);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              box_write(box, lane, j,
+                        make_uint4(__float_as_uint(__uint_as_float(v[4 * j]) * alpha), __float_as_uint(__uint_as_float(v[4 * j + 1]) * alpha),
+                                   __float_as_uint(__uint_as_float(v[4 * j + 2]) * alpha), __float_as_uint(__uint_as_float(v[4 * j + 3]) * alpha)));
+            }
+          }
+          if (c == kBoxes - 1 || col0 + kColsPerBox >= N) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M) {
+            if (EPI == EPI_F32_ACC || EPI == EPI_BF16_ACC) tma_reduce_add_2d(&tmC, box, col0, row0);
+            else tma_store_2d(&tmC, box, col0, row0);
+            tma_store_commit();
+          }
+          ++nstore;
+        }
+        continue;
+      }
+
+      // register -> global path
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tc.n0 + c * 32;
+        const int col0 = tc.ni * BN + c * 32;
         if (col0 >= N) break;
         uint32_t v[32];
         B200_TMEM_LD_32(v, t_row + c * 32);
@@ -273,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (row < M) {
           if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + (long long)row * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 7) == 0) {
+            if (col0 + 32 <= N && (ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(Cv) & 15) == 0) {
               uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -297,7 +489,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
           } else {
             float* dst = reinterpret_cast<float*>(Cv) + (long long)row * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 3) == 0) {
+            if (col0 + 32 <= N && (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(Cv) & 15) == 0) {
               float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -323,6 +515,14 @@ __global__ void __launch_bounds__(THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
     }
+    // every bulk store of this warp has left shared memory and reached global memory before the CTA exits
+    if (lane == 0) tma_store_wait<0>();
+    __syncwarp();
+    if (TRACE && q == 2 && lane == 0) {
+      trace[4] = wait_acc;
+      trace[5] = clock64() - t_begin;
+      trace[7] = wait_store;
+    }
   }
 
   // Neither CTA may free its TMEM or exit while the other can still reach into it.
@@ -335,25 +535,36 @@ __global__ void __launch_bounds__(THREADS, 1)
   }
 }
 
-template <int A_MN, int B_MN, int EPI>
-void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int M, int N, int K, long long ldc, float alpha,
-                    int* status, int max_ctas, cudaStream_t stream) {
-  auto kernel = gemm_bf16_2sm_kernel<A_MN, B_MN, EPI>;
+struct LaunchArgs {
+  CUtensorMap tmA, tmB, tmC, tmC2;
+  void* C;
+  int M, N, K;
+  long long ldc;
+  float alpha;
+  int* status;
+  int max_ctas;
+  KernelOpts opts;
+  cudaStream_t stream;
+};
+
+template <int A_MN, int B_MN, int EPI, bool TRACE>
+void launch_variant(const LaunchArgs& a) {
+  auto kernel = gemm_bf16_2sm_kernel<A_MN, B_MN, EPI, TRACE>;
   static bool configured = false;
   if (!configured) {
     check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "gemm 2sm smem attr");
     configured = true;
   }
-  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int tiles = ((a.M + 2 * BM - 1) / (2 * BM)) * ((a.N + BN - 1) / BN) * a.opts.split_k;
   int pairs = sm_count() / 2;
-  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (a.max_ctas > 0 && a.max_ctas / 2 < pairs) pairs = a.max_ctas / 2 > 0 ? a.max_ctas / 2 : 1;
   if (tiles < pairs) pairs = tiles;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
+  cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -361,38 +572,124 @@ void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, C, M, N, K, ldc, alpha, status), "gemm_bf16_2sm launch");
+  check_cuda(cudaLaunchKernelEx(&cfg, kernel, a.tmA, a.tmB, a.tmC, a.tmC2, a.C, a.M, a.N, a.K, a.ldc, a.alpha, a.status, a.opts),
+             "gemm_bf16_2sm launch");
   count_launch();
 }
 
 template <int A_MN, int B_MN>
-void launch_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int M, int N, int K, long long ldc,
-                float alpha, int* status, int max_ctas, cudaStream_t stream) {
+void launch_epi(int epi, const LaunchArgs& a) {
+  const bool trace = a.opts.trace != nullptr;
   switch (epi) {
-    case EPI_BF16: launch_variant<A_MN, B_MN, EPI_BF16>(tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream); break;
-    case EPI_F32: launch_variant<A_MN, B_MN, EPI_F32>(tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream); break;
-    case EPI_F32_ACC: launch_variant<A_MN, B_MN, EPI_F32_ACC>(tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream); break;
-    case EPI_BF16_ACC: launch_variant<A_MN, B_MN, EPI_BF16_ACC>(tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream); break;
+    case EPI_BF16:
+      if (trace) launch_variant<A_MN, B_MN, EPI_BF16, true>(a);
+      else launch_variant<A_MN, B_MN, EPI_BF16, false>(a);
+      break;
+    case EPI_F32: launch_variant<A_MN, B_MN, EPI_F32, false>(a); break;
+    case EPI_F32_ACC:
+      if (trace) launch_variant<A_MN, B_MN, EPI_F32_ACC, true>(a);
+      else launch_variant<A_MN, B_MN, EPI_F32_ACC, false>(a);
+      break;
+    case EPI_BF16_ACC: launch_variant<A_MN, B_MN, EPI_BF16_ACC, false>(a); break;
     default: throw std::runtime_error("gemm_bf16_2sm: unknown epilogue");
   }
 }
 
+// Raster: the 74 pairs that run at a time should cover a patch of the output that is as square as possible in bytes
+// of operands (its A rows and B rows are what L2 serves to all of them); a panel is `group` tiles tall and spans all
+// columns, so consecutive pairs share A within a panel column and B across the panel's rows.
+int default_group(int M, int N) {
+  const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
+  int g = 8;
+  if (n_tiles < 9) g = 16;
+  if (g > m_tiles) g = m_tiles;
+  return g > 0 ? g : 1;
+}
+
+// Split of K for the accumulating epilogues (the partial sums meet in the bulk reduction, so the split costs nothing):
+// taken when the tiles alone would leave the last wave of CTA pairs mostly idle.
+int default_split(int M, int N, int K, int pairs) {
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int k_blocks = (K + BK - 1) / BK;
+  auto efficiency = [&](int split) {
+    const int units = tiles * split;
+    const int waves = (units + pairs - 1) / pairs;
+    return (double)units / ((double)waves * pairs);
+  };
+  int best = 1;
+  double best_eff = efficiency(1);
+  for (int split = 2; split <= 4; ++split) {
+    if (k_blocks / split < 16) break;
+    const double e = efficiency(split);
+    if (e > best_eff + 0.04) {
+      best = split;
+      best_eff = e;
+    }
+  }
+  return best;
+}
+
+PairGemmTuning g_tuning;
+
 }  // namespace
+
+PairGemmTuning& pair_gemm_tuning() { return g_tuning; }
 
 // Same contract as gemm_bf16 (see gemm_bf16.cu).
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                    bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return;
   if ((lda & 7) || (ldb & 7)) throw std::runtime_error("gemm_bf16_2sm: leading dimensions of A and B must be multiples of 8");
-  const CUtensorMap tmA = a_mn ? make_tensor_map_2d_b16(A, M, K, lda, 64, BK) : make_tensor_map_2d_b16(A, K, M, lda, BK, BM);
-  const CUtensorMap tmB = b_mn ? make_tensor_map_2d_b16(B, N, K, ldb, 64, BK) : make_tensor_map_2d_b16(B, K, N, ldb, BK, BN_HALF);
-  if (a_mn) {
-    if (b_mn) launch_epi<1, 1>(epi, tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream);
-    else launch_epi<1, 0>(epi, tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream);
-  } else {
-    if (b_mn) launch_epi<0, 1>(epi, tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream);
-    else launch_epi<0, 0>(epi, tmA, tmB, C, M, N, K, ldc, alpha, status, max_ctas, stream);
+  LaunchArgs a;
+  a.tmA = a_mn ? make_tensor_map_2d_b16(A, M, K, lda, 64, BK) : make_tensor_map_2d_b16(A, K, M, lda, BK, BM);
+  a.tmB = b_mn ? make_tensor_map_2d_b16(B, N, K, ldb, 64, BK) : make_tensor_map_2d_b16(B, K, N, ldb, BK, BN_HALF);
+  const bool bf16_out = epi == EPI_BF16 || epi == EPI_BF16_ACC;
+  const int esize = bf16_out ? 2 : 4;
+  const bool c_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esize) % 16 == 0 && !g_tuning.direct_store;
+  if (c_ok) a.tmC = bf16_out ? make_tensor_map_2d_b16(C, N, M, ldc, 64, 32) : make_tensor_map_2d_f32(C, N, M, ldc, 32, 32);
+  else a.tmC = a.tmA;
+  a.tmC2 = a.tmC;
+  a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.alpha = alpha; a.status = status; a.max_ctas = max_ctas; a.stream = stream;
+  a.opts.group = g_tuning.group != 0 ? g_tuning.group : default_group(M, N);
+  a.opts.tma_store = c_ok ? 1 : 0;
+  a.opts.k_skew = g_tuning.k_skew;
+  a.opts.swiglu_i = 0;
+  a.opts.split_k = 1;
+  if (c_ok && (epi == EPI_F32_ACC || epi == EPI_BF16_ACC) && max_ctas <= 0)
+    a.opts.split_k = g_tuning.split_k > 0 ? g_tuning.split_k : default_split(M, N, K, sm_count() / 2);
+  {
+    const int k_blocks = (K + BK - 1) / BK;  // every partial sum covers at least four k-blocks
+    if (a.opts.split_k > k_blocks / 4) a.opts.split_k = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
   }
+  a.opts.trace = g_tuning.trace;
+  if (a_mn) {
+    if (b_mn) launch_epi<1, 1>(epi, a);
+    else launch_epi<1, 0>(epi, a);
+  } else {
+    if (b_mn) launch_epi<0, 1>(epi, a);
+    else launch_epi<0, 0>(epi, a);
+  }
+}
+
+// fc[M, 2I] = A[M, K] W[2I, K]^T (both halves stored) and act[M, I] = fc[:, :I] * silu(fc[:, I:]) in one kernel.
+void gemm_bf16_swiglu(const void* A, const void* W, void* fc, void* act, int M, int I, int K, long long lda, long long ldw,
+                      long long ldfc, long long ldact, int* status, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return;
+  if ((lda & 7) || (ldw & 7) || (ldfc & 7) || (ldact & 7) || (I % BN_HALF) != 0 || M < 2 * BM)
+    throw std::runtime_error("gemm_bf16_swiglu: needs I % 128 == 0, M >= 256 and leading dimensions that are multiples of 8");
+  LaunchArgs a;
+  a.tmA = make_tensor_map_2d_b16(A, K, M, lda, BK, BM);
+  a.tmB = make_tensor_map_2d_b16(W, K, 2 * (long long)I, ldw, BK, BN_HALF);
+  a.tmC = make_tensor_map_2d_b16(fc, 2 * (long long)I, M, ldfc, 64, 32);
+  a.tmC2 = make_tensor_map_2d_b16(act, I, M, ldact, 64, 32);
+  a.C = fc; a.M = M; a.N = 2 * I; a.K = K; a.ldc = ldfc; a.alpha = 1.f; a.status = status; a.max_ctas = 0; a.stream = stream;
+  a.opts.group = g_tuning.group != 0 ? g_tuning.group : default_group(M, 2 * I);
+  a.opts.tma_store = 1;
+  a.opts.k_skew = g_tuning.k_skew;
+  a.opts.swiglu_i = I;
+  a.opts.split_k = 1;
+  a.opts.trace = nullptr;
+  launch_variant<0, 0, EPI_SWIGLU, false>(a);
 }
 
 }  // namespace b200

@@ -15,6 +15,19 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long 
 // ---- gemm/gemm_bf16_2sm.cu (CTA pairs, 256 x 256 tiles)
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                    bool a_mn, bool b_mn, int epi, float alpha, int* status, int max_ctas, cudaStream_t stream);
+// fc[M, 2I] = A W^T with W = [up rows | gate rows] and act[M, I] = fc[:, :I] * silu(fc[:, I:]) from one kernel
+// (needs I % 128 == 0 and M >= 256).
+void gemm_bf16_swiglu(const void* A, const void* W, void* fc, void* act, int M, int I, int K, long long lda, long long ldw,
+                      long long ldfc, long long ldact, int* status, cudaStream_t stream);
+// Process-wide knobs of the CTA-pair kernel (0 / null = built-in choice); meant for micro-benchmarks.
+struct PairGemmTuning {
+  int group = 0;               // tile raster: > 0 row panels of that many 256-row tiles, < 0 column panels
+  int k_skew = 0;              // start the walk over K at a tile-dependent k-block
+  int direct_store = 0;        // epilogue writes from registers instead of bulk tensor stores
+  int split_k = 0;             // accumulating epilogues: partial sums over K per tile (0 = built-in choice, 1 = none)
+  long long* trace = nullptr;  // device buffer of 8 cycle counters per CTA, filled by the traced build of the kernel
+};
+PairGemmTuning& pair_gemm_tuning();
 
 // ---- ops/norm.cu
 int rmsnorm_bwd_partial_rows(int T);

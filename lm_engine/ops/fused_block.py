@@ -54,9 +54,15 @@ class FusedDenseBlockFn(torch.autograd.Function):
         n2, rstd2, h = C.rmsnorm_fwd(a, x, ln2_w, eps, True)
         del a
         fc = torch.empty(T, w_fc.shape[0], device=x.device, dtype=x.dtype)
-        C.gemm(n2, w_fc, fc, False, False, False, 1.0, st, 0)
+        inter = w_fc.shape[0] // 2
+        if inter % 128 == 0 and T >= 256:
+            # up-projection with the activation in its epilogue: fc is written for backward, never read back here
+            act = torch.empty(T, inter, device=x.device, dtype=x.dtype)
+            C.gemm_swiglu(n2, w_fc, fc, act, st)
+        else:
+            C.gemm(n2, w_fc, fc, False, False, False, 1.0, st, 0)
+            act = C.swiglu_fwd(fc)
         del n2
-        act = C.swiglu_fwd(fc)
         m = torch.empty(T, H, device=x.device, dtype=x.dtype)
         C.gemm(act, w_proj, m, False, False, False, 1.0, st, 0)
         del act

@@ -44,25 +44,109 @@ def bench_gemm(args) -> None:
     flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
     shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes] if args.shapes else [
         (8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 8192, 8192), (4096, 128256, 4096)]
+    trace = torch.zeros(8 * 148, dtype=torch.int64, device="cuda") if args.trace else None
     for M, N, K in shapes:
         flops = 2.0 * M * N * K
         for layout in args.layouts:
             a_mn, b_mn = layout[0] == "t", layout[1] == "n"
             a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
             b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
-            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            record = dict(op="gemm", layout=layout, m=M, n=N, k=K)
-            for name, variant in (("cta1", 1), ("cta_pair", 2)):
-                if args.variant not in ("all", name):
+            out = torch.empty(M, N, device="cuda", dtype=torch.float32 if args.accumulate else torch.bfloat16)
+            record = dict(op="gemm", layout=layout, m=M, n=N, k=K, accumulate=args.accumulate)
+            if args.variant in ("all", "cta1"):
+                ms = _time(lambda: C.gemm(a, b, out, a_mn, b_mn, args.accumulate, 1.0, st, 0, 1), args.iters, args.warmup, flush)
+                record["cta1_ms"], record["cta1_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+            if args.variant in ("all", "cta_pair"):
+                # knobs of the CTA-pair kernel: raster group (0 = built-in choice), k skew, register-store epilogue
+                configs = [(group, skew, direct, split) for group in args.groups for skew in args.k_skew
+                           for direct in ([False, True] if args.direct_store else [False]) for split in args.split_k]
+
+                def key_of(group, skew, direct, split=0):
+                    return ("cta_pair" + (f"_g{group}" if group else "") + (f"_s{skew}" if skew else "") + ("_direct" if direct else "")
+                            + (f"_k{split}" if split else ""))
+
+                def run_pair(group, skew, direct, split=0):
+                    C.gemm_tuning(group, skew, direct, trace, split)
+                    C.gemm(a, b, out, a_mn, b_mn, args.accumulate, 1.0, st, 0, 2)
+
+                if args.interleave:
+                    # all candidates (and the library) take turns launch by launch after a warm-up long enough to reach the
+                    # power-capped clock, so that clock drift during the sweep hits every candidate alike
+                    am, bm = (a.t() if a_mn else a), (b if b_mn else b.t())
+                    out_lib = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+                    end = torch.cuda.Event(enable_timing=True)
+                    begin = torch.cuda.Event(enable_timing=True)
+                    begin.record()
+                    while True:
+                        for _ in range(20):
+                            run_pair(0, 0, False)
+                        end.record()
+                        end.synchronize()
+                        if begin.elapsed_time(end) > args.heat_ms:
+                            break
+                    samples: dict[str, list[float]] = {}
+                    for _ in range(args.iters):
+                        for cfg in configs + ["cublas"]:
+                            flush.zero_() if flush is not None else None
+                            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            e0.record()
+                            if cfg == "cublas":
+                                torch.matmul(am, bm, out=out_lib)
+                            else:
+                                run_pair(*cfg)
+                            e1.record()
+                            e1.synchronize()
+                            samples.setdefault(cfg if cfg == "cublas" else key_of(*cfg), []).append(e0.elapsed_time(e1))
+                    for key, values in samples.items():
+                        values.sort()
+                        ms = values[len(values) // 2]
+                        record[f"{key}_ms"], record[f"{key}_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+                    C.gemm_tuning(0, 0, False, None)
+                    record["status"] = int(st.item())
+                    _emit(record)
                     continue
-                ms = _time(lambda: C.gemm(a, b, out, a_mn, b_mn, False, 1.0, st, 0, variant), args.iters, args.warmup, flush)
-                record[f"{name}_ms"], record[f"{name}_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+                for group, skew, direct, split in configs:
+                    ms = _time(lambda: run_pair(group, skew, direct, split), args.iters, args.warmup, flush)
+                    key = key_of(group, skew, direct, split)
+                    record[f"{key}_ms"], record[f"{key}_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+                    if trace is not None:
+                        # cycle counters of the last launch, averaged over the leader CTAs: share of the MMA
+                        # thread's time spent waiting for operands / for a free accumulator, and of the
+                        # epilogue's time spent waiting for a finished accumulator / for its store boxes
+                        t = trace.view(148, 8)[0::2].double()
+                        total, epi_total = t[:, 3].clamp(min=1), t[:, 5].clamp(min=1)
+                        record[f"{key}_trace"] = dict(
+                            mma_wait_operands=round((t[:, 1] / total).mean().item(), 3),
+                            mma_wait_accumulator=round((t[:, 2] / total).mean().item(), 3),
+                            producer_wait_stage=round((t[:, 0] / total).mean().item(), 3),
+                            epilogue_wait_accumulator=round((t[:, 4] / epi_total).mean().item(), 3),
+                            epilogue_wait_store=round((t[:, 7] / epi_total).mean().item(), 3),
+                            mma_cycles=int(total.mean().item()), tiles_per_pair=round(t[:, 6].mean().item(), 2))
+                C.gemm_tuning(0, 0, False, None)
             if not args.profile:
                 am, bm = (a.t() if a_mn else a), (b if b_mn else b.t())
-                ms = _time(lambda: torch.matmul(am, bm, out=out), args.iters, args.warmup, flush)
+                out_lib = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+                ms = _time(lambda: torch.matmul(am, bm, out=out_lib), args.iters, args.warmup, flush)
                 record["cublas_ms"], record["cublas_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
             record["status"] = int(st.item())
             _emit(record)
+    if args.swiglu:
+        # c_fc GEMM with the SwiGLU activation in its epilogue against GEMM followed by the stand-alone kernel
+        T, H, I = args.tokens, args.hidden, args.intermediate
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02
+        fc = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+        act = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * T * 2 * I * H
+
+        def unfused():
+            C.gemm(x, w, fc, False, False, False, 1.0, st, 0, 2)
+            return C.swiglu_fwd(fc)
+
+        ms_f = _time(lambda: C.gemm_swiglu(x, w, fc, act, st), args.iters, args.warmup, flush)
+        ms_u = _time(unfused, args.iters, args.warmup, flush)
+        _emit(dict(op="gemm_swiglu", tokens=T, hidden=H, intermediate=I, fused_ms=round(ms_f, 4), fused_tflops=round(flops / ms_f / 1e9, 1),
+                   gemm_then_swiglu_ms=round(ms_u, 4), status=int(st.item())))
 
 
 def bench_attention(args) -> None:
@@ -234,6 +318,15 @@ def main() -> None:
     parser.add_argument("--layouts", nargs="*", default=["nt"], help="gemm: nt (y = x w^T), nn (dgrad), tn (wgrad)")
     parser.add_argument("--variant", default="all", choices=["all", "cta1", "cta_pair"])
     parser.add_argument("--direction", default="all", choices=["all", "fwd", "bwd"])
+    parser.add_argument("--groups", nargs="*", type=int, default=[0], help="gemm: raster groups of the CTA-pair kernel to sweep (0 = built-in)")
+    parser.add_argument("--k-skew", nargs="*", type=int, default=[0], help="gemm: k-block skews of the CTA-pair kernel to sweep")
+    parser.add_argument("--split-k", nargs="*", type=int, default=[0], help="gemm --accumulate: splits of K to sweep (0 = built-in, 1 = none)")
+    parser.add_argument("--direct-store", action="store_true", help="gemm: also time the register-store epilogue")
+    parser.add_argument("--accumulate", action="store_true", help="gemm: fp32 accumulate into the output (weight-gradient form)")
+    parser.add_argument("--trace", action="store_true", help="gemm: report where the MMA and epilogue threads of the CTA-pair kernel wait")
+    parser.add_argument("--interleave", action="store_true", help="gemm: candidates and the library take turns launch by launch after heating the GPU to its power-capped clock")
+    parser.add_argument("--heat-ms", type=float, default=1500.0, help="gemm --interleave: length of the warm-up under load")
+    parser.add_argument("--swiglu", action="store_true", help="gemm: also time the c_fc GEMM with the SwiGLU epilogue")
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--profile", action="store_true", help="no comparison library, no L2 flush kernel")

@@ -143,42 +143,83 @@ def _make_transfer_groups(world: int) -> dict:
 
 
 class _Mailbox:
-    """Point-to-point transfers of one training step."""
+    """Point-to-point transfers of one training step.
+
+    What crosses a stage boundary (hidden states + the running auxiliary loss, or their gradients) travels as ONE
+    message: the scalar is appended to the flattened hidden states as raw fp32 bits. Receives are posted ahead of
+    time (``prefetch``) so that a transfer runs under the compute of the action before the one that consumes it;
+    ``recv`` only waits. Sends are asynchronous and are waited for at the end of the step.
+    """
 
     def __init__(self, schedule: PipelineSchedule) -> None:
         self.schedule = schedule
         self.pending = []
         self.local: dict[tuple, list[torch.Tensor]] = {}
+        self.posted: dict[tuple, tuple] = {}
+
+    @staticmethod
+    def _tail(dtype: torch.dtype) -> int:
+        return 4 // torch.empty((), dtype=dtype).element_size() if dtype != torch.float64 else 1
+
+    @classmethod
+    def _pack(cls, hidden: torch.Tensor, scalar: torch.Tensor) -> torch.Tensor:
+        tail = cls._tail(hidden.dtype)
+        flat = torch.empty(hidden.numel() + tail, device=hidden.device, dtype=hidden.dtype)
+        flat[: hidden.numel()].copy_(hidden.detach().reshape(-1))
+        if hidden.dtype == torch.float64:
+            flat[-1] = scalar.detach().double()
+        else:
+            flat[hidden.numel() :].view(torch.float32).copy_(scalar.detach().float().reshape(1))
+        return flat
+
+    @classmethod
+    def _unpack(cls, flat: torch.Tensor, like: torch.Tensor) -> list[torch.Tensor]:
+        hidden = flat[: like.numel()].view(like.shape)
+        if like.dtype == torch.float64:
+            scalar = flat[-1].float()
+        else:
+            scalar = flat[like.numel() :].view(torch.float32).reshape(())
+        return [hidden, scalar]
+
+    def _route(self, src_stage: int, dst_stage: int, micro: int, direction: str):
+        s = self.schedule
+        src, dst = s.owner(src_stage), s.owner(dst_stage)
+        tag = (dst_stage * s.microbatches + micro) * 2 + (0 if direction == FORWARD else 1)
+        return src, dst, s.groups.get((src, dst, direction)), tag
 
     def send(self, tensors: list[torch.Tensor], src_stage: int, dst_stage: int, micro: int, direction: str) -> None:
-        s = self.schedule
-        src, dst = s.owner(src_stage), s.owner(dst_stage)
-        key = (dst_stage, micro, direction)
+        src, dst, group, tag = self._route(src_stage, dst_stage, micro, direction)
         if src == dst:
-            self.local[key] = [t.detach() for t in tensors]
+            self.local[(dst_stage, micro, direction)] = [t.detach() for t in tensors]
             return
-        group = s.groups.get((src, dst, direction))
-        tag = (dst_stage * s.microbatches + micro) * 2 + (0 if direction == FORWARD else 1)
-        for i, t in enumerate(tensors):
-            self.pending.append(dist.isend(t.detach().contiguous(), dst=s.global_rank_of[dst], group=group, tag=tag * 4 + i))
+        flat = self._pack(tensors[0], tensors[1])
+        self.pending.append((dist.isend(flat, dst=self.schedule.global_rank_of[dst], group=group, tag=tag), flat))
+
+    def prefetch(self, like: torch.Tensor, src_stage: int, dst_stage: int, micro: int, direction: str) -> None:
+        """Post the receive for ``(dst_stage, micro, direction)`` now; ``like`` gives shape and dtype of the hidden states."""
+        key = (dst_stage, micro, direction)
+        src, dst, group, tag = self._route(src_stage, dst_stage, micro, direction)
+        if src == dst or key in self.posted:
+            return
+        flat = torch.empty(like.numel() + self._tail(like.dtype), device=like.device, dtype=like.dtype)
+        work = dist.irecv(flat, src=self.schedule.global_rank_of[src], group=group, tag=tag)
+        self.posted[key] = (work, flat, like)
 
     def recv(self, like: list[torch.Tensor], src_stage: int, dst_stage: int, micro: int, direction: str) -> list[torch.Tensor]:
-        s = self.schedule
-        src, dst = s.owner(src_stage), s.owner(dst_stage)
         key = (dst_stage, micro, direction)
+        src, dst, _, _ = self._route(src_stage, dst_stage, micro, direction)
         if src == dst:
             return self.local.pop(key)
-        group = s.groups.get((src, dst, direction))
-        tag = (dst_stage * s.microbatches + micro) * 2 + (0 if direction == FORWARD else 1)
-        out = [torch.empty_like(t) for t in like]
-        for i, t in enumerate(out):
-            dist.irecv(t, src=s.global_rank_of[src], group=group, tag=tag * 4 + i).wait()
-        return out
+        self.prefetch(like[0], src_stage, dst_stage, micro, direction)
+        work, flat, hidden_like = self.posted.pop(key)
+        work.wait()
+        return self._unpack(flat, hidden_like)
 
     def finish(self) -> None:
-        for work in self.pending:
+        for work, _ in self.pending:
             work.wait()
         self.pending.clear()
+        assert not self.posted, "a posted pipeline receive was never consumed"
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -211,8 +252,15 @@ def run_stage(wrapper, inputs: dict, labels, boundary_input, lm_loss_multiplier:
 
 
 def pipeline_train_step(model_container, schedule: PipelineSchedule, optimizer_container, lr_scheduler_container, train_dataloader,
-                        gradient_clipping, sequence_length: int | None = None, lm_loss_multiplier: float = 1) -> MetricsTrackingDict:
+                        gradient_clipping, sequence_length: int | None = None, lm_loss_multiplier: float | None = None) -> MetricsTrackingDict:
+    """One optimizer step under pipeline parallelism. The last stage's loss is a sum over tokens scaled by
+    ``lm_loss_multiplier``; when it is not given it is ``1 / (micro_batch_size * sequence_length)``, the normalisation
+    of the step without pipeline parallelism (parity: lm_engine/distributed.py:398 of the reference)."""
     from ..data import get_next_batch
+
+    if lm_loss_multiplier is None:
+        mbs = next(iter(schedule.stage_to_wrapper.values())).micro_batch_size
+        lm_loss_multiplier = 1.0 if sequence_length is None else 1.0 / (mbs * sequence_length)
 
     # the loader yields either all micro-batches of the step at once or one micro-batch per item
     micro_batch_size = next(iter(schedule.stage_to_wrapper.values())).micro_batch_size
@@ -228,21 +276,43 @@ def pipeline_train_step(model_container, schedule: PipelineSchedule, optimizer_c
     assert len(micro_batches) == schedule.microbatches, "the loader's batch is not a whole number of micro-batches"
 
     mailbox = _Mailbox(schedule)
-    prepared: dict[tuple[int, int], dict] = {}
+    prepared: dict[tuple[int, int], tuple] = {}
     live: dict[tuple[int, int], tuple] = {}  # (stage, micro) -> (boundary inputs that need gradients, outputs)
     metrics = MetricsTrackingDict({})
     last = schedule.num_stages - 1
 
-    for kind, stage, micro in schedule.actions:
-        wrapper = schedule.stage_to_wrapper[stage]
-        if kind == FORWARD:
+    def prepare(stage: int, micro: int):
+        key = (stage, micro)
+        if key not in prepared:
+            wrapper = schedule.stage_to_wrapper[stage]
             inputs = wrapper._prepare_model_inputs({"text": micro_batches[micro]})
             labels = inputs.pop("labels")
-            prepared[(stage, micro)] = inputs
+            prepared[key] = (inputs, labels)
+        return prepared[key]
+
+    def post_receive(index: int) -> None:
+        # the receive of action `index` is posted while the action before it computes
+        if index >= len(schedule.actions):
+            return
+        kind, stage, micro = schedule.actions[index]
+        wrapper = schedule.stage_to_wrapper[stage]
+        if kind == FORWARD and stage > 0:
+            inputs, _ = prepare(stage, micro)
+            mailbox.prefetch(_boundary_like(wrapper, inputs)[0], stage - 1, stage, micro, FORWARD)
+        elif kind == BACKWARD and stage < last and (stage, micro) in prepared:
+            inputs, _ = prepared[(stage, micro)]
+            mailbox.prefetch(_boundary_like(wrapper, inputs)[0], stage + 1, stage, micro, BACKWARD)
+
+    post_receive(0)
+    for index, (kind, stage, micro) in enumerate(schedule.actions):
+        post_receive(index + 1)
+        wrapper = schedule.stage_to_wrapper[stage]
+        if kind == FORWARD:
+            inputs, labels = prepare(stage, micro)
             boundary = None
             if stage > 0:
                 hidden, aux = mailbox.recv(_boundary_like(wrapper, inputs), stage - 1, stage, micro, FORWARD)
-                boundary = (hidden.requires_grad_(True), aux.requires_grad_(True))
+                boundary = (hidden.requires_grad_(True), aux.clone().requires_grad_(True))
             output = run_stage(wrapper, inputs, labels, boundary, lm_loss_multiplier)
             if stage < last:
                 hidden_out, aux_out = output

@@ -89,11 +89,14 @@ def train_step_without_pipeline_parallel(
 
 
 def train_step_with_pipeline_parallel(model_container, pipeline_schedule, optimizer_container, lr_scheduler_container,
-                                      train_dataloader, gradient_clipping, sequence_length) -> MetricsTrackingDict:
+                                      train_dataloader, gradient_clipping, sequence_length,
+                                      lm_loss_multiplier: float | None = None) -> MetricsTrackingDict:
+    """One optimizer step through the pipeline schedule; the loss is normalised by ``lm_loss_multiplier``
+    (``1 / (micro_batch_size * sequence_length)`` when not given), as in the step without pipeline parallelism."""
     from .parallel.pipeline import pipeline_train_step
 
     return pipeline_train_step(model_container, pipeline_schedule, optimizer_container, lr_scheduler_container,
-                               train_dataloader, gradient_clipping, sequence_length)
+                               train_dataloader, gradient_clipping, sequence_length, lm_loss_multiplier=lm_loss_multiplier)
 
 
 def track_val_metrics(global_step: int, experiments_tracker, metrics_tracker: MetricsTrackingDict, group_name: str | None = None) -> None:
@@ -173,7 +176,7 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
             else:
                 loss_dict = train_step_with_pipeline_parallel(
                     model_container, pipeline_schedule, optimizer_container, lr_scheduler_container, train_dataloader,
-                    tp.gradient_clipping, sequence_length)
+                    tp.gradient_clipping, sequence_length, lm_loss_multiplier=lm_loss_multiplier)
             metrics_tracker = metrics_tracker + loss_dict
             if prof is not None and hasattr(prof, "step"):
                 prof.step()

@@ -105,9 +105,10 @@ def main() -> None:
         if pipeline_schedule is None:
             metrics = train_step_without_pipeline_parallel(container, optimizers, schedulers, loader, 1.0, lm_loss_multiplier=multiplier)
         else:
-            from lm_engine.parallel.pipeline import pipeline_train_step
+            # the entry point's own call: the loss normalisation is derived from micro-batch size and sequence length
+            from lm_engine.pretrain import train_step_with_pipeline_parallel
 
-            metrics = pipeline_train_step(container, pipeline_schedule, optimizers, schedulers, loader, 1.0, 128, lm_loss_multiplier=multiplier)
+            metrics = train_step_with_pipeline_parallel(container, pipeline_schedule, optimizers, schedulers, loader, 1.0, 128)
         for key in list(metrics.keys()):
             metrics[key] = float(metrics[key])
         grad_norm = metrics["grad_norm"]

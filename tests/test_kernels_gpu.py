@@ -80,6 +80,69 @@ def test_gemm_strided_views(C):
     assert outbuf[:, :128].abs().sum().item() == 0 and outbuf[:, 512:].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("group,k_skew,direct,split", [(1, 0, False, 1), (3, 0, False, 2), (-2, 0, False, 3), (16, 5, False, 0), (0, 0, True, 0)])
+def test_gemm_pair_raster_and_epilogue_variants(C, group, k_skew, direct, split):
+    # every raster / k-skew / epilogue choice of the CTA-pair kernel computes the same product, including on ragged edges
+    torch.manual_seed(3)
+    try:
+        for (M, N, K) in [(1100, 1352, 520), (2048, 768, 1024)]:
+            a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+            ref = a.float() @ b.float().t()
+            st = _status()
+            C.gemm_tuning(group, k_skew, direct, None, split)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            C.gemm(a, b, out, False, False, False, 1.0, st, 0, 2)
+            assert _rel_err(out, ref) < 6e-3
+            base = torch.randn(M, N, device="cuda", dtype=torch.float32)
+            acc = base.clone()
+            C.gemm(a, b, acc, False, False, True, 1.0, st, 0, 2)
+            assert _rel_err(acc, base + ref) < 1e-5
+            base16 = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+            acc16 = base16.clone()
+            C.gemm(a, b, acc16, False, False, True, 1.0, st, 0, 2)
+            assert _rel_err(acc16, base16.float() + ref) < 8e-3
+            assert st.item() == 0
+    finally:
+        C.gemm_tuning(0, 0, False, None)
+
+
+def test_gemm_pair_unaligned_output_takes_the_register_path(C):
+    torch.manual_seed(4)
+    M, N, K = 512, 300, 256
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    buf = torch.zeros(M, N + 3, device="cuda", dtype=torch.bfloat16)  # row stride 303 elements: no tensor map possible
+    out = buf[:, :N]
+    st = _status()
+    C.gemm(a, b, out, False, False, False, 1.0, st, 0, 2)
+    assert st.item() == 0
+    assert _rel_err(out, a.float() @ b.float().t()) < 6e-3
+    assert buf[:, N:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("T,H,I", [(256, 256, 128), (1000, 512, 384), (4096, 1024, 2048)])
+def test_gemm_with_swiglu_epilogue(C, T, H, I):
+    torch.manual_seed(5)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * (H**-0.5)
+    fc = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    act = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    C.gemm_swiglu(x, w, fc, act, st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    ref_fc = x.float() @ w.float().t()
+    assert _rel_err(fc, ref_fc) < 6e-3
+    up, gate = ref_fc[:, :I], ref_fc[:, I:]
+    assert _rel_err(act, up * torch.nn.functional.silu(gate)) < 1e-2
+    # same bits as the two-kernel path: the activation is computed from the bf16-rounded projection
+    fc2 = torch.empty_like(fc)
+    C.gemm(x, w, fc2, False, False, False, 1.0, st, 0, 2)
+    assert torch.equal(fc, fc2)
+    assert torch.equal(act, C.swiglu_fwd(fc2))
+
+
 @pytest.mark.parametrize("T,H", [(7, 64), (33, 4096), (5, 2560), (3, 8192), (2, 16384)])
 def test_rmsnorm(C, T, H):
     torch.manual_seed(0)
