@@ -12,6 +12,8 @@
 //   returns 0 on success; otherwise a non-zero code and a NUL-terminated explanation in error_message.
 //
 // Limits and rules:
+//   * dy, h, w, rstd, dh and dw must not be NULL (code 6); dy, h, w, dres, dh and dw must be 16-byte aligned and rstd
+//     4-byte aligned (code 7): the kernels use 16-byte accesses, so a bad pointer is refused here, before any launch.
 //   * H must be a multiple of 8 and at most B200_NOALLOC_RMSNORM_MAX_H; larger rows are rejected (code 2).
 //   * The scratch is one array of B200_NOALLOC_RMSNORM_MAX_ROWS x B200_NOALLOC_RMSNORM_MAX_H floats (5 MiB) in the
 //     library image; every GPU that loads the library holds it until the process exits.

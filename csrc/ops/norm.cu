@@ -276,6 +276,28 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* h, const voi
     return 2;
   }
   if (T == 0) return 0;
+  {
+    // The kernels read and write 16 bytes at a time: a missing or misaligned pointer would otherwise surface as a
+    // device-side fault instead of an error code.
+    const void* required[] = {dy, h, w, rstd, dh, dw};
+    for (const void* p : required) {
+      if (p == nullptr) {
+        copy_message(error_message, error_message_len, "b200_rmsnorm_bwd_noalloc: dy, h, w, rstd, dh and dw must not be NULL");
+        return 6;
+      }
+    }
+    const void* vectors[] = {dy, h, w, dres, dh, dw};
+    for (const void* p : vectors) {
+      if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) {
+        copy_message(error_message, error_message_len, "b200_rmsnorm_bwd_noalloc: dy, h, w, dres, dh and dw must be 16-byte aligned");
+        return 7;
+      }
+    }
+    if ((reinterpret_cast<uintptr_t>(rstd) & 3u) != 0) {
+      copy_message(error_message, error_message_len, "b200_rmsnorm_bwd_noalloc: rstd must be 4-byte aligned");
+      return 7;
+    }
+  }
 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

@@ -110,12 +110,58 @@ def _as_expert_sharded(local: torch.Tensor, engine) -> torch.Tensor:
     return DTensor.from_local(local.contiguous(), mesh, [Shard(0)], run_check=False, shape=torch.Size(shape), stride=stride)
 
 
-def _view(unit, full_slot: torch.Tensor, engine) -> torch.Tensor:
-    return _as_expert_sharded(full_slot, engine) if getattr(unit, "local_only", False) else _as_sharded(full_slot, engine)
+def _tp_world() -> int:
+    return ProcessGroupManager.get_tensor_parallel_world_size() if ProcessGroupManager.is_initialized() else 1
+
+
+def _as_tp_sharded(local: torch.Tensor, dim: int, engine) -> torch.Tensor:
+    """A tensor-parallel parameter: every tensor-parallel rank holds another block along ``dim``. On disk it is ONE
+    tensor of the full shape, the ranks' blocks concatenated along ``dim`` in rank order (what a ``Shard(dim)`` DTensor
+    over the ``tp`` mesh dimension means, and the form the reference writes; ``fix_unsharded_state_dict`` turns it into
+    the single-device layout for gated and fused projections). Over the data-parallel dimensions the block is sharded
+    on dim 0 when that is a different dimension, else replicated (one data-parallel rank writes it)."""
+    from torch.distributed.tensor import DTensor, Replicate, Shard
+
+    tp = _tp_world()
+    local = local.contiguous()
+    shape = list(local.shape)
+    shape[dim] *= tp
+    stride = torch.empty(shape, device="meta").stride()
+    names, placements = [], []
+    if engine.replica_world > 1:
+        names.append("ddp")
+        placements.append(Replicate())
+    if engine.shard_world > 1:
+        names.append("fsdp")
+        if dim != 0 and local.shape[0] >= engine.shard_world:
+            placements.append(Shard(0))
+            local = _dim0_chunk(local, engine.shard_world, engine.shard_rank)
+        else:
+            placements.append(Replicate())
+    names.append("tp")
+    placements.append(Shard(dim))
+    mesh = ProcessGroupManager.get_mesh()[tuple(names)] if len(names) > 1 else ProcessGroupManager.get_mesh()["tp"]
+    return DTensor.from_local(local, mesh, placements, run_check=False, shape=torch.Size(shape), stride=stride)
+
+
+def _view(unit, slot, full_slot: torch.Tensor, engine) -> torch.Tensor:
+    if getattr(unit, "local_only", False):
+        return _as_expert_sharded(full_slot, engine)
+    dim = getattr(slot.param, "_tp_shard_dim", None)
+    if dim is not None and _tp_world() > 1 and _distributed():
+        return _as_tp_sharded(full_slot, dim % max(full_slot.dim(), 1), engine)
+    return _as_sharded(full_slot, engine)
 
 
 def _local_value(unit, value: torch.Tensor, engine) -> torch.Tensor:
-    """What this rank keeps of a loaded tensor: everything, or (expert-parallel units) its own experts."""
+    """What this rank keeps of a loaded tensor: everything, its own experts (expert-parallel units), or its own
+    tensor-parallel block (a DTensor sharded over ``tp`` is gathered over the data-parallel dimensions only)."""
+    if isinstance(value, torch.Tensor) and hasattr(value, "placements") and "tp" in (value.device_mesh.mesh_dim_names or ()):
+        from torch.distributed.tensor import Replicate
+
+        names = value.device_mesh.mesh_dim_names
+        target = [p if n == "tp" else Replicate() for n, p in zip(names, value.placements)]
+        return value.redistribute(value.device_mesh, target).to_local()
     full = _to_full(value) if isinstance(value, torch.Tensor) else value
     if getattr(unit, "local_only", False) and engine.shard_world > 1 and full.dim() > 0:
         return full.chunk(engine.shard_world, dim=0)[engine.shard_rank]
@@ -162,7 +208,7 @@ def get_model_state_dict(model_container) -> dict[str, torch.Tensor]:
         for unit in engine.units:
             full = _unit_full_fp32(unit, engine, "master")
             for slot in unit.slots:
-                out[slot.name] = _view(unit, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
+                out[slot.name] = _view(unit, slot, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
             del full
     return out
 
@@ -215,7 +261,7 @@ def get_optimizer_state_dict(model_container, optimizer_container) -> dict[str, 
             fulls = {f: _unit_full_fp32(unit, engine, f, optimizer) for f in fields}
             for slot in unit.slots:
                 for f, full in fulls.items():
-                    out[f"state.{slot.name}.{f}"] = _view(unit, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
+                    out[f"state.{slot.name}.{f}"] = _view(unit, slot, full[slot.offset : slot.offset + slot.numel].view(slot.shape).clone(), engine)
                 out[f"state.{slot.name}.step"] = torch.tensor(float(step_of_group_name.get(slot.group, 0)))
                 for key, value in hyper_of_group_name.get(slot.group, {}).items():
                     out[f"param_groups.{slot.name}.{key}"] = value
@@ -490,18 +536,18 @@ def load_checkpoint_for_inference(args, mode: Mode, use_meta: bool = False):
             ProcessGroupManager.set_dummy_pipeline_parallel_world_size(1), ProcessGroupManager.set_dummy_pipeline_parallel_rank(0):
         container = get_model_container(training_args, Mode.inference if mode != Mode.unsharding else Mode.unsharding)
     wrapper = container[0]
-    target = {k: v for k, v in wrapper.state_dict().items() if not k.startswith("teacher_model.")}
-    state = {k: torch.empty(v.shape, dtype=torch.float32) for k, v in target.items()}
-
+    # tensors are allocated with the shapes on disk: a tensor-parallel run writes every split parameter as the
+    # rank-order concatenation of its blocks (padded vocabulary, q_attn / kv_attn for multi-query attention), which
+    # `fix_unsharded_state_dict` turns into the single-device layout afterwards
     combined = os.path.isdir(_model_optimizer_path(load_path))
-    if combined:
-        holder = {"state": {"model": state}}
-        dcp.load(holder, checkpoint_id=_model_optimizer_path(load_path), no_dist=True)
-        state = holder["state"]["model"]
-    else:
-        holder = {"state": state}
-        dcp.load(holder, checkpoint_id=_model_path(load_path), no_dist=True)
-        state = holder["state"]
+    store = _model_optimizer_path(load_path) if combined else _model_path(load_path)
+    prefix = "state.model." if combined else "state."
+    saved = dcp.FileSystemReader(store).read_metadata().state_dict_metadata
+    state = {k[len(prefix):]: torch.empty(tuple(v.size), dtype=torch.float32) for k, v in saved.items()
+             if k.startswith(prefix) and hasattr(v, "size") and not k[len(prefix):].startswith("teacher_model.")}
+    holder = {"state": {"model": state}} if combined else {"state": state}
+    dcp.load(holder, checkpoint_id=store, no_dist=True)
+    state = holder["state"]["model"] if combined else holder["state"]
     if saved_tp > 1:
         from ..hf_models.tp_weights import fix_unsharded_state_dict
 

@@ -24,7 +24,7 @@ from .kernels import enable_kernels
 from .model_wrapper import get_model_container
 from .optimization import get_learning_rate, get_optimizer_container, get_scheduler_container
 from .pretrain import set_seed
-from .train_utils import all_reduce_metrics_tracker, get_torch_profiler, track_metrics
+from .train_utils import all_reduce_metrics_tracker, check_device_health, get_torch_profiler, track_metrics
 from .utils import (
     ExperimentsTracker,
     MetricsTrackingDict,
@@ -112,6 +112,7 @@ def train(args: TrainingArgs, model_container, optimizer_container, lr_scheduler
                 prof.step()
             bar.update()
             if global_step % args.logging_args.log_interval == 0:
+                check_device_health()
                 metrics_tracker = metrics_tracker / args.logging_args.log_interval
                 metrics_tracker["learning_rate"] = get_learning_rate(model_container, lr_scheduler_container)
                 track_metrics(global_step, experiments_tracker, metrics_tracker, context="train")
@@ -119,6 +120,7 @@ def train(args: TrainingArgs, model_container, optimizer_container, lr_scheduler
             if tp.eval_during_training and (global_step % tp.eval_interval == 0 or global_step == tp.num_training_steps):
                 evaluate(val_dataloader, model_container, global_step, experiments_tracker)
             if global_step % args.save_args.save_interval == 0 or global_step == tp.num_training_steps:
+                check_device_health()  # never write a checkpoint of a step that ran on partial data
                 save_checkpoint(args, model_container, optimizer_container, lr_scheduler_container, train_dataloader,
                                 experiments_tracker, global_step)
     ensure_last_checkpoint_is_saved()

@@ -57,6 +57,11 @@ def get_autoregressive_language_modeling_loss(
     if reduction not in ("sum", "mean"):
         raise ValueError(f"unexpected reduction ({reduction})")
     fused = lm_logits is None
+    if fused and tensor_parallel_enabled:
+        # the LM head is split over the vocabulary under tensor parallelism: a softmax over this rank's slice alone,
+        # with labels that are not offset, would be silently wrong (the reference asserts the same)
+        raise ValueError("fused linear + cross entropy cannot be combined with tensor parallelism; pass the "
+                         "vocabulary-parallel logits instead")
     x = hidden_states if fused else lm_logits
 
     if use_padding_free_transformer:

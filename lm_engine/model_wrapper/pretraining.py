@@ -90,7 +90,9 @@ class ModelWrapperForPretraining(ModelWrapper):
         return self.get_loss(output, labels, lm_loss_multiplier=lm_loss_multiplier)
 
     def get_loss(self, model_outputs, labels: torch.Tensor, lm_loss_multiplier: float = 1) -> dict:
-        fused = is_kernel_allowed(Kernel.fused_linear_cross_entropy_cute) and self.is_custom_model
+        # under tensor parallelism the LM head is vocabulary-parallel: its logits go to the vocabulary-parallel loss
+        fused = (is_kernel_allowed(Kernel.fused_linear_cross_entropy_cute) and self.is_custom_model
+                 and not ProcessGroupManager.is_tensor_parallel_enabled())
         hint = None
         if fused and self.training and torch.is_grad_enabled():
             ga = StepTracker.get_gradient_accumulation_steps() or 1

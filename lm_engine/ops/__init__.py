@@ -50,12 +50,20 @@ def status_word(device: torch.device | None = None) -> torch.Tensor:
     return _STATUS[index]
 
 
+STATUS_GRAD_SCALE_MISMATCH = 6  # fused linear + cross entropy: upstream gradient differs from the promised scale
+
+
 def check_status() -> None:
-    """Host-side check of the status words (synchronises); raises if any kernel reported a timeout."""
+    """Host-side check of the status words (synchronises); raises if any kernel reported a timeout or a violated
+    assumption."""
     for index, word in _STATUS.items():
         code = int(word.item())
         if code != 0:
             word.zero_()
+            if code == STATUS_GRAD_SCALE_MISMATCH:
+                raise RuntimeError(f"cuda:{index}: the fused linear + cross entropy was promised a gradient scale "
+                                   "(grad_scale_hint) that differs from the gradient it received; its weight and input "
+                                   "gradients of the steps since the last check are wrong")
             raise RuntimeError(f"a kernel on cuda:{index} gave up waiting (status {code})")
 
 
@@ -321,6 +329,8 @@ class _FusedLinearCrossEntropyFn(torch.autograd.Function):
         ctx.dw = dw
         ctx.accumulated_in_place = target is not None
         ctx.trusted = trusted
+        ctx.grad_scale = gs
+        ctx.status = st
         ctx.weight_dtype = weight.dtype
         return loss_rows.sum()
 
@@ -336,7 +346,13 @@ class _FusedLinearCrossEntropyFn(torch.autograd.Function):
         if dw is not None:
             dw = dw.to(ctx.weight_dtype)
         # `trusted`: the caller passed the upstream gradient of the summed loss as `grad_scale`, so the stored
-        # gradients (and whatever was accumulated into an engine-owned fp32 buffer) are already final.
+        # gradients (and whatever was accumulated into an engine-owned fp32 buffer) are already final. The claim is
+        # checked on the device, without a host sync: an upstream gradient that differs from the promised scale raises
+        # the status word, which `check_status()` turns into an error at the next log / save point.
+        if ctx.trusted:
+            promised = ctx.grad_scale
+            wrong = (dloss.detach().float().reshape(()) - promised).abs() > 1e-4 * abs(promised) + 1e-30
+            ctx.status.copy_(torch.where(wrong & (ctx.status == 0), torch.full_like(ctx.status, STATUS_GRAD_SCALE_MISMATCH), ctx.status))
         return dx, dw, None, None, None, None
 
 

@@ -129,3 +129,10 @@ def get_peer_group(group: dist.ProcessGroup | None, device: torch.device) -> Pee
             log_rank_0(logging.WARNING, f"peer memory is unavailable ({type(error).__name__}: {error}); collectives stay on NCCL")
             _GROUPS[key] = None
     return _GROUPS[key]
+
+
+def check_all_peer_groups() -> None:
+    """Raise if any peer group of this process recorded a barrier that gave up (synchronises with the device)."""
+    for group in _GROUPS.values():
+        if group is not None:
+            group.check()

@@ -25,7 +25,7 @@ from .hf_models import disable_generation_cache
 from .kernels import enable_kernels
 from .model_wrapper import get_model_container
 from .optimization import get_learning_rate, get_optimizer_container, get_scheduler_container
-from .train_utils import all_reduce_metrics_tracker, get_model_tflops, get_torch_profiler, track_metrics
+from .train_utils import all_reduce_metrics_tracker, check_device_health, get_model_tflops, get_torch_profiler, track_metrics
 from .utils import (
     DeviceTimer,
     ExperimentsTracker,
@@ -189,6 +189,7 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
                 for key in list(metrics_tracker.keys()):
                     if isinstance(metrics_tracker[key], torch.Tensor):
                         metrics_tracker[key] = metrics_tracker[key].item()
+                check_device_health()
                 metrics_tracker = all_reduce_metrics_tracker(metrics_tracker)
                 metrics_tracker["learning_rate"] = get_learning_rate(model_container, lr_scheduler_container)
                 if model_flops:
@@ -205,6 +206,7 @@ def train(args: TrainingArgs, model_container: ModelContainer, pipeline_schedule
                 evaluate(val_dataloaders, model_container, global_step, experiments_tracker, eval_steps, val_group_names, lm_loss_multiplier)
 
             if global_step % save_interval == 0 or global_step == num_training_steps:
+                check_device_health()  # never write a checkpoint of a step that ran on partial data
                 save_checkpoint(args, model_container=model_container, optimizer_container=optimizer_container,
                                 lr_scheduler_container=lr_scheduler_container, train_dataloader=None,
                                 experiments_tracker=experiments_tracker, iteration=global_step,

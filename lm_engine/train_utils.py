@@ -119,3 +119,20 @@ def get_model_tflops(config, batch_size: int, sequence_length: int,
         total += f
     total += _linear_flops(b * s, h, v)
     return total / 1e12
+
+
+def check_device_health() -> None:
+    """Stop the run if a kernel reported a bounded wait that ran out, a peer barrier that a rank never reached, or a
+    violated assumption of a fused op since the last check.
+
+    Every device-side wait of this library is bounded: on expiry a kernel records a status code and returns, so the
+    step goes on with partial data. The training loops call this where they synchronise with the device anyway (after
+    reading the logged loss, and always before a checkpoint is written) so that such a step is never trained on further
+    or saved. Costs one small device-to-host read per status word; does nothing on CPU."""
+    if not torch.cuda.is_available():
+        return
+    from . import ops
+    from .parallel.symmetric import check_all_peer_groups
+
+    ops.check_status()
+    check_all_peer_groups()

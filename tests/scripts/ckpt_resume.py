@@ -1,5 +1,7 @@
 """Phase "save": train 3 steps, checkpoint, train 2 more and record their losses. Phase "resume": load the checkpoint
-and train the 2 steps again. Usage: [torchrun ...] ckpt_resume.py <phase> <save_dir> <out.json> [async|sync] [expert parallel size]"""
+and train the 2 steps again. Phase "unshard" (one process): rebuild the single-device model from the checkpoint and write its
+weights. Usage: [torchrun ...] ckpt_resume.py <phase> <save_dir> <out.json> [async|sync] [expert parallel size]
+[tensor parallel size]"""
 
 import json
 import os
@@ -29,12 +31,21 @@ def main() -> None:
     use_async = len(sys.argv) > 4 and sys.argv[4] == "async"
     world = int(os.environ.get("WORLD_SIZE", 1))
     ep = int(sys.argv[5]) if len(sys.argv) > 5 else 0
-    config = tiny_config(8 // world, 5, ep=ep)
+    tp = int(sys.argv[6]) if len(sys.argv) > 6 else 1
+    if phase == "unshard":
+        from lm_engine.arguments import UnshardingArgs
+        from lm_engine.checkpointing import load_checkpoint_for_inference
+
+        args = UnshardingArgs(load_args=dict(load_path=save_dir), unsharded_path=os.path.join(save_dir, "unsharded"))
+        _, _, state = load_checkpoint_for_inference(args, Mode.unsharding, use_meta=False)
+        torch.save({k: v.float() for k, v in state.items()}, out_path)
+        return
+    config = tiny_config(8 // (world // tp), 5, ep=ep, tp=tp)
     config["save_args"] = dict(save_path=save_dir, save_interval=3, async_checkpointing=use_async)
     if phase == "resume":
         config["load_args"] = dict(load_path=save_dir)
     args = args_from_dict(Mode.training, config)
-    init_distributed(zero_stage=3, expert_parallel_world_size=max(ep, 1))
+    init_distributed(zero_stage=3, expert_parallel_world_size=max(ep, 1), tensor_parallel_world_size=tp)
     StepTracker(args.training_parameters.micro_batch_size, 1)
     set_seed(42 if phase == "save" else 7)  # a resumed run must not depend on its own seed
     container = get_model_container(args, Mode.training)

@@ -92,6 +92,38 @@ def test_pretrain_unshard_generate(tmp_path):
     assert len(lines) == 3 and "generated_text" in json.loads(lines[0])
 
 
+def test_training_stops_before_saving_when_a_kernel_reported_a_timeout(tmp_path):
+    """A status word raised by a kernel whose bounded wait ran out (made here on the host: the health check is replaced
+    by one that reports status 4 at the first save point) ends the run before a checkpoint is written."""
+    save = tmp_path / "ckpt"
+    config = dict(
+        datasets=[dict(class_name="SyntheticDataset", data_name="synthetic", class_args=dict(sequence_length=32, seed=3))],
+        model_args=dict(model_class="AutoModelForCausalLM", pretrained_config=_model_config(), use_padding_free_transformer=False),
+        tuning_args=dict(tuning_method="pretraining"),
+        save_args=dict(save_path=str(save), save_interval=2),
+        training_parameters=dict(num_training_steps=4, micro_batch_size=2, gradient_accumulation_steps=1, eval_during_training=False),
+        optimizer_args=dict(class_name="TorchAdamW", class_args=dict(lr=1e-3)),
+        lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=1),
+        mixed_precision_args=dict(dtype="fp32"),
+        logging_args=dict(log_interval=100),
+    )
+    path = tmp_path / "pretrain.yml"
+    path.write_text(yaml.safe_dump(config))
+    driver = (
+        "import lm_engine.pretrain as p\n"
+        "def failing():\n"
+        "    raise RuntimeError('a kernel on cuda:0 gave up waiting (status 4)')\n"
+        "p.check_device_health = failing\n"
+        f"p.main(argv=['--config', r'{path}'])\n"
+    )
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29743")
+    result = subprocess.run([sys.executable, "-c", driver], env=env, cwd=str(tmp_path), timeout=900, capture_output=True, text=True)
+    assert result.returncode != 0
+    assert "gave up waiting (status 4)" in result.stderr
+    assert not (save / "latest_checkpointed_iteration.json").exists()
+    assert not (save / "global_step2" / "model").exists()
+
+
 def test_finetune_on_debug_dataset(tmp_path):
     tokenizer = _tokenizer(tmp_path)
     config = dict(

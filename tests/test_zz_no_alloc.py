@@ -55,11 +55,15 @@ def test_no_alloc_rmsnorm_bwd_matches_regular_entry_point_twice():
 
         dh = torch.empty_like(x)
         dw = torch.full((H,), 123.0, device="cuda")
+        torch.cuda.synchronize()
         allocated_before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()  # the driver's view: catches allocations that bypass torch's allocator
         code, message = _call(fn, dy, x, w, rstd, dres, dh, dw, False)
         assert code == 0, message
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated_before
+        if (T, H) != (777, 4096):  # the very first call may still load the kernels' code onto the device
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert _rel(dh, dh_ref) < 1e-3
         assert _rel(dw, dw_ref) < 1e-4
 
@@ -79,3 +83,20 @@ def test_no_alloc_rejects_oversized_rows():
     dw = torch.zeros(H, device="cuda")
     code, message = _call(fn, x, x, w, rstd, None, torch.empty_like(x), dw, False)
     assert code == 2 and "MAX_H" in message
+
+
+def test_no_alloc_rejects_missing_and_misaligned_pointers():
+    # checked on the host before any launch: nothing reaches the GPU
+    fn = _library()
+    T, H = 4, 256
+    x = torch.zeros(T, H + 8, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(T, device="cuda")
+    dw = torch.zeros(H, device="cuda")
+    good = x[:, :H].contiguous()
+    message = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    code = fn(good.data_ptr(), good.data_ptr(), w.data_ptr(), 0, 0, good.data_ptr(), dw.data_ptr(), 0, T, H, stream, message, 256)
+    assert code == 6 and "NULL" in message.value.decode()
+    code = fn(good.data_ptr() + 2, good.data_ptr(), w.data_ptr(), rstd.data_ptr(), 0, good.data_ptr(), dw.data_ptr(), 0, T, H, stream, message, 256)
+    assert code == 7 and "aligned" in message.value.decode()
