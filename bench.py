@@ -53,6 +53,13 @@ def parse_args():
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not the headline config)")
     p.add_argument("--gradient-accumulation-steps", type=int, default=None, help="debug only")
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--no-moe", action="store_true", help="dense run only: skip the second record (40-expert MoE)")
+    p.add_argument("--moe-steps", type=int, default=None, help="timed steps of the MoE record (default: max(3, steps // 4))")
+    p.add_argument("--reference-compile", type=str, default="auto", choices=["auto", "on", "off"],
+                   help="reference arm: its own distributed_args.torch_compile option (auto = the faster one as measured on a B200)")
+    p.add_argument("--budget-output", type=str, default=None,
+                   help="after the timed regions run one more step with per-site device timers and write the per-kernel time budget there (JSON)")
+    p.add_argument("--child-output", type=str, default=None, help=argparse.SUPPRESS)
     return p.parse_args()
 
 
@@ -260,6 +267,23 @@ def run_native(cli) -> dict:
                    "h2d_bytes_per_step": ga * mb * (seq + 1) * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss}
         ops.check_status()
 
+        if cli.budget_output is not None:
+            # one extra, untimed-for-the-headline step with CUDA events around every launch site of the block schedule,
+            # the loss and the optimizer tail; the sites are sequential on one stream, so their sum is the step
+            from lm_engine.ops import timeline
+
+            torch.cuda.synchronize()
+            timeline.enable_timing(True)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            step(feed_device)
+            t1.record()
+            sites = timeline.report()
+            timeline.enable_timing(False)
+            if rank == 0:
+                with open(cli.budget_output, "w") as handle:
+                    json.dump({"step_ms": t0.elapsed_time(t1), "n_gpus": world, "config": spec["name"], "sites": sites}, handle, indent=1)
+
     tokens_per_step = ga * mb * seq * world
     ms_per_step = ms / cli.steps
     value = tokens_per_step / (ms_per_step / 1e3)
@@ -275,7 +299,8 @@ def run_native(cli) -> dict:
                    "global_batch": ga * mb * world, "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
                    "parallelism": (f"ep{expert_parallel} x " if moe else "") +
                    f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; gathered bf16 weights kept for the step)",
-                   "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)"},
+                   "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)",
+                   "kernels": kernels, "gradient_checkpointing": None},
         "tflops_per_gpu": tflops_per_gpu, "mfu": tflops_per_gpu / peak, "mfu_peak": f"{peak} TFLOP/s {peak_src}",
         "clocks": clocks, "gpu_launches": launches, "loss_after_warmup": loss_after_warmup,
         "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
@@ -293,6 +318,40 @@ def run_native(cli) -> dict:
     return result if rank == 0 else None
 
 
+def moe_record(cli) -> dict | None:
+    """Second record of the default run: the 40-expert top-8 MoE config, measured by a child process of every rank (same
+    launch environment, rendezvous on the next port) after this process has released the GPU. Returns rank 0's record."""
+    import gc
+
+    import torch
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    rank = int(os.environ.get("RANK", 0))
+    env = dict(os.environ)
+    if "MASTER_PORT" in env:
+        env["MASTER_PORT"] = str(int(env["MASTER_PORT"]) + 1)
+    # the children rendezvous among themselves: rank 0's child hosts the store instead of looking for the launcher's
+    for key in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_USE_AGENT_STORE"):
+        env.pop(key, None)
+    out_path = os.path.join(tempfile.gettempdir(), f"bench-moe-{os.getpid()}-{rank}.json")
+    steps = cli.moe_steps or max(3, cli.steps // 4)
+    cmd = [sys.executable, os.path.abspath(__file__), "--config", "moe", "--gpus", str(cli.gpus), "--steps", str(steps), "--warmup", "3",
+           "--impl", cli.impl, "--reference-compile", "off", "--child-output", out_path]
+    if cli.skip_e2e:
+        cmd.append("--skip-e2e")
+    done = subprocess.run(cmd, env=env, stdout=subprocess.DEVNULL if rank else None)
+    record = None
+    if rank == 0:
+        if done.returncode == 0 and os.path.exists(out_path):
+            with open(out_path) as handle:
+                record = json.load(handle)
+            os.unlink(out_path)
+        else:
+            record = {"unavailable": f"the MoE run exited with code {done.returncode}"}
+    return record
+
+
 def main() -> None:
     cli = parse_args()
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
@@ -302,8 +361,20 @@ def main() -> None:
         result = run_reference(cli, SPECS[cli.config], REPO_ROOT)
     else:
         result = run_native(cli)
+    headline = cli.config == "dense" and cli.layers is None and cli.gradient_accumulation_steps is None
+    if headline and not cli.no_moe and cli.child_output is None:
+        # the metric names both models: the MoE record rides along under "moe"; the headline `value` stays the dense one
+        moe = moe_record(cli)
+        if result is not None and moe is not None:
+            keep = ("value", "unit", "ms_per_step", "steps", "warmup", "config", "e2e", "tflops_per_gpu", "mfu", "gpu_launches",
+                    "loss_after_warmup", "peak_memory_gib", "clocks", "metric", "unavailable", "reference_notes")
+            result["moe"] = {k: moe[k] for k in keep if k in moe}
     if result is not None:
-        print(json.dumps(result), flush=True)
+        if cli.child_output is not None:
+            with open(cli.child_output, "w") as handle:
+                json.dump(result, handle)
+        else:
+            print(json.dumps(result), flush=True)
 
 
 if __name__ == "__main__":

@@ -12,8 +12,10 @@
 The sharded engine stores parameters as flat slices, so for the distributed-checkpoint files every parameter (and its
 optimizer moments) is re-expressed as a DTensor sharded on dim 0 over the ``fsdp`` mesh, which is the on-disk form of
 the reference and lets checkpoints be reloaded on a different number of ranks. A file named ``KILLSWITCH`` in
-``save_path`` makes the job exit cleanly after the next save. ``latest_checkpointed_iteration.json`` is only
-written once every shard of the checkpoint is on disk.
+``save_path`` makes the job exit cleanly after the next save. A checkpoint is written under
+``global_step{N}.incomplete`` and renamed to ``global_step{N}`` once every shard is on disk; only then is
+``latest_checkpointed_iteration.json`` replaced (atomically), so neither the directory nor the pointer ever names a
+partial checkpoint.
 """
 
 from __future__ import annotations
@@ -22,6 +24,7 @@ import json
 import logging
 import os
 import random
+import shutil
 import sys
 
 import numpy as np
@@ -359,7 +362,14 @@ def save_checkpoint(args, model_container, optimizer_container, lr_scheduler_con
     global _PENDING
     ensure_last_checkpoint_is_saved()
     save_path_root = args.save_args.save_path
-    save_path = _base(save_path_root, iteration)
+    # everything is written into `global_step{N}.incomplete`; the directory gets its final name only when every rank
+    # has written its part, so a `global_step{N}` directory that exists is always whole (a job killed mid-save
+    # leaves an `.incomplete` directory that nothing reads)
+    final_path = _base(save_path_root, iteration)
+    save_path = final_path + ".incomplete"
+    if ProcessGroupManager.get_global_rank() == 0 and os.path.isdir(save_path):
+        shutil.rmtree(save_path)
+    _barrier()
     os.makedirs(save_path, exist_ok=True)
     save_optimizer = args.save_args.save_optimizer and optimizer_container is not None
 
@@ -386,6 +396,9 @@ def save_checkpoint(args, model_container, optimizer_container, lr_scheduler_con
     def finalize() -> None:
         _barrier()
         if ProcessGroupManager.get_global_rank() == 0:
+            if os.path.isdir(final_path):
+                shutil.rmtree(final_path)
+            os.replace(save_path, final_path)
             tmp = _latest_path(save_path_root) + ".tmp"
             with open(tmp, "w") as handle:
                 json.dump({"latest_checkpointed_iteration": iteration}, handle, indent=4)

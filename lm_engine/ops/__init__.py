@@ -12,6 +12,7 @@ import torch
 import torch.nn.functional as F
 
 from .build import is_extension_built, load_extension
+from .timeline import site
 
 _C = None
 _STATUS: dict[int, torch.Tensor] = {}
@@ -319,12 +320,16 @@ class _FusedLinearCrossEntropyFn(torch.autograd.Function):
             n = min(rows, T - start)
             xc = x[start : start + n]
             lg = logits[:n]
-            C.gemm(xc, weight, lg, False, False, False, 1.0, st, 0)
-            loss_rows[start : start + n] = C.cross_entropy_(lg, labels[start : start + n], logit_scale, gs, ignore_index, need_dx or need_dw)
+            with site("loss.lm_head.logits"):
+                C.gemm(xc, weight, lg, False, False, False, 1.0, st, 0)
+            with site("loss.cross_entropy"):
+                loss_rows[start : start + n] = C.cross_entropy_(lg, labels[start : start + n], logit_scale, gs, ignore_index, need_dx or need_dw)
             if need_dx:
-                C.gemm(lg, weight, dx[start : start + n], False, True, False, 1.0, st, 0)
+                with site("loss.lm_head.dgrad"):
+                    C.gemm(lg, weight, dx[start : start + n], False, True, False, 1.0, st, 0)
             if need_dw:
-                C.gemm(lg, xc, dw_buf, True, True, True, 1.0, st, 0)
+                with site("loss.lm_head.wgrad"):
+                    C.gemm(lg, xc, dw_buf, True, True, True, 1.0, st, 0)
         ctx.dx = dx
         ctx.dw = dw
         ctx.accumulated_in_place = target is not None

@@ -61,7 +61,6 @@ def build_extension(verbose: bool = False, force: bool = False):
             "-Xptxas",
             "-v",
         ],
-        extra_ldflags=["-lcuda"] if False else [],
         build_directory=str(_BUILD_DIR),
         with_cuda=True,
         verbose=verbose,

@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from . import _weight_grad_target, native, status_word
+from .timeline import site
 
 
 def _wgrad(C, dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, st):
@@ -42,31 +43,42 @@ class FusedDenseBlockFn(torch.autograd.Function):
         C = native()
         st = status_word(x.device)
         T, H = x.shape
-        n1, rstd1 = C.rmsnorm_fwd(x, None, ln1_w, eps, False)
+        with site("fwd.ln1"):
+            n1, rstd1 = C.rmsnorm_fwd(x, None, ln1_w, eps, False)
         qkv = torch.empty(T, w_qkv.shape[0], device=x.device, dtype=x.dtype)
-        C.gemm(n1, w_qkv, qkv, False, False, False, 1.0, st, 0)
+        with site("fwd.c_attn"):
+            C.gemm(n1, w_qkv, qkv, False, False, False, 1.0, st, 0)
         del n1
         if rope_dim > 0:
-            C.rope_(qkv, cos, sin, position_ids, groups, qpg, head_dim, rope_dim, False)
-        attn, lse = C.attn_fwd(qkv, cu_seqlens, max_seqlen, groups, qpg, head_dim, softmax_scale, True, st)
+            with site("fwd.rope"):
+                C.rope_(qkv, cos, sin, position_ids, groups, qpg, head_dim, rope_dim, False)
+        with site("fwd.attention"):
+            attn, lse = C.attn_fwd(qkv, cu_seqlens, max_seqlen, groups, qpg, head_dim, softmax_scale, True, st)
         a = torch.empty(T, H, device=x.device, dtype=x.dtype)
-        C.gemm(attn, w_o, a, False, False, False, 1.0, st, 0)
-        n2, rstd2, h = C.rmsnorm_fwd(a, x, ln2_w, eps, True)
+        with site("fwd.attn_c_proj"):
+            C.gemm(attn, w_o, a, False, False, False, 1.0, st, 0)
+        with site("fwd.residual+ln2"):
+            n2, rstd2, h = C.rmsnorm_fwd(a, x, ln2_w, eps, True)
         del a
         fc = torch.empty(T, w_fc.shape[0], device=x.device, dtype=x.dtype)
         inter = w_fc.shape[0] // 2
         if inter % 128 == 0 and T >= 256:
             # up-projection with the activation in its epilogue: fc is written for backward, never read back here
             act = torch.empty(T, inter, device=x.device, dtype=x.dtype)
-            C.gemm_swiglu(n2, w_fc, fc, act, st)
+            with site("fwd.c_fc+swiglu"):
+                C.gemm_swiglu(n2, w_fc, fc, act, st)
         else:
-            C.gemm(n2, w_fc, fc, False, False, False, 1.0, st, 0)
-            act = C.swiglu_fwd(fc)
+            with site("fwd.c_fc"):
+                C.gemm(n2, w_fc, fc, False, False, False, 1.0, st, 0)
+            with site("fwd.swiglu"):
+                act = C.swiglu_fwd(fc)
         del n2
         m = torch.empty(T, H, device=x.device, dtype=x.dtype)
-        C.gemm(act, w_proj, m, False, False, False, 1.0, st, 0)
+        with site("fwd.mlp_c_proj"):
+            C.gemm(act, w_proj, m, False, False, False, 1.0, st, 0)
         del act
-        y = C.add_bf16(h, m)
+        with site("fwd.residual_add"):
+            y = C.add_bf16(h, m)
         ctx.save_for_backward(x, rstd1, qkv, attn, lse, h, rstd2, fc, ln1_w, w_qkv, w_o, ln2_w, w_fc, w_proj, cos, sin,
                               position_ids, cu_seqlens)
         ctx.meta = (max_seqlen, groups, qpg, head_dim, rope_dim, softmax_scale, eps)
@@ -84,37 +96,57 @@ class FusedDenseBlockFn(torch.autograd.Function):
 
         # ---- MLP
         dact = torch.empty(T, w_proj.shape[1], device=x.device, dtype=x.dtype)
-        C.gemm(dy, w_proj, dact, False, True, False, 1.0, st, 0)
-        dfc, act = C.swiglu_bwd(dact, fc, True)
+        with site("bwd.mlp_c_proj.dgrad"):
+            C.gemm(dy, w_proj, dact, False, True, False, 1.0, st, 0)
+        with site("bwd.swiglu"):
+            dfc, act = C.swiglu_bwd(dact, fc, True)
         del dact
-        g_proj = _wgrad(C, dy, act, w_proj, st)
+        with site("bwd.mlp_c_proj.wgrad"):
+            g_proj = _wgrad(C, dy, act, w_proj, st)
         del act
-        n2, _ = C.rmsnorm_fwd(h, None, ln2_w, eps, False)
-        g_fc = _wgrad(C, dfc, n2, w_fc, st)
+        with site("bwd.ln2.recompute"):
+            n2, _ = C.rmsnorm_fwd(h, None, ln2_w, eps, False)
+        with site("bwd.c_fc.wgrad"):
+            g_fc = _wgrad(C, dfc, n2, w_fc, st)
         del n2
         dn2 = torch.empty(T, H, device=x.device, dtype=x.dtype)
-        C.gemm(dfc, w_fc, dn2, False, True, False, 1.0, st, 0)
+        with site("bwd.c_fc.dgrad"):
+            C.gemm(dfc, w_fc, dn2, False, True, False, 1.0, st, 0)
         del dfc
         buf2, acc2 = _norm_wgrad_buffer(ln2_w)
-        dh = C.rmsnorm_bwd(dn2, h, ln2_w, rstd2, dy, buf2, acc2)
+        with site("bwd.ln2"):
+            dh = C.rmsnorm_bwd(dn2, h, ln2_w, rstd2, dy, buf2, acc2)
         del dn2
 
         # ---- attention
         dattn = torch.empty(T, w_o.shape[1], device=x.device, dtype=x.dtype)
-        C.gemm(dh, w_o, dattn, False, True, False, 1.0, st, 0)
-        g_o = _wgrad(C, dh, attn, w_o, st)
-        dqkv = C.attn_bwd(dattn, qkv, attn, lse, cu_seqlens, max_seqlen, groups, qpg, head_dim, softmax_scale, True, st)
+        with site("bwd.attn_c_proj.dgrad"):
+            C.gemm(dh, w_o, dattn, False, True, False, 1.0, st, 0)
+        with site("bwd.attn_c_proj.wgrad"):
+            g_o = _wgrad(C, dh, attn, w_o, st)
+        with site("bwd.attention"):
+            dqkv = C.attn_bwd(dattn, qkv, attn, lse, cu_seqlens, max_seqlen, groups, qpg, head_dim, softmax_scale, True, st)
         del dattn
         if rope_dim > 0:
-            C.rope_(dqkv, cos, sin, position_ids, groups, qpg, head_dim, rope_dim, True)
-        n1, _ = C.rmsnorm_fwd(x, None, ln1_w, eps, False)
-        g_qkv = _wgrad(C, dqkv, n1, w_qkv, st)
+            with site("bwd.rope"):
+                C.rope_(dqkv, cos, sin, position_ids, groups, qpg, head_dim, rope_dim, True)
+        with site("bwd.ln1.recompute"):
+            n1, _ = C.rmsnorm_fwd(x, None, ln1_w, eps, False)
+        with site("bwd.c_attn.wgrad"):
+            g_qkv = _wgrad(C, dqkv, n1, w_qkv, st)
         del n1
         dn1 = torch.empty(T, H, device=x.device, dtype=x.dtype)
-        C.gemm(dqkv, w_qkv, dn1, False, True, False, 1.0, st, 0)
+        with site("bwd.c_attn.dgrad"):
+            C.gemm(dqkv, w_qkv, dn1, False, True, False, 1.0, st, 0)
         del dqkv
         buf1, acc1 = _norm_wgrad_buffer(ln1_w)
-        dx = C.rmsnorm_bwd(dn1, x, ln1_w, rstd1, dh, buf1, acc1)
+        with site("bwd.ln1"):
+            dx = C.rmsnorm_bwd(dn1, x, ln1_w, rstd1, dh, buf1, acc1)
+
+        # every gradient of this block is in place: under sharded data parallelism the block's reduce-scatter may start
+        unit = getattr(w_qkv, "_lm_engine_unit", None)
+        if unit is not None and acc1 and acc2 and getattr(unit, "engine", None) is not None:
+            unit.engine.unit_backward_done(unit)
 
         g_ln1 = None if acc1 else buf1.to(ln1_w.dtype)
         g_ln2 = None if acc2 else buf2.to(ln2_w.dtype)

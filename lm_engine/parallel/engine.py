@@ -31,6 +31,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
+from ..ops.timeline import site
 from ..utils import ProcessGroupManager
 from .collectives import all_gather_in_place, all_reduce_sum, reduce_scatter_in_place
 
@@ -203,6 +204,13 @@ class ShardedTrainingEngine:
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=device)
         self.micro_steps_since_reduce = 0
+        # reduce-scatter of a unit as soon as its last backward of the optimizer step is done (see arm_early_reduction)
+        self.early_reduction_armed = False
+        self._early_reduced: set[int] = set()
+        self._side_stream = None
+        self._side_done = None
+        for unit in self.units:
+            unit.engine = self
 
     # ------------------------------------------------------------------ construction
     def _build_units(self, model: nn.Module, block_class_names: set[str], group_of, frozen_prefixes) -> None:
@@ -374,6 +382,35 @@ class ShardedTrainingEngine:
         for unit in self.units:
             unit.grad.zero_()
 
+    # ------------------------------------------------------------------ reduction under the last backward pass
+    def arm_early_reduction(self) -> bool:
+        """Call before the LAST micro-step of an optimizer step. From then on a unit whose backward pass reports itself
+        finished (``unit_backward_done``) is reduce-scattered at once on a side stream, under the backward pass of the
+        units below it, so that only the units that finish last (the first block, the embeddings) are reduced in the
+        open after the backward pass. Needs the peer-memory collectives; returns whether it is active."""
+        import os
+
+        self.early_reduction_armed = (self.peer is not None and self.tp_world == 1 and self.replica_world == 1
+                                      and os.environ.get("LM_ENGINE_OVERLAP_REDUCE", "1") != "0")
+        return self.early_reduction_armed
+
+    @torch.no_grad()
+    def unit_backward_done(self, unit: "FlatUnit") -> None:
+        """Every gradient of ``unit`` for this optimizer step is in its fp32 buffer (called by the backward pass of the
+        unit's last micro-step, on the compute stream)."""
+        if not self.early_reduction_armed or unit.local_only or id(unit) in self._early_reduced:
+            return
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        ready = torch.cuda.Event()
+        ready.record()
+        self._side_stream.wait_event(ready)
+        with torch.cuda.stream(self._side_stream):
+            # all ranks have this unit's gradients complete; then each sums its slice of all copies
+            self.peer.side_barrier()
+            self.peer.reduce_scatter_f32(self.arenas[torch.float32], unit.grad_shard, unit.grad_shard)
+        self._early_reduced.add(id(unit))
+
     @torch.no_grad()
     def reduce_gradients(self) -> None:
         """Sum gradients over the data parallel ranks; afterwards ``unit.grad_shard`` holds this rank's slice. Under
@@ -386,11 +423,21 @@ class ShardedTrainingEngine:
             # every rank has finished its backward pass; then each sums its own slice of all copies; then nobody
             # clears or refills its copy before the others have read it
             arena = self.arenas[torch.float32]
-            self.peer.barrier()
-            for unit in self.units:
-                if not unit.local_only:
-                    self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
-            self.peer.barrier()
+            if self._early_reduced:
+                with site("step.wait_for_early_reduce_scatter"):
+                    done = torch.cuda.Event()
+                    done.record(self._side_stream)
+                    torch.cuda.current_stream().wait_event(done)
+            with site("step.barrier_before_reduce_scatter"):
+                self.peer.barrier()
+            with site("step.reduce_scatter"):
+                for unit in self.units:
+                    if not unit.local_only and id(unit) not in self._early_reduced:
+                        self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
+            with site("step.barrier_after_reduce_scatter"):
+                self.peer.barrier()
+            self._early_reduced.clear()
+            self.early_reduction_armed = False
         for unit in self.units:
             if unit.local_only:
                 continue
@@ -506,7 +553,8 @@ class ShardedTrainingEngine:
         (a device scalar; nothing here synchronises with the host)."""
         if precomputed_norm_sq is None:
             self.reduce_gradients()
-        grad_norm = self.clip_grad_norm(max_norm, extra_norm_groups, precomputed_norm_sq)
+        with site("step.grad_norm"):
+            grad_norm = self.clip_grad_norm(max_norm, extra_norm_groups, precomputed_norm_sq)
         fused = getattr(optimizer, "writes_compute_copy", False)
         if fused:
             optimizer.grad_scale = self.clip_coef
@@ -515,14 +563,17 @@ class ShardedTrainingEngine:
             factor = self.clip_coef * self.grad_mul
             for unit in self.units:
                 unit.grad_shard.mul_(factor.to(unit.grad_shard.device))
-        optimizer.step()
+        with site("step.adamw(+broadcast)"):
+            optimizer.step()
         if lr_scheduler is not None:
             lr_scheduler.step()
-        self.refresh_parameters(masters_already_cast=fused, broadcast_done=fused and getattr(optimizer, "last_step_broadcast", False))
+        with site("step.refresh_parameters"):
+            self.refresh_parameters(masters_already_cast=fused, broadcast_done=fused and getattr(optimizer, "last_step_broadcast", False))
         if fused and self.shard_world == 1:
             pass  # the fused kernel cleared every gradient element it consumed
         else:
-            self.zero_grad()
+            with site("step.zero_grad"):
+                self.zero_grad()
         return grad_norm
 
     # ------------------------------------------------------------------ state dicts (full, fp32, by parameter name)

@@ -68,6 +68,10 @@ class PeerGroup:
         self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.control = self.alloc(_CONTROL_WORDS, torch.int32, zero=True)
+        # a second set of flags with its own epoch counter: barriers issued on a side stream (collectives that run under
+        # compute) must not interleave their epochs with those of the main stream
+        self.side_epoch = 0
+        self.side_control = self.alloc(_CONTROL_WORDS, torch.int32, zero=True)
         # the flags must read zero everywhere before the first barrier kernel publishes an epoch
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
@@ -93,6 +97,12 @@ class PeerGroup:
         """All ranks of the group have reached this point of their streams (and their earlier writes are visible)."""
         self.epoch += 1
         ops.native().peer_barrier(self.control.ptrs, self.rank, self.epoch & 0x7FFFFFFF, self.timeout_seconds, self.status)
+
+    def side_barrier(self) -> None:
+        """Same as :meth:`barrier` on the second set of flags; every rank must issue these from one (side) stream and in
+        the same order."""
+        self.side_epoch += 1
+        ops.native().peer_barrier(self.side_control.ptrs, self.rank, self.side_epoch & 0x7FFFFFFF, self.timeout_seconds, self.status)
 
     def check(self) -> None:
         """Host-side check of the status word (synchronises with the device)."""

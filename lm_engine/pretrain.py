@@ -68,8 +68,10 @@ def train_step_without_pipeline_parallel(
     ga = StepTracker.get_gradient_accumulation_steps()
     metrics = MetricsTrackingDict({})
 
-    for _ in range(ga):
+    for micro_step in range(ga):
         batch = get_next_batch(train_dataloader)
+        if micro_step == ga - 1 and hasattr(engine, "arm_early_reduction"):
+            engine.arm_early_reduction()  # gradients of a block are reduced as soon as its last backward is done
         with forward_context():
             loss_dict = model(batch, lm_loss_multiplier=lm_loss_multiplier)
         with backward_context():

