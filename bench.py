@@ -178,6 +178,7 @@ def run_native(cli) -> dict:
 
     set_logger("WARNING")
     ops.require_native()
+    ops.set_strict(True)  # an op that would leave the sm_100a kernels for a PyTorch path raises instead
     spec = SPECS[cli.config]
     moe = "num_experts" in spec
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
@@ -302,7 +303,7 @@ def run_native(cli) -> dict:
                    "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)",
                    "kernels": kernels, "gradient_checkpointing": None},
         "tflops_per_gpu": tflops_per_gpu, "mfu": tflops_per_gpu / peak, "mfu_peak": f"{peak} TFLOP/s {peak_src}",
-        "clocks": clocks, "gpu_launches": launches, "loss_after_warmup": loss_after_warmup,
+        "clocks": clocks, "gpu_launches": launches, "pytorch_fallbacks": sum(ops.fallback_counts().values()), "loss_after_warmup": loss_after_warmup,
         "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
     }
     if expert_parallel > 1:

@@ -3,7 +3,7 @@
 One YAML file per run; each top-level key is a strict pydantic section (unknown keys are errors). The section and
 field names follow lm_engine/arguments.py:32-526 of the reference so existing configs keep working. Fields that
 exist only here: ``distributed_args.expert_parallel_world_size``, ``distributed_args.fused_collectives``,
-``distributed_args.keep_parameters_gathered`` and ``mixed_precision_args.fp8_recipe``.
+``distributed_args.keep_parameters_gathered``, ``mixed_precision_args.fp8_recipe`` and ``kernel_args.strict``.
 """
 
 from __future__ import annotations
@@ -276,6 +276,9 @@ class LoggingArgs(BaseArgs):
 
 class KernelArgs(BaseArgs):
     kernels: list[Kernel] = []
+    # raise when an op would run its PyTorch restatement on CUDA bf16 tensors instead of the sm_100a kernel
+    # (without it such a site is counted and logged once; see lm_engine.ops.fallback_counts)
+    strict: bool = False
 
 
 class TeacherArgs(BaseArgs):

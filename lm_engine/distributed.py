@@ -18,6 +18,28 @@ from .parallel.engine import ShardedTrainingEngine
 from .utils import ProcessGroupManager, log_rank_0, string_to_torch_dtype
 
 
+def _keep_parameters_gathered(dist_args, wrapper, dtype: torch.dtype) -> bool:
+    """Stage 0 and 2 keep every rank's full compute copy (that is what those stages mean). Stage 3 follows
+    ``keep_parameters_gathered``; left unset, the gathered weights and the full-size fp32 gradient buffer stay resident
+    when they fit comfortably (collectives once per optimizer step instead of per block and micro-step), and the blocks
+    are gathered and released one by one when they do not."""
+    if dist_args.stage != 3 or ProcessGroupManager.get_sharding_world_size() == 1:
+        return True
+    if dist_args.keep_parameters_gathered is not None:
+        return bool(dist_args.keep_parameters_gathered)
+    if not torch.cuda.is_available():
+        return True
+    params = sum(p.numel() for p in wrapper.parameters() if p.requires_grad)
+    width = torch.empty((), dtype=dtype).element_size()
+    shard = ProcessGroupManager.get_sharding_world_size()
+    resident_bytes = params * (width + 4) + params * 12 // shard
+    capacity = torch.cuda.get_device_properties(ProcessGroupManager.get_device()).total_memory
+    keep = resident_bytes < 0.6 * capacity
+    if not keep:
+        log_rank_0(logging.INFO, "stage 3: the gathered weights do not fit next to the activations; blocks are gathered and released one by one")
+    return keep
+
+
 def wrap_model_container_for_distributed_training(args, model_container: ModelContainer):
     dist_args = args.distributed_args
     dtype = string_to_torch_dtype(args.mixed_precision_args.dtype)
@@ -45,6 +67,7 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
             set_expert_capacity_factor(dist_args.expert_capacity_factor)
         engine = ShardedTrainingEngine(
             wrapper,
+            resident_parameters=_keep_parameters_gathered(dist_args, wrapper, dtype),
             compute_dtype=dtype,
             zero_stage=dist_args.stage,
             device=device,

@@ -85,7 +85,9 @@ class StickBreakingAttention(Attention):
         from ...enums import Kernel
         from ...kernels import is_kernel_allowed
 
-        return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.native_available()
+        from ...ops.attention import padded_head_dim
+
+        return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and padded_head_dim(self.head_dim) is not None and ops.native_available()
                 and hasattr(ops.native(), "sb_attn_fwd") and is_kernel_allowed(Kernel.stickbreaking_attention))
 
     def _heads(self, qkv: torch.Tensor):
@@ -106,12 +108,22 @@ class StickBreakingAttention(Attention):
     def forward(self, hidden_states: torch.Tensor, ctx: SequenceContext, past_key_values=None) -> torch.Tensor:
         qkv = self.c_attn(hidden_states)
         if ctx.packed and self._kernel_ok(qkv):
-            out, rem = _FusedStickBreaking.apply(qkv.contiguous(), ctx.cu_seqlens_int32(), self.num_key_value_heads, self.group_size,
-                                                 self.head_dim, self.softmax_scale)
+            from ...ops.attention import pad_fused_qkv, padded_head_dim
+
             tokens = qkv.shape[0]
-            mixed = out.view(tokens, self.num_heads, self.head_dim) + rem.t().unsqueeze(-1).to(out.dtype) * self.head_bias.to(out.dtype)
+            width = padded_head_dim(self.head_dim)
+            if width != self.head_dim:
+                # head widths between the kernel widths (80, 96) run on the wider kernel over zero-padded heads
+                qkv = pad_fused_qkv(qkv.contiguous(), self.num_key_value_heads, self.group_size, self.head_dim, width)
+            out, rem = _FusedStickBreaking.apply(qkv.contiguous(), ctx.cu_seqlens_int32(), self.num_key_value_heads, self.group_size,
+                                                 width, self.softmax_scale)
+            out = out.view(tokens, self.num_heads, width)[:, :, : self.head_dim]
+            mixed = out + rem.t().unsqueeze(-1).to(out.dtype) * self.head_bias.to(out.dtype)
             mixed = self.norm(mixed.reshape(tokens, self.hidden_size))
         elif ctx.packed:
+            from ... import ops
+
+            ops.note_fallback("stickbreaking_attention", f"head_dim {self.head_dim} or the kernel is not enabled", qkv)
             bounds = ctx.cu_seqlens.tolist()
             pieces = [self._mix(*self._heads(qkv[s:e])) for s, e in zip(bounds[:-1], bounds[1:]) if e > s]
             mixed = torch.cat(pieces, dim=0)

@@ -68,6 +68,50 @@ def check_status() -> None:
             raise RuntimeError(f"a kernel on cuda:{index} gave up waiting (status {code})")
 
 
+# ----------------------------------------------------------------------------- fallbacks are never silent
+_STRICT = False
+_FALLBACKS: dict[str, int] = {}
+_WARNED: set[str] = set()
+
+
+def set_strict(on: bool = True) -> None:
+    """Strict mode: an op that would leave the sm_100a kernels for the PyTorch restatement on CUDA bf16 tensors raises
+    instead (``kernel_args.strict`` in the YAML, ``LM_ENGINE_STRICT=1`` in the environment; the benchmark and the GPU
+    tests run with it)."""
+    global _STRICT
+    _STRICT = bool(on)
+
+
+def is_strict() -> bool:
+    import os
+
+    return _STRICT or os.environ.get("LM_ENGINE_STRICT", "0") == "1"
+
+
+def note_fallback(site: str, reason: str, *tensors: torch.Tensor) -> None:
+    """Called where an op takes the PyTorch path. On a machine with the native kernels and CUDA bf16 operands that is
+    a lost kernel: it is counted (``fallback_counts()``), logged once per site and reason, and an error in strict mode.
+    CPU tensors and other dtypes take the PyTorch path by design and are not reported."""
+    if not native_available():
+        return
+    if not any(t is not None and t.is_cuda and t.dtype == torch.bfloat16 for t in tensors):
+        return
+    key = f"{site}: {reason}"
+    _FALLBACKS[key] = _FALLBACKS.get(key, 0) + 1
+    if is_strict():
+        raise RuntimeError(f"strict mode: {site} would run the PyTorch path instead of its sm_100a kernel ({reason})")
+    if key not in _WARNED:
+        _WARNED.add(key)
+        import logging
+
+        logging.getLogger(__name__).warning(f"{site} runs the PyTorch path instead of its sm_100a kernel ({reason}); reported once")
+
+
+def fallback_counts() -> dict[str, int]:
+    """``{"site: reason": visits}`` of every op call that left the native kernels since the process started."""
+    return dict(_FALLBACKS)
+
+
 def launch_count() -> int:
     return int(native().launch_count()) if native_available() else 0
 
@@ -87,6 +131,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
         if ok:
             native().gemm(a, b, out, a_mn, b_mn, accumulate, alpha, status_word(a.device), max_ctas)
             return out
+        note_fallback("gemm", "row stride not a multiple of 8 elements or base not 16-byte aligned", a, b)
+    else:
+        note_fallback("gemm", "operands are not both bf16", a, b)
     am = a.t() if a_mn else a
     bm = b if b_mn else b.t()
     res = (am.float() @ bm.float()) * alpha
@@ -137,6 +184,7 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     if use_native(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
         return _LinearFn.apply(x, weight, bias)
+    note_fallback("linear", "input and weight are not both bf16 or the inner size is not a multiple of 8", x, weight)
     return F.linear(x, weight, bias)
 
 
@@ -180,6 +228,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, residual: 
     """RMSNorm over the last dim. With ``residual`` returns ``(norm(x + residual), x + residual)``."""
     if weight is not None and use_native(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
         return _RMSNormFn.apply(x, weight, eps, residual)
+    note_fallback("rmsnorm", "no weight, mixed dtypes or a row length that is not a multiple of 8", x)
     h = x if residual is None else x + residual
     y = F.rms_norm(h, (h.shape[-1],), weight, eps)
     return y if residual is None else (y, h)
@@ -203,6 +252,7 @@ def swiglu_packed(x: torch.Tensor) -> torch.Tensor:
     """``up * silu(gate)`` for ``x = [up | gate]`` along the last dim."""
     if use_native(x) and x.dtype == torch.bfloat16 and (x.shape[-1] // 2) % 8 == 0:
         return _SwiGLUFn.apply(x)
+    note_fallback("swiglu", "intermediate size is not a multiple of 8", x)
     up, gate = x.chunk(2, dim=-1)
     return up * F.silu(gate)
 
@@ -249,6 +299,7 @@ def rope_fused_qkv(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     if use_native(qkv) and qkv.dtype == torch.bfloat16 and rd % 16 == 0 and cos.dtype == torch.float32:
         pid = None if position_ids is None else position_ids.to(torch.int32).contiguous()
         return _RopeFn.apply(qkv, cos.contiguous(), sin.contiguous(), pid, groups, qpg, d, rd)
+    note_fallback("rope", "rotary dimension is not a multiple of 16 or the tables are not fp32", qkv)
     return rope_torch(qkv, cos, sin, position_ids, groups, qpg, d, rd)
 
 
@@ -277,6 +328,7 @@ class _EmbeddingFn(torch.autograd.Function):
 def embedding(weight: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     if use_native(weight) and weight.dtype == torch.bfloat16 and ids.is_cuda and weight.shape[1] % 8 == 0:
         return _EmbeddingFn.apply(weight, ids.long(), float(scale))
+    note_fallback("embedding", "hidden size is not a multiple of 8 or the ids are not on the device", weight)
     out = F.embedding(ids, weight)
     return out if scale == 1.0 else out * scale
 
@@ -369,6 +421,7 @@ def fused_linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, labels: to
     if use_native(x2, weight) and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x2.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0:
         loss = _FusedLinearCrossEntropyFn.apply(x2.contiguous(), weight, lab.long().contiguous(), float(logit_scale), ignore_index, grad_scale_hint)
     else:
+        note_fallback("fused_linear_cross_entropy", "mixed dtypes or sizes that are not multiples of 8", x2, weight)
         logits = F.linear(x2, weight).float() * logit_scale
         loss = F.cross_entropy(logits, lab.long(), ignore_index=ignore_index, reduction="sum")
     if reduction == "mean":

@@ -12,7 +12,7 @@ import math
 import torch
 import torch.nn.functional as F
 
-from . import native, native_available, status_word
+from . import native, native_available, note_fallback, status_word
 
 
 def split_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int):
@@ -68,12 +68,37 @@ class _FusedQKVAttentionFn(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None
 
 
+def padded_head_dim(d: int) -> int | None:
+    """The head width the kernels run for a head of width ``d``: 64 or 128 themselves, the next of the two for any
+    other multiple of 8 up to 128 (80 and 96 run as 128, 32 as 64), ``None`` when the kernels cannot take it."""
+    if d in (64, 128):
+        return d
+    if d % 8 or d > 128 or d <= 0:
+        return None
+    return 64 if d < 64 else 128
+
+
+def pad_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int, dp: int) -> torch.Tensor:
+    """``[T, groups * (qpg + 2) * d] -> [T, groups * (qpg + 2) * dp]`` with every head zero-padded to ``dp`` channels.
+    Zero key / query channels add nothing to the scores and zero value channels give zero output channels, so attention
+    over the padded heads, cut back to ``d`` channels, is attention over the original heads (differentiable)."""
+    T = qkv.shape[0]
+    return F.pad(qkv.view(T, groups * (qpg + 2), d), (0, dp - d)).view(T, groups * (qpg + 2) * dp)
+
+
 def attention_fused_qkv(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, groups: int, qpg: int, d: int,
                         scale: float | None = None, causal: bool = True, dropout_p: float = 0.0) -> torch.Tensor:
     """Attention over a fused projection ``[T, groups*(qpg+2)*d]`` -> ``[T, groups*qpg*d]``."""
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     if dropout_p == 0.0 and _native_attention_ok(qkv, d):
         return _FusedQKVAttentionFn.apply(qkv, cu_seqlens.to(torch.int32), max_seqlen, groups, qpg, d, scale, causal)
+    dp = padded_head_dim(d)
+    if dropout_p == 0.0 and dp is not None and dp != d and _native_attention_ok(qkv, dp):
+        # head widths between the two kernel widths (80, 96, ...) run on the wider kernel over zero-padded heads
+        wide = pad_fused_qkv(qkv, groups, qpg, d, dp)
+        out = _FusedQKVAttentionFn.apply(wide, cu_seqlens.to(torch.int32), max_seqlen, groups, qpg, dp, scale, causal)
+        return out.view(qkv.shape[0], groups * qpg, dp)[:, :, :d].reshape(qkv.shape[0], groups * qpg * d)
+    note_fallback("attention", "attention dropout" if dropout_p != 0.0 else f"head_dim {d} or the strides of the fused projection", qkv)
     q, k, v = split_fused_qkv(qkv, groups, qpg, d)
     out = attention_varlen_reference(q, k, v, cu_seqlens, scale, causal, dropout_p)
     return out.reshape(qkv.shape[0], groups * qpg * d)

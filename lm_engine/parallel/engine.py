@@ -15,7 +15,10 @@ What the reference gets from FSDP2 ``fully_shard`` (lm_engine/distributed.py:223
   replication group for hybrid sharding).
 * With 180 GB per GPU the gathered compute copy stays resident for the whole optimizer step (all
   gradient-accumulation micro-steps), so parameters are gathered once per step rather than twice per micro-step.
-  ``keep_parameters_gathered=False`` restores per-unit gather/release around each unit's forward and backward.
+  ``resident_parameters=False`` (``distributed_args.keep_parameters_gathered: false``) instead keeps only the
+  1 / N shards of every block: its parameters are all-gathered into a pooled buffer before the block's forward and
+  before its backward pass and released afterwards, and its gradients are reduce-scattered right after its backward
+  pass into a persistent fp32 shard, so no full-size weight copy or gradient buffer of the blocks outlives a block.
 
 The same code runs on CPU ranks over gloo (fp32) - that is what the 2-rank loss-parity test uses.
 """
@@ -68,9 +71,13 @@ class Segment:
 class FlatUnit:
     def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], group_of: Callable[[str, nn.Parameter], str],
                  group_order: list[str], shard_world: int, shard_rank: int, compute_dtype: torch.dtype,
-                 device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None) -> None:
+                 device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None, resident: bool = True) -> None:
         self.name = name
         self.local_only = False  # True: this rank's own parameters (expert parallelism), no collective touches them
+        # False: only this rank's shard of the compute copy and of the gradients is kept; the full buffers exist while
+        # the unit's forward / backward pass runs (see ShardedTrainingEngine.gather_unit / release_unit)
+        self.resident = resident
+        self.module = None
         self.world = shard_world
         self.rank = shard_rank
         self.compute_dtype = compute_dtype
@@ -94,12 +101,20 @@ class FlatUnit:
 
         aliased = compute_dtype == torch.float32
         new = storage if storage is not None else (lambda n, dtype: torch.zeros(n, dtype=dtype, device=device))
-        self.compute = new(self.numel, compute_dtype)
-        # fp32 training keeps no separate master: the shard region of the compute buffer is the master
-        self.master = self.compute[lo : lo + self.shard_numel] if aliased else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+        if resident:
+            self.compute = new(self.numel, compute_dtype)
+            # fp32 training keeps no separate master: the shard region of the compute buffer is the master
+            self.master = self.compute[lo : lo + self.shard_numel] if aliased else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.compute_shard = self.compute[lo : lo + self.shard_numel]
+            self.grad = new(self.numel, torch.float32)
+            self.grad_shard = self.grad[lo : lo + self.shard_numel]
+        else:
+            self.compute = None  # gathered on demand
+            self.master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.compute_shard = self.master if aliased else torch.zeros(self.shard_numel, dtype=compute_dtype, device=device)
+            self.grad = None  # full-size only during the unit's backward pass
+            self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
         self.master_is_alias = aliased
-        self.grad = new(self.numel, torch.float32)
-        self.grad_shard = self.grad[lo : lo + self.shard_numel]
 
         self.segments: list[Segment] = []
         for g, (g0, g1) in self.group_ranges.items():
@@ -109,7 +124,7 @@ class FlatUnit:
             seg = Segment(self, g, s0 - lo, s1 - s0)
             seg.master = nn.Parameter(self.master[seg.start : seg.start + seg.numel], requires_grad=True)
             seg.master.grad = self.grad_shard[seg.start : seg.start + seg.numel]
-            seg.compute = None if aliased else self.compute[s0:s1]
+            seg.compute = None if aliased else self.compute_shard[s0 - lo : s1 - lo]
             seg.master._lm_engine_segment = seg
             self.segments.append(seg)
 
@@ -126,20 +141,36 @@ class FlatUnit:
     def adopt(self, slot: _Slot, value_fp32: torch.Tensor) -> None:
         """Copy an initial value into the flat storage and re-point the parameter at its compute view."""
         flat = value_fp32.reshape(-1)
+        slot.param._lm_engine_unit = self
+        lo, hi = self.shard_range
+        a, b = max(slot.offset, lo), min(slot.offset + slot.numel, hi)
+        if not self.resident:
+            if b > a:
+                self.master[a - lo : b - lo].copy_(flat[a - slot.offset : b - slot.offset])
+                if not self.master_is_alias:
+                    self.compute_shard[a - lo : b - lo].copy_(flat[a - slot.offset : b - slot.offset])
+            if self.compute is not None:  # adopted while gathered (checkpoint load between two passes)
+                self.compute[slot.offset : slot.offset + slot.numel].copy_(flat)
+            else:
+                self.point_parameter_at_placeholder(slot)
+            return
         self.compute[slot.offset : slot.offset + slot.numel].copy_(flat)
         if not self.master_is_alias:
-            lo, hi = self.shard_range
-            a, b = max(slot.offset, lo), min(slot.offset + slot.numel, hi)
             if b > a:
                 self.master[a - lo : b - lo].copy_(flat[a - slot.offset : b - slot.offset])
         view = self.compute[slot.offset : slot.offset + slot.numel].view(slot.shape)
         slot.param.data = view
         slot.param.main_grad = self.grad[slot.offset : slot.offset + slot.numel].view(slot.shape)
-        slot.param._lm_engine_unit = self
+
+    def point_parameter_at_placeholder(self, slot: _Slot) -> None:
+        """A released parameter keeps its shape (code that only asks for sizes keeps working) but owns no memory."""
+        slot.param.data = torch.empty(1, dtype=self.compute_dtype, device=self.device).expand(slot.shape)
+        if hasattr(slot.param, "main_grad"):
+            del slot.param.main_grad
 
     def full_param_fp32(self, slot: _Slot, group: dist.ProcessGroup | None) -> torch.Tensor:
         """The fp32 master value of one parameter, assembled from all shards (used for checkpoints)."""
-        if self.master_is_alias:
+        if self.master_is_alias and self.resident:
             return self.compute[slot.offset : slot.offset + slot.numel].view(slot.shape).float().clone()
         if self.world == 1:
             full = self.master
@@ -166,8 +197,14 @@ class ShardedTrainingEngine:
         fused_collectives: bool = True,
         frozen_prefixes: tuple[str, ...] = (),
         sequence_parallel: bool = False,
+        resident_parameters: bool = True,
     ) -> None:
         self.model = model
+        # False: the parameters of every block exist in full only while that block runs (ZeRO-3 as the reference's
+        # `reshard_after_forward`): per block an all-gather before its forward and before its backward pass and a
+        # reduce-scatter of its gradients after its backward pass; between those only the 1 / N shards are held
+        self.resident_parameters = resident_parameters
+        self._buffer_pool: dict[tuple[int, torch.dtype], list[torch.Tensor]] = {}
         self.sequence_parallel = sequence_parallel
         self.compute_dtype = compute_dtype
         self.zero_stage = zero_stage
@@ -240,11 +277,22 @@ class ShardedTrainingEngine:
             if local:
                 split_plan.append((unit_name + ".experts", module, local, True))
 
-        storage = self._peer_storage(sum(FlatUnit.planned_numel(params, self.shard_world) for _, _, params, local in split_plan if not local))
+        def sharded(module, local_only) -> bool:
+            return not self.resident_parameters and module is not None and not local_only and self.shard_world > 1
+
+        if not self.resident_parameters and self.tp_world > 1:
+            raise NotImplementedError("keep_parameters_gathered=False is not available together with tensor parallelism")
+        storage = self._peer_storage(sum(FlatUnit.planned_numel(params, self.shard_world) for _, module, params, local in split_plan
+                                         if not local and not sharded(module, local)))
         materialised: set[int] = set()
         for unit_name, module, params, local_only in split_plan:
             if local_only:
                 unit = FlatUnit(unit_name, params, group_of, self.group_order, 1, 0, self.compute_dtype, self.device, None)
+            elif sharded(module, local_only):
+                unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
+                                self.compute_dtype, self.device, None, resident=False)
+                unit.module = module
+                self._install_gather_hooks(unit, module)
             else:
                 unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
                                 self.compute_dtype, self.device, storage)
@@ -252,7 +300,7 @@ class ShardedTrainingEngine:
             self._materialise(unit, module if id(module) not in materialised else None)
             materialised.add(id(module))
             self.units.append(unit)
-            if self.peer is not None and not local_only:
+            if self.peer is not None and not local_only and unit.resident:
                 arena = self.arenas[self.compute_dtype]
                 for seg in unit.segments:
                     if seg.compute is not None:
@@ -344,6 +392,78 @@ class ShardedTrainingEngine:
                 for name, b in buffers:
                     module._buffers[name] = b.to(self.device)
 
+    # ------------------------------------------------------------------ parameters that exist in full only while used
+    def _take_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        free = self._buffer_pool.setdefault((numel, dtype), [])
+        return free.pop() if free else torch.empty(numel, dtype=dtype, device=self.device)
+
+    def _give_buffer(self, buf: torch.Tensor) -> None:
+        self._buffer_pool.setdefault((buf.numel(), buf.dtype), []).append(buf)
+
+    @torch.no_grad()
+    def gather_unit(self, unit: FlatUnit, for_backward: bool = False) -> None:
+        """Make the full parameters of a sharded unit available (all-gather of the ranks' shards into a pooled
+        buffer); for a backward pass also a zeroed full-size fp32 gradient buffer behind ``param.main_grad``."""
+        if unit.resident:
+            return
+        if unit.compute is None:
+            buf = self._take_buffer(unit.numel, self.compute_dtype)
+            lo, hi = unit.shard_range
+            buf[lo:hi].copy_(unit.compute_shard)
+            all_gather_in_place(buf, unit.shard_numel, unit.rank, self.shard_group)
+            unit.compute = buf
+            for slot in unit.slots:
+                slot.param.data = buf[slot.offset : slot.offset + slot.numel].view(slot.shape)
+        if for_backward and unit.grad is None:
+            unit.grad = self._take_buffer(unit.numel, torch.float32).zero_()
+            for slot in unit.slots:
+                slot.param.main_grad = unit.grad[slot.offset : slot.offset + slot.numel].view(slot.shape)
+
+    @torch.no_grad()
+    def release_unit(self, unit: FlatUnit) -> None:
+        """Give the full buffers back. Gradients of the pass that just ended are summed over the ranks first and this
+        rank's slice is added to its persistent gradient shard."""
+        if unit.resident:
+            return
+        if unit.grad is not None:
+            for slot in unit.slots:  # gradients that autograd left in .grad join the buffer before it is reduced
+                g = slot.param.grad
+                if g is not None:
+                    slot.param.main_grad.add_(g.to(torch.float32))
+                    slot.param.grad = None
+            reduced = reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
+            unit.grad_shard.add_(reduced)
+            self._give_buffer(unit.grad)
+            unit.grad = None
+        if unit.compute is not None:
+            self._give_buffer(unit.compute)
+            unit.compute = None
+        for slot in unit.slots:
+            unit.point_parameter_at_placeholder(slot)
+
+    def _install_gather_hooks(self, unit: FlatUnit, module: nn.Module) -> None:
+        unit.in_backward = False
+
+        def before_forward(mod, args):
+            self.gather_unit(unit)
+
+        def after_forward(mod, args, output):
+            if not unit.in_backward:  # a forward pass re-run inside the backward pass (activation checkpointing) keeps them
+                self.release_unit(unit)
+
+        def before_backward(mod, grad_output):
+            unit.in_backward = True
+            self.gather_unit(unit, for_backward=True)
+
+        def after_backward(mod, grad_input, grad_output):
+            unit.in_backward = False
+            self.release_unit(unit)
+
+        module.register_forward_pre_hook(before_forward)
+        module.register_forward_hook(after_forward)
+        module.register_full_backward_pre_hook(before_backward)
+        module.register_full_backward_hook(after_backward)
+
     # ------------------------------------------------------------------ views for the optimizer
     def segments(self) -> list[Segment]:
         return [seg for unit in self.units for seg in unit.segments]
@@ -366,10 +486,12 @@ class ShardedTrainingEngine:
     @torch.no_grad()
     def fold_autograd_grads(self) -> None:
         """Add gradients that autograd left in ``param.grad`` into the fp32 accumulation buffers."""
-        for _, slot in self.named_slots():
+        for unit, slot in self.named_slots():
             g = slot.param.grad
             if g is None:
                 continue
+            if not unit.resident and not hasattr(slot.param, "main_grad"):
+                raise RuntimeError(f"{slot.name}: a gradient arrived after the unit's gradients were reduced and released")
             if g.is_cuda and g.dtype == torch.bfloat16 and ops.native_available() and g.is_contiguous():
                 ops.native().cast_bf16_to_f32(g.view(-1), slot.param.main_grad.view(-1), True, 1.0)
             else:
@@ -380,7 +502,7 @@ class ShardedTrainingEngine:
     @torch.no_grad()
     def zero_grad(self) -> None:
         for unit in self.units:
-            unit.grad.zero_()
+            (unit.grad if unit.resident else unit.grad_shard).zero_()
 
     # ------------------------------------------------------------------ reduction under the last backward pass
     def arm_early_reduction(self) -> bool:
@@ -432,7 +554,7 @@ class ShardedTrainingEngine:
                 self.peer.barrier()
             with site("step.reduce_scatter"):
                 for unit in self.units:
-                    if not unit.local_only and id(unit) not in self._early_reduced:
+                    if not unit.local_only and unit.resident and id(unit) not in self._early_reduced:
                         self.peer.reduce_scatter_f32(arena, unit.grad_shard, unit.grad_shard)
             with site("step.barrier_after_reduce_scatter"):
                 self.peer.barrier()
@@ -441,7 +563,9 @@ class ShardedTrainingEngine:
         for unit in self.units:
             if unit.local_only:
                 continue
-            if self.shard_world > 1 and self.peer is None:
+            if not unit.resident:
+                self.release_unit(unit)  # normally done by the backward hook already
+            elif self.shard_world > 1 and self.peer is None:
                 reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
             if self.replica_world > 1:
                 all_reduce_sum(unit.grad_shard, self.replica_group)
@@ -525,8 +649,7 @@ class ShardedTrainingEngine:
         broadcast_by_optimizer = masters_already_cast and broadcast_done and self.peer is not None
         for unit in self.units:
             if not unit.master_is_alias and not masters_already_cast:
-                lo, hi = unit.shard_range
-                dst = unit.compute[lo:hi]
+                dst = unit.compute_shard
                 if dst.is_cuda and ops.native_available() and dst.dtype == torch.bfloat16:
                     ops.native().cast_f32_to_bf16(unit.master, dst)
                 else:
@@ -536,11 +659,11 @@ class ShardedTrainingEngine:
                 arena = self.arenas[self.compute_dtype]
                 self.peer.barrier()
                 for unit in self.units:
-                    if not unit.local_only:
+                    if not unit.local_only and unit.resident:
                         self.peer.all_gather(arena, unit.compute, unit.shard_numel)
             else:
                 for unit in self.units:
-                    if not unit.local_only:
+                    if not unit.local_only and unit.resident:
                         all_gather_in_place(unit.compute, unit.shard_numel, unit.rank, self.shard_group, False)
         if self.peer is not None:
             self.peer.barrier()  # every rank's stores into this rank's copy have landed before the next forward pass
@@ -569,7 +692,7 @@ class ShardedTrainingEngine:
             lr_scheduler.step()
         with site("step.refresh_parameters"):
             self.refresh_parameters(masters_already_cast=fused, broadcast_done=fused and getattr(optimizer, "last_step_broadcast", False))
-        if fused and self.shard_world == 1:
+        if fused and (self.shard_world == 1 or all(not u.resident or u.local_only for u in self.units)):
             pass  # the fused kernel cleared every gradient element it consumed
         else:
             with site("step.zero_grad"):
@@ -596,7 +719,8 @@ class ShardedTrainingEngine:
 
     def memory_summary(self) -> dict[str, float]:
         gib = 1 / 2**30
-        compute = sum(u.compute.numel() * u.compute.element_size() for u in self.units)
-        grads = sum(u.grad.numel() * 4 for u in self.units)
+        width = torch.empty((), dtype=self.compute_dtype).element_size()
+        compute = sum((u.numel if u.resident else u.shard_numel) * width for u in self.units)
+        grads = sum((u.numel if u.resident else u.shard_numel) * 4 for u in self.units)
         master = sum(0 if u.master_is_alias else u.master.numel() * 4 for u in self.units)
         return {"compute_GiB": compute * gib, "grad_GiB": grads * gib, "master_GiB": master * gib}

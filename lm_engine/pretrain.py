@@ -255,6 +255,9 @@ def main(mode: Mode = Mode.training, argv: list[str] | None = None) -> None:
                 gradient_accumulation_steps=args.training_parameters.gradient_accumulation_steps)
     set_seed(args.random_args.seed)
 
+    from . import ops
+
+    ops.set_strict(args.kernel_args.strict)
     with enable_kernels(args.kernel_args.kernels):
         model_container = get_model_container(args, mode)
         model_container, pipeline_schedule = wrap_model_container_for_distributed_training(args, model_container)

@@ -49,7 +49,8 @@ def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, 
         lr_scheduler_args=dict(lr_decay_style="cosine", num_warmup_steps=2),
         mixed_precision_args=dict(dtype="fp32"),
         distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp, pipeline_parallel_world_size=pp,
-                              num_pipeline_stages=stages, pipeline_parallel_schedule=schedule, **({"expert_parallel_world_size": ep} if ep > 1 else {})),
+                              num_pipeline_stages=stages, pipeline_parallel_schedule=schedule, **({"expert_parallel_world_size": ep} if ep > 1 else {}),
+                              **({"keep_parameters_gathered": False} if os.environ.get("TINY_SHARDED_PARAMETERS") == "1" else {})),
     )
 
 

@@ -11,9 +11,10 @@ import pytest
 SCRIPT = os.path.join(os.path.dirname(__file__), "scripts", "tiny_pretrain.py")
 
 
-def _run(tmp_path, world: int, port: int, stage: int = 3):
-    out = tmp_path / f"curve_w{world}_s{stage}.json"
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+def _run(tmp_path, world: int, port: int, stage: int = 3, sharded_parameters: bool = False):
+    out = tmp_path / f"curve_w{world}_s{stage}_{int(sharded_parameters)}.json"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="",
+               TINY_SHARDED_PARAMETERS="1" if sharded_parameters else "0")
     if world == 1:
         cmd = [sys.executable, SCRIPT, str(out), "8", "20", str(stage)]
     else:
@@ -32,3 +33,16 @@ def test_two_rank_loss_curve_matches_single_process(tmp_path, stage):
         assert abs(a["loss"] - b["loss"]) < 2e-5 * max(1.0, abs(a["loss"]))
         assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-4 * max(1.0, abs(a["grad_norm"]))
     assert single[-1]["loss"] < single[0]["loss"]
+
+
+def test_blocks_gathered_and_released_one_by_one_give_the_same_curve(tmp_path):
+    """``keep_parameters_gathered: false``: every block's parameters exist in full only during its forward and its
+    backward pass, its gradients are reduce-scattered right after its backward pass. Same losses and gradient norms
+    as one process, on two and on four ranks."""
+    single = _run(tmp_path, 1, 29641, 3)
+    for world, port in ((2, 29643), (4, 29645)):
+        other = _run(tmp_path, world, port, 3, sharded_parameters=True)
+        assert len(single) == len(other) == 20
+        for a, b in zip(single, other):
+            assert abs(a["loss"] - b["loss"]) < 2e-5 * max(1.0, abs(a["loss"]))
+            assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-4 * max(1.0, abs(a["grad_norm"]))

@@ -324,6 +324,52 @@ def test_attention_fwd_bwd(C, groups, qpg, d, lengths):
     assert _rel_err(mine[:, :, :qpg], g[:, :, :qpg]) < 2e-2  # dQ
 
 
+@pytest.mark.parametrize("d,groups,qpg", [(80, 2, 2), (96, 1, 4), (32, 2, 1)])
+def test_attention_head_widths_between_the_kernel_widths(C, d, groups, qpg):
+    """Head widths the kernels do not have (80, 96, 32) run on the next wider kernel over zero-padded heads: outputs
+    and gradients against the fp32 reference, with strict mode on so that a PyTorch path would raise."""
+    from lm_engine import ops
+    from lm_engine.ops.attention import attention_fused_qkv
+
+    torch.manual_seed(0)
+    lengths = [300, 77, 513]
+    T = sum(lengths)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device="cuda")
+    qkv = torch.randn(T, groups * (qpg + 2) * d, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    scale = d**-0.5
+    ops.set_strict(True)
+    try:
+        out = attention_fused_qkv(qkv, cu, max(lengths), groups, qpg, d, scale, True)
+        dout = torch.randn_like(out)
+        out.backward(dout)
+    finally:
+        ops.set_strict(False)
+    ops.check_status()
+    q32 = qkv.detach().float().requires_grad_(True)
+    ref = _attention_reference(q32, cu, groups, qpg, d, scale)
+    ref.backward(dout.float())
+    assert out.shape == ref.shape
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(qkv.grad, q32.grad) < 2e-2
+
+
+def test_strict_mode_turns_a_pytorch_fallback_into_an_error(C):
+    from lm_engine import ops
+
+    a = torch.randn(64, 24, device="cuda", dtype=torch.bfloat16)[:, :20]  # row stride 24 elements is fine, inner size 20 is not
+    w = torch.randn(32, 20, device="cuda", dtype=torch.bfloat16)
+    before = sum(ops.fallback_counts().values())
+    out = ops.linear(a, w)  # counted, logged once, computed by PyTorch
+    assert _rel_err(out, a.float() @ w.float().t()) < 1e-2
+    assert sum(ops.fallback_counts().values()) == before + 1
+    ops.set_strict(True)
+    try:
+        with pytest.raises(RuntimeError, match="strict mode"):
+            ops.linear(a, w)
+    finally:
+        ops.set_strict(False)
+
+
 @pytest.mark.parametrize("T,H,I,E,k", [(300, 256, 128, 4, 2), (1000, 512, 256, 8, 4), (64, 128, 64, 40, 8)])
 def test_scattered_experts_fwd_bwd(C, T, H, I, E, k):
     from lm_engine.ops.moe import scattered_experts_mlp

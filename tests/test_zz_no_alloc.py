@@ -56,8 +56,8 @@ def test_no_alloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         dh = torch.empty_like(x)
         dw = torch.full((H,), 123.0, device="cuda")
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]  # the driver's view: catches allocations that bypass torch's allocator
         allocated_before = torch.cuda.memory_allocated()
-        free_before, _ = torch.cuda.mem_get_info()  # the driver's view: catches allocations that bypass torch's allocator
         code, message = _call(fn, dy, x, w, rstd, dres, dh, dw, False)
         assert code == 0, message
         torch.cuda.synchronize()
