@@ -184,10 +184,8 @@ def run_native(cli) -> dict:
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
     expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
-    # expert row buffers: up to four times a rank's balanced share (the worst case, every entry of the group on one rank,
-    # for 2 and 4 ranks; half of it for 8); the number of entries this bound dropped is reported and must be 0 for the
-    # run to count as dropless
-    capacity = float(min(expert_parallel, 4))
+    # expert row buffers are sized exactly for the fullest rank of every layer (no capacity factor: nothing can be dropped)
+    capacity = None
     extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else None
     args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
 

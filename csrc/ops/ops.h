@@ -66,4 +66,11 @@ void gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long l
               bool b_mn, int a_fmt, int b_fmt, int epi, float alpha, const float* scale_a, const float* scale_b, int* status,
               cudaStream_t stream);
 
+// MXFP8 GEMM (gemm/gemm_mxfp8.cu): 8-bit payloads with one UE8M0 scale per 32 elements along K, scale codes in 512-byte
+// tiles of 128 rows x 4 blocks; mx_scale_bytes gives the size of such a buffer.
+long long mx_scale_bytes(long long rows, long long k);
+void gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long lda,
+                long long ldb, long long ldc, bool a_mn, bool b_mn, int a_fmt, int b_fmt, int epi, float alpha, int* status,
+                cudaStream_t stream);
+
 }  // namespace b200

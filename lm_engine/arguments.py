@@ -216,8 +216,9 @@ class DistributedArgs(BaseArgs):
     expert_parallel_world_size: int = 1
     # True: collectives are issued from this engine's own peer-memory kernels; False: NCCL baseline path
     fused_collectives: bool = True
-    # expert parallelism: row buffers hold this multiple of a rank's balanced share of the routed entries; entries
-    # beyond it are dropped. None: buffers are sized for the worst case and nothing is ever dropped.
+    # expert parallelism: None = dropless, row buffers sized per layer for the fullest rank (one small device-to-host
+    # read per MoE layer); a factor >= 1 = static buffers of that multiple of a rank's balanced share, no host read,
+    # entries beyond it are dropped and counted.
     expert_capacity_factor: float | None = None
     # ZeRO-3 only. None: keep the gathered bf16 weights for a whole optimizer step when they fit in memory,
     # otherwise gather per block; True / False force one or the other.

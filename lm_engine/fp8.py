@@ -7,10 +7,13 @@ operands, so the forward, data-gradient and weight-gradient products use the sam
 transposed copies.
 
 ``fp8_recipe: mxfp8`` selects the OCP microscaling format instead: e4m3 payload with one power-of-two (E8M0) scale per 32
-consecutive elements along the contraction dimension of each product. Its operands are quantised exactly as the format
-prescribes and multiplied after dequantisation by the bf16 tcgen05 GEMM, which reproduces the numerics of MXFP8
-training; a GEMM that consumes the block scales natively (``tcgen05.mma.kind::mxf8f6f4.block_scale``) does not exist
-here yet, so this recipe has the speed of bf16 plus the quantisation passes.
+consecutive elements along the contraction dimension of each product. On the GPU a quantisation kernel writes payload
+and scale codes (the latter in the tile layout the tensor core reads) and the products run on the block-scaled tcgen05
+GEMM (``tcgen05.mma.kind::mxf8f6f4.block_scale``, ``csrc/gemm/gemm_mxfp8.cu``): forward with blocks along the input
+features of activations and weights, data gradient with blocks along the output features (the weight read MN-major),
+weight gradient with blocks along the tokens (both operands read MN-major), i.e. every tensor is quantised once per
+direction it is contracted along. Sizes that are not multiples of 128, and CPU tensors, take the PyTorch restatement
+of the same format (quantise, dequantise, multiply), which is also the numerical oracle of the kernels.
 """
 
 from __future__ import annotations
@@ -91,7 +94,62 @@ class _MXLinear(torch.autograd.Function):
         return dx.view(ctx.shape), dw.to(weight.dtype), db
 
 
+class _MXLinearNative(torch.autograd.Function):
+    """The same three products on the block-scaled GEMM. ``quantize_mx(t, along_rows)`` quantises a row-major matrix in
+    blocks of 32 along its columns (``False``) or along its rows (``True``) and returns payload and tiled scale codes."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        C, st = ops.native(), ops.status_word(x.device)
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        xq, xs = C.quantize_mx(x2, False, E4M3)
+        wq, ws = C.quantize_mx(weight.contiguous(), False, E4M3)
+        y = torch.empty(x2.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+        C.gemm_mxfp8(xq, xs, wq, ws, y, False, False, E4M3, E4M3, False, 1.0, st)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x2)
+        ctx.weight, ctx.shape, ctx.has_bias = weight, shape, bias is not None
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        weight = ctx.weight
+        C, st = ops.native(), ops.status_word(dy.device)
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        # dx[T, in] = dy[T, out] . W[out, in]: blocks along the output features; W read MN-major
+        gq, gs = C.quantize_mx(dy2, False, E4M3)
+        wq, ws = C.quantize_mx(weight.contiguous(), True, E4M3)
+        dx = torch.empty(dy2.shape[0], weight.shape[1], dtype=torch.bfloat16, device=dy.device)
+        C.gemm_mxfp8(gq, gs, wq, ws, dx, False, True, E4M3, E4M3, False, 1.0, st)
+        # dW[out, in] = dy^T . x: blocks along the tokens; both read MN-major; accumulated into the fp32 main gradient
+        # when the engine provides one
+        gq, gs = C.quantize_mx(dy2, True, E4M3)
+        xq, xs = C.quantize_mx(x2, True, E4M3)
+        target = getattr(weight, "main_grad", None)
+        if target is not None:
+            C.gemm_mxfp8(gq, gs, xq, xs, target, True, True, E4M3, E4M3, True, 1.0, st)
+            dw = None
+        else:
+            dw32 = torch.empty(weight.shape, dtype=torch.float32, device=dy.device)
+            C.gemm_mxfp8(gq, gs, xq, xs, dw32, True, True, E4M3, E4M3, False, 1.0, st)
+            dw = dw32.to(weight.dtype)
+        db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx.view(ctx.shape), dw, db
+
+
+def _mx_native_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    tokens = x.numel() // x.shape[-1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and ops.native_available()
+            and hasattr(ops.native(), "gemm_mxfp8") and tokens % 128 == 0 and weight.shape[0] % 128 == 0 and weight.shape[1] % 128 == 0)
+
+
 def mx_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    if _mx_native_ok(x, weight):
+        return _MXLinearNative.apply(x, weight, bias)
+    ops.note_fallback("mx_linear", "token count or feature sizes are not multiples of 128", x, weight)
     return _MXLinear.apply(x, weight, bias)
 
 

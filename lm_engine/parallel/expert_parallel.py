@@ -33,9 +33,13 @@ from .symmetric import PeerBuffer, PeerGroup, get_peer_group
 
 _WORKSPACES: dict[int, "_Workspace"] = {}
 
-# Row buffers of a rank hold at most ``capacity_factor x (its balanced share of the routed entries)`` rows (plus tile
-# padding); None sizes them for the worst case, in which every entry of the group lands on one rank. Entries beyond the
-# bound are dropped (they contribute nothing to their token) and counted on the device in ``_DROPPED``.
+# Sizing of the per-rank row buffers (expert inputs, projections, outputs):
+#   None (default)  exact and dropless: every rank derives, from the routing table it already holds for the whole group,
+#                   the tile-padded row count of the fullest rank and reads it back (one small device-to-host read per
+#                   MoE layer and forward pass); buffers then hold what the busiest rank needs, nothing is ever dropped
+#   a factor >= 1   static bound without a host read: ``factor x (a rank's balanced share of the routed entries)`` rows
+#                   (plus tile padding); entries beyond it are dropped (they contribute nothing to their token) and
+#                   counted on the device in ``_DROPPED``
 _CAPACITY_FACTOR: float | None = None
 # CTAs of the fused dispatch + GEMM kernel that pull rows from the peers (each keeps about 190 KB in flight)
 _GATHER_CTAS = int(os.environ.get("LM_ENGINE_MOE_GATHER_CTAS", "32"))
@@ -54,9 +58,15 @@ def dropped_entries(device: torch.device) -> int:
     return 0 if counter is None else int(counter.item())
 
 
-def _capacity_rows(entries_per_rank: int, local_experts: int) -> int | None:
+def _capacity_rows(entries_per_rank: int, local_experts: int, selected_all: torch.Tensor | None = None,
+                   num_experts: int | None = None) -> int | None:
     if _CAPACITY_FACTOR is None:
-        return None
+        if selected_all is None:
+            return None
+        # rows of the fullest rank, identical on every rank because all of them hold the same routing table
+        counts = torch.bincount(selected_all.long(), minlength=num_experts)[:num_experts]
+        padded = (counts + TILE - 1) // TILE * TILE
+        return max(TILE, int(padded.view(-1, local_experts).sum(dim=1).max().item()))
     return int(_CAPACITY_FACTOR * entries_per_rank + 0.5) + local_experts * (TILE - 1)
 
 
@@ -195,7 +205,7 @@ class _ExpertParallelFn(torch.autograd.Function):
         selected_all = torch.cat(_all_gather_plain(selected_experts.reshape(-1).to(torch.int32)))
         weights_all = torch.cat(_all_gather_plain(router_weights.reshape(-1).float()))
         layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
-                                      capacity_rows=_capacity_rows(entries, local))
+                                      capacity_rows=_capacity_rows(entries, local, selected_all, num_experts))
         _count_dropped(layout)
         rows = layout.rows
 

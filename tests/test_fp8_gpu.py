@@ -71,3 +71,86 @@ def test_fp8_manager_converts_linears():
     loss.backward()
     assert abs(float(loss) - float(reference)) < 0.05 * float(reference)
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+@pytest.mark.parametrize("along_rows", [False, True])
+@pytest.mark.parametrize("shape", [(256, 384), (1024, 128), (384, 1280)])
+def test_mx_quantisation_kernel_matches_the_format_definition(along_rows, shape):
+    """Payload bytes and scale codes of the kernel equal the PyTorch statement of OCP MXFP8 (e4m3, shared exponent
+    floor(log2(amax)) - 8, round to nearest even), for blocks along the columns and along the rows."""
+    from lm_engine import ops
+    from lm_engine.fp8 import mx_quantize
+
+    torch.manual_seed(0)
+    C = ops.native()
+    x = (torch.randn(*shape, device="cuda") * torch.exp(torch.randn(*shape, device="cuda") * 3)).bfloat16()
+    x[0, :64] = 0  # an all-zero block
+    q, sf = C.quantize_mx(x, along_rows, 0)
+    ref_q, ref_s = mx_quantize(x, dim=0 if along_rows else 1)
+    assert torch.equal(q, ref_q.view(torch.uint8))
+    rows, k = (shape[1], shape[0]) if along_rows else shape
+    plain = C.mx_scales_to_plain(sf, rows, k)
+    expected = ref_s.t().contiguous() if along_rows else ref_s
+    assert torch.equal(plain, expected)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(384, 512, 640), (128, 256, 128), (1000, 776, 1024)])
+def test_block_scaled_gemm_against_the_dequantised_product(a_mn, b_mn, shape):
+    from lm_engine import ops
+    from lm_engine.fp8 import mx_dequantize, mx_quantize
+
+    torch.manual_seed(1)
+    C, st = ops.native(), ops.status_word(torch.device("cuda"))
+    M, N, K = shape
+    if (a_mn and M % 16) or (b_mn and N % 16):
+        pytest.skip("MN-major 8-bit operands need a row length that is a multiple of 16 bytes")
+    # values spread over many binades so that a wrong scale block shows up at once
+    a = (torch.randn(M, K, device="cuda") * torch.exp2(torch.randint(-6, 6, (M, K // 32), device="cuda").repeat_interleave(32, 1).float())).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * torch.exp2(torch.randint(-6, 6, (N, K // 32), device="cuda").repeat_interleave(32, 1).float())).bfloat16()
+    a_in = a.t().contiguous() if a_mn else a          # what the GEMM reads: [K, M] when MN-major
+    b_in = b.t().contiguous() if b_mn else b
+    aq, asf = C.quantize_mx(a_in, a_mn, 0)            # blocks always run along K
+    bq, bsf = C.quantize_mx(b_in, b_mn, 0)
+    a_ref = mx_dequantize(*mx_quantize(a, dim=1), dim=1)
+    b_ref = mx_dequantize(*mx_quantize(b, dim=1), dim=1)
+    ref = a_ref @ b_ref.t()
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    C.gemm_mxfp8(aq, asf, bq, bsf, out, a_mn, b_mn, 0, 0, False, 1.0, st)
+    ops.check_status()
+    assert ((out - ref).norm() / ref.norm()).item() < 1e-5  # same operands, fp32 accumulation: only the summation order differs
+    base = torch.randn(M, N, device="cuda")
+    acc = base.clone()
+    C.gemm_mxfp8(aq, asf, bq, bsf, acc, a_mn, b_mn, 0, 0, True, 0.5, st)
+    assert ((acc - (base + 0.5 * ref)).norm() / ref.norm()).item() < 1e-5
+    ops.check_status()
+
+
+def test_mx_linear_runs_the_block_scaled_kernels_and_matches_the_emulation():
+    from lm_engine import ops
+    from lm_engine.fp8 import _MXLinear, mx_linear
+
+    torch.manual_seed(2)
+    x = torch.randn(512, 768, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(1024, 768, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    bias = torch.randn(1024, device="cuda").bfloat16().requires_grad_(True)
+    ops.set_strict(True)
+    try:
+        y = mx_linear(x, w, bias)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+    finally:
+        ops.set_strict(False)
+    ops.check_status()
+    xe, we, be = (t.detach().clone().requires_grad_(True) for t in (x, w, bias))
+    ye = _MXLinear.apply(xe, we, be)
+    ye.backward(dy)
+
+    def relative(a, b):
+        return float((a.float() - b.float()).norm() / b.float().norm())
+
+    assert relative(y, ye) < 1e-2          # same quantised operands; bf16 rounding of the emulation's operands and outputs
+    assert relative(x.grad, xe.grad) < 1e-2
+    assert relative(w.grad, we.grad) < 1e-2
+    xr, wr = x.detach().float(), w.detach().float()
+    assert relative(y, xr @ wr.t() + bias.detach().float()) < 0.05  # and close to the unquantised product
