@@ -57,6 +57,8 @@ def parse_args():
     p.add_argument("--moe-steps", type=int, default=None, help="timed steps of the MoE record (default: max(3, steps // 4))")
     p.add_argument("--reference-compile", type=str, default="auto", choices=["auto", "on", "off"],
                    help="reference arm: its own distributed_args.torch_compile option (auto = the faster one as measured on a B200)")
+    p.add_argument("--sharded-parameters", action="store_true",
+                   help="distributed_args.keep_parameters_gathered=false: blocks are gathered and released one by one (not the headline mode)")
     p.add_argument("--budget-output", type=str, default=None,
                    help="after the timed regions run one more step with per-site device timers and write the per-kernel time budget there (JSON)")
     p.add_argument("--child-output", type=str, default=None, help=argparse.SUPPRESS)
@@ -186,7 +188,9 @@ def run_native(cli) -> dict:
     expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
     # expert row buffers are sized exactly for the fullest rank of every layer (no capacity factor: nothing can be dropped)
     capacity = None
-    extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else None
+    extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else {}
+    if cli.sharded_parameters:
+        extra["keep_parameters_gathered"] = False
     args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
 
     init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel)
@@ -297,12 +301,15 @@ def run_native(cli) -> dict:
         "config": {"model": spec["name"] + ("" if cli.layers is None else f"-DEBUG-{cli.layers}-layers"),
                    "global_batch": ga * mb * world, "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
                    "parallelism": (f"ep{expert_parallel} x " if moe else "") +
-                   f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; gathered bf16 weights kept for the step)",
+                   f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; " +
+                   ("blocks gathered and released one by one)" if cli.sharded_parameters else "gathered bf16 weights kept for the step)"),
                    "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)",
                    "kernels": kernels, "gradient_checkpointing": None},
         "tflops_per_gpu": tflops_per_gpu, "mfu": tflops_per_gpu / peak, "mfu_peak": f"{peak} TFLOP/s {peak_src}",
         "clocks": clocks, "gpu_launches": launches, "pytorch_fallbacks": sum(ops.fallback_counts().values()), "loss_after_warmup": loss_after_warmup,
         "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
+        # the driver's view (includes the symmetric-memory arenas, which the tensor allocator does not see)
+        "device_memory_used_gib": (torch.cuda.mem_get_info()[1] - torch.cuda.mem_get_info()[0]) / 2**30,
     }
     if expert_parallel > 1:
         from lm_engine.parallel.expert_parallel import dropped_entries
@@ -360,7 +367,7 @@ def main() -> None:
         result = run_reference(cli, SPECS[cli.config], REPO_ROOT)
     else:
         result = run_native(cli)
-    headline = cli.config == "dense" and cli.layers is None and cli.gradient_accumulation_steps is None
+    headline = cli.config == "dense" and cli.layers is None and cli.gradient_accumulation_steps is None and not cli.sharded_parameters
     if headline and not cli.no_moe and cli.child_output is None:
         # the metric names both models: the MoE record rides along under "moe"; the headline `value` stays the dense one
         moe = moe_record(cli)

@@ -28,6 +28,8 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ... import ops
+from ...enums import Kernel
+from ...kernels import is_kernel_allowed
 from ...utils import ProcessGroupManager, SafeTensorsWeightsManager, divide_if_divisible
 from ...parallel import tensor_parallel as tp
 from ..config import CommonConfig, GPTBaseConfig, LadderResidualConfig
@@ -149,6 +151,9 @@ class RowParallelLinear(nn.Module):
         super().__init__()
         self.in_features, self.out_features, self.std = in_features, out_features, std
         self.sequence_parallel = sequence_parallel
+        # True: forward only starts the reduction of the output; whoever consumes it calls tp.finish_reduction (the ladder
+        # residual blocks do, one sub-block later, so that the collective runs under that sub-block's compute)
+        self.overlap_reduction = False
         self.in_features_per_rank = divide_if_divisible(in_features, tp.tp_world(), "input features must be divisible by the tensor parallel size")
         self.weight = nn.Parameter(torch.empty(out_features, self.in_features_per_rank))
         self.bias = nn.Parameter(torch.empty(out_features)) if bias else None
@@ -171,6 +176,8 @@ class RowParallelLinear(nn.Module):
                 y = fused_tp.linear_rs(x, self.weight)  # reduce-scatter inside the GEMM epilogue
                 return y if self.bias is None else y + self.bias
         y = ops.linear(x, self.weight, None)
+        if self.overlap_reduction and self.bias is None:
+            return tp.row_parallel_output_async(y, self.sequence_parallel)
         y = tp.row_parallel_output(y, self.sequence_parallel)
         return y if self.bias is None else y + self.bias
 
@@ -496,14 +503,31 @@ class LadderResidualBlock_TP(Block_TP):
     """The block of ``ladder_residual``: the outputs of the previous block join the stream here, one step late, so
     their reductions have the previous sub-block's compute to hide behind."""
 
+    def _overlap(self) -> bool:
+        """``Kernel.ladder_residual_overlapped_layer``: the reductions of the two row-parallel projections are started
+        and left running; the previous block's attention output is waited for before this block's attention input is
+        formed and its MLP output before this block's MLP input, i.e. every reduction has one sub-block of compute to
+        hide behind (parity: lm_engine/hf_models/models/ladder_residual_TP/layer.py:140-390 of the reference, which does
+        the same with asynchronous functional collectives). Needs projections without bias and without dropout, and
+        the plain (not kernel-fused) collectives."""
+        plain = lambda module: isinstance(module, nn.Identity) or getattr(module, "p", 0) == 0  # noqa: E731
+        ok = (is_kernel_allowed(Kernel.ladder_residual_overlapped_layer) and tp.tp_world() > 1 and self.m_residual is None
+              and isinstance(self.mlp_block, MLP_TP) and plain(self.sequence_mixer.dropout) and plain(self.mlp_block.dropout)
+              and self.sequence_mixer.c_proj.bias is None and self.mlp_block.c_proj.bias is None
+              and not ProcessGroupManager.is_async_tensor_parallel_enabled())
+        self.sequence_mixer.c_proj.overlap_reduction = ok
+        self.mlp_block.c_proj.overlap_reduction = ok
+        return ok
+
     def forward(self, current_attention_out, current_mlp_out, residual, ctx, past_key_values=None):
+        self._overlap()
         if current_attention_out is not None:
-            residual = residual + current_attention_out
+            residual = residual + tp.finish_reduction(current_attention_out)
         current_attention_out = self.sequence_mixer(self.ln_1(residual), ctx, past_key_values)
         if self.m_residual is not None:
             current_attention_out = current_attention_out * self.m_residual
         if current_mlp_out is not None:
-            residual = residual + current_mlp_out
+            residual = residual + tp.finish_reduction(current_mlp_out)
         current_mlp_out = self.mlp_block(self.ln_2(residual))
         if self.m_residual is not None:
             current_mlp_out = current_mlp_out * self.m_residual
@@ -745,7 +769,7 @@ class LadderResidualModel_TP(LadderResidualPreTrainedModel_TP, BaseModelMixin_TP
         residual = hidden_states
         for block in self.h.values():
             attention_out, mlp_out, residual = block(attention_out, mlp_out, residual, ctx, past_key_values)
-        return residual + attention_out + mlp_out
+        return residual + tp.finish_reduction(attention_out) + tp.finish_reduction(mlp_out)
 
 
 class LadderResidualForCausalLM_TP(LadderResidualPreTrainedModel_TP, CausalLMModelMixin_TP):

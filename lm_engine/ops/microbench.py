@@ -149,6 +149,42 @@ def bench_gemm(args) -> None:
                    gemm_then_swiglu_ms=round(ms_u, 4), status=int(st.item())))
 
 
+def bench_mxfp8(args) -> None:
+    """Block-scaled MXFP8 GEMM and its quantisation kernels; denominators: this library's bf16 GEMM on the same shape and
+    ``torch._scaled_mm`` (the library's tensor-scaled fp8 GEMM) as the measured fp8 rate of the machine."""
+    C, st = native(), status_word(torch.device("cuda"))
+    flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
+    shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes] if args.shapes else [
+        (8192, 6144, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 8192, 8192)]
+    for M, N, K in shapes:
+        flops = 2.0 * M * N * K
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        aq, asf = C.quantize_mx(a, False, 0)
+        bq, bsf = C.quantize_mx(b, False, 0)
+        record = dict(op="gemm_mxfp8", layout="nt", m=M, n=N, k=K)
+        ms = _time(lambda: C.gemm_mxfp8(aq, asf, bq, bsf, out, False, False, 0, 0, False, 1.0, st), args.iters, args.warmup, flush)
+        record["mxfp8_ms"], record["mxfp8_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+        ms = _time(lambda: C.gemm(a, b, out, False, False, False, 1.0, st, 0, 2), args.iters, args.warmup, flush)
+        record["bf16_pair_ms"], record["bf16_pair_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+        ms = _time(lambda: C.quantize_mx(a, False, 0), args.iters, args.warmup, flush)
+        record["quantize_along_columns_ms"], record["quantize_along_columns_gbs"] = round(ms, 4), round(M * K * 3.03 / ms / 1e6, 1)
+        if M % 128 == 0:
+            ms = _time(lambda: C.quantize_mx(a, True, 0), args.iters, args.warmup, flush)
+            record["quantize_along_rows_ms"], record["quantize_along_rows_gbs"] = round(ms, 4), round(M * K * 3.03 / ms / 1e6, 1)
+        if not args.profile and hasattr(torch, "_scaled_mm"):
+            try:
+                a8, b8 = a.to(torch.float8_e4m3fn), b.to(torch.float8_e4m3fn)
+                one = torch.ones((), device="cuda")
+                ms = _time(lambda: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), args.iters, args.warmup, flush)
+                record["library_fp8_ms"], record["library_fp8_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
+            except Exception as error:  # the library call is only a yardstick
+                record["library_fp8_error"] = f"{type(error).__name__}: {error}"[:200]
+        record["status"] = int(st.item())
+        _emit(record)
+
+
 def bench_attention(args) -> None:
     C, st = native(), status_word(torch.device("cuda"))
     flush = None if args.profile else torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device="cuda")
@@ -313,7 +349,7 @@ def bench_scans(args) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("op", choices=["gemm", "attention", "moe", "elementwise", "scans"])
+    parser.add_argument("op", choices=["gemm", "mxfp8", "attention", "moe", "elementwise", "scans"])
     parser.add_argument("--shapes", nargs="*", help="gemm: MxNxK ...; attention: SEQUENCESxLENGTH ...")
     parser.add_argument("--layouts", nargs="*", default=["nt"], help="gemm: nt (y = x w^T), nn (dgrad), tn (wgrad)")
     parser.add_argument("--variant", default="all", choices=["all", "cta1", "cta_pair"])
@@ -340,7 +376,7 @@ def main() -> None:
     parser.add_argument("--top-k", type=int, default=8)
     parser.add_argument("--vocab", type=int, default=128256)
     args = parser.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "moe": bench_moe, "elementwise": bench_elementwise, "scans": bench_scans}[args.op](args)
+    {"gemm": bench_gemm, "mxfp8": bench_mxfp8, "attention": bench_attention, "moe": bench_moe, "elementwise": bench_elementwise, "scans": bench_scans}[args.op](args)
 
 
 if __name__ == "__main__":

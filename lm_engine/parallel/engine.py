@@ -520,7 +520,7 @@ class ShardedTrainingEngine:
     def unit_backward_done(self, unit: "FlatUnit") -> None:
         """Every gradient of ``unit`` for this optimizer step is in its fp32 buffer (called by the backward pass of the
         unit's last micro-step, on the compute stream)."""
-        if not self.early_reduction_armed or unit.local_only or id(unit) in self._early_reduced:
+        if not self.early_reduction_armed or unit.local_only or not unit.resident or id(unit) in self._early_reduced:
             return
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)

@@ -187,6 +187,84 @@ def row_parallel_output(y: torch.Tensor, sequence_parallel: bool) -> torch.Tenso
     return scatter_tokens(y, token_dim(y)) if sequence_parallel else reduce_from_tp(y)
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# reductions that run under the next piece of compute (ladder residual)
+class _StartReduction(torch.autograd.Function):
+    """Starts the all-reduce / reduce-scatter of a row-parallel output and returns at once. The result must not be read
+    before :func:`finish_reduction` has been applied to it. Backward is the transposed collective of the synchronous
+    functions (identity / all-gather), run in place."""
+
+    @staticmethod
+    def forward(ctx, y, sequence_parallel):
+        ctx.sequence_parallel = sequence_parallel
+        ctx.dim = token_dim(y)
+        world = tp_world()
+        y = y.contiguous()
+        ctx.sliced_later = False
+        if not sequence_parallel:
+            out = y.clone()
+            work = dist.all_reduce(out, group=tp_group(), async_op=True)
+        elif y.is_cuda and ctx.dim == 0:
+            out = y.new_empty((y.shape[0] // world, *y.shape[1:]))
+            work = dist.reduce_scatter_tensor(out, y, group=tp_group(), async_op=True)
+            out._reduction_input = y  # the input must stay alive until the collective has read it
+        else:
+            total = y.clone()
+            work = dist.all_reduce(total, group=tp_group(), async_op=True)  # gloo has no reduce-scatter
+            out = total
+            out._slice = (ctx.dim, world, tp_rank())
+            ctx.sliced_later = True
+        out._pending_reduction = work
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.sliced_later:
+            return _all_reduce(g), None  # g holds this rank's slice and zeros elsewhere: the sum over ranks is the gather
+        return (_all_gather(g, ctx.dim) if ctx.sequence_parallel else g), None
+
+
+class _FinishReduction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        work = getattr(x, "_pending_reduction", None)
+        if work is not None:
+            work.wait()
+            x._pending_reduction = None
+        piece = getattr(x, "_slice", None)
+        ctx.piece = piece
+        if piece is not None:
+            dim, world, rank = piece
+            return x.chunk(world, dim=dim)[rank].contiguous()
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.piece is not None:
+            dim, world, rank = ctx.piece
+            shape = list(g.shape)
+            shape[dim] *= world
+            full = g.new_zeros(shape)
+            full.narrow(dim, rank * g.shape[dim], g.shape[dim]).copy_(g)
+            return full
+        return g
+
+
+def row_parallel_output_async(y: torch.Tensor, sequence_parallel: bool) -> torch.Tensor:
+    """Like :func:`row_parallel_output`, but only STARTS the collective (on the communication library's own stream):
+    the caller goes on with independent work and applies :func:`finish_reduction` where the value is needed."""
+    if tp_world() == 1:
+        return y
+    return _StartReduction.apply(y, sequence_parallel)
+
+
+def finish_reduction(x: torch.Tensor | None) -> torch.Tensor | None:
+    """Wait for a reduction started by :func:`row_parallel_output_async` (no-op for anything else)."""
+    if x is None or not (hasattr(x, "_pending_reduction") or hasattr(x, "_slice")):
+        return x
+    return _FinishReduction.apply(x)
+
+
 class _VocabParallelCrossEntropy(torch.autograd.Function):
     """Cross entropy over logits whose vocabulary dimension is split across the group: three small all-reduces (row
     maximum, sum of exponentials, target logit) instead of gathering ``[tokens, vocab]``."""

@@ -73,7 +73,7 @@ def check_collectives(rank: int, world: int, device: torch.device, multimem: boo
         print(f"collectives ok (multimem={multimem}, multicast address {'present' if buf.multicast_ptr else 'absent'})", flush=True)
 
 
-def train_losses(fused: bool, steps: int = 3) -> list[float]:
+def train_losses(fused: bool, steps: int = 3, resident: bool = True) -> list[float]:
     from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
     from lm_engine.optimization.optimizer import FusedAdamW
     from lm_engine.parallel.engine import ShardedTrainingEngine
@@ -85,8 +85,10 @@ def train_losses(fused: bool, steps: int = 3) -> list[float]:
                            max_position_embeddings=256, tie_word_embeddings=False, sequence_mixer_blocks=[layer_attn] * 2, mlp_blocks=[layer_mlp] * 2)
     torch.manual_seed(7)
     model = GPTBaseForCausalLM(config)
-    engine = ShardedTrainingEngine(model, compute_dtype=torch.bfloat16, device=device, fused_collectives=fused)
+    engine = ShardedTrainingEngine(model, compute_dtype=torch.bfloat16, device=device, fused_collectives=fused, resident_parameters=resident)
     assert (engine.peer is not None) == fused, "peer memory was not set up"
+    if not resident:
+        assert all(not u.resident for u in engine.units if u.module is not None), "blocks are expected to be sharded"
     optimizer = FusedAdamW([seg.master for seg in engine.segments()], lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
     rank = dist.get_rank()
     losses = []
@@ -102,7 +104,12 @@ def train_losses(fused: bool, steps: int = 3) -> list[float]:
         losses.append(float(value))
     if engine.peer is not None:
         engine.peer.check()
-    checksum = sum(float(unit.compute.float().sum()) for unit in engine.units)
+    checksum = 0.0
+    for unit in engine.units:  # sum over the whole compute copy, whichever way it is stored
+        part = unit.compute_shard.float().sum()
+        if unit.world > 1:
+            dist.all_reduce(part)
+        checksum += float(part)
     return losses + [checksum]
 
 
@@ -118,10 +125,12 @@ def main() -> None:
     os.environ["LM_ENGINE_PEER_MULTIMEM"] = "1"
     nccl = train_losses(False)
     peer = train_losses(True)
+    sharded = train_losses(False, resident=False)  # blocks gathered and released one by one (NCCL collectives)
     if rank == 0:
-        print("nccl", nccl, "\npeer", peer, flush=True)
-    for a, b in zip(nccl, peer):
+        print("nccl", nccl, "\npeer", peer, "\nsharded parameters", sharded, flush=True)
+    for a, b, c in zip(nccl, peer, sharded):
         assert abs(a - b) <= 2e-3 * max(1.0, abs(a)), (nccl, peer)
+        assert abs(a - c) <= 2e-3 * max(1.0, abs(a)), (nccl, sharded)
     dist.barrier()
     if rank == 0:
         print("PEER_CHECK_OK", flush=True)

@@ -110,6 +110,29 @@ def check_ladder() -> None:
     ids = torch.randint(0, 250, (2, 32))
     close(local(input_ids=ids).logits, full(input_ids=ids).logits, "ladder logits")
 
+    # overlapped layer: the row-parallel reductions are only started inside the sub-block and waited for one sub-block
+    # later; outputs and gradients must not change (with and without sequence parallelism, padded and packed)
+    from lm_engine.enums import Kernel
+    from lm_engine.kernels import enable_kernels
+
+    for sequence_parallel in (False, True):
+        for packed in (False, True):
+            torch.manual_seed(5)
+            model = LadderResidualForCausalLM_TP(config, sequence_parallel=sequence_parallel, use_padding_free_transformer=packed)
+            model.train()
+            batch = [row.tolist() for row in ids] if packed else ids
+            plain = model(input_ids=batch, labels=batch)
+            plain.loss.backward()
+            plain_grads = {k: p.grad.clone() for k, p in model.named_parameters()}
+            model.zero_grad()
+            with enable_kernels([Kernel.ladder_residual_overlapped_layer]):
+                overlapped = model(input_ids=batch, labels=batch)
+                assert model.transformer.h["0"].sequence_mixer.c_proj.overlap_reduction, "the overlapped layer did not switch on"
+                overlapped.loss.backward()
+            close(overlapped.loss, plain.loss, f"ladder overlapped loss sp={sequence_parallel} packed={packed}")
+            for key, p in model.named_parameters():
+                close(p.grad, plain_grads[key], f"ladder overlapped grad of {key} sp={sequence_parallel} packed={packed}", atol=5e-6)
+
 
 def check_pipeline_stages() -> None:
     """Two stages chained by hand reproduce the single-stage model."""
