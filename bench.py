@@ -57,6 +57,9 @@ def parse_args():
     p.add_argument("--moe-steps", type=int, default=None, help="timed steps of the MoE record (default: max(3, steps // 4))")
     p.add_argument("--reference-compile", type=str, default="auto", choices=["auto", "on", "off"],
                    help="reference arm: its own distributed_args.torch_compile option (auto = the faster one as measured on a B200)")
+    p.add_argument("--expert-capacity-factor", type=float, default=None,
+                   help="MoE with expert parallelism: static row buffers of this multiple of a rank's balanced share instead of the "
+                        "default exact (dropless) sizing; dropped entries are counted and reported")
     p.add_argument("--sharded-parameters", action="store_true",
                    help="distributed_args.keep_parameters_gathered=false: blocks are gathered and released one by one (not the headline mode)")
     p.add_argument("--budget-output", type=str, default=None,
@@ -187,7 +190,7 @@ def run_native(cli) -> dict:
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
     expert_parallel = cli.gpus if moe and cli.gpus > 1 and spec["num_experts"] % cli.gpus == 0 else 1
     # expert row buffers are sized exactly for the fullest rank of every layer (no capacity factor: nothing can be dropped)
-    capacity = None
+    capacity = cli.expert_capacity_factor
     extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else {}
     if cli.sharded_parameters:
         extra["keep_parameters_gathered"] = False

@@ -63,3 +63,114 @@ def test_state_dict_and_loss_match_reference(tmp_path):
         mine = model(input_ids=data["ids"], labels=data["ids"])
     assert torch.allclose(mine.logits, data["logits"], atol=3e-6, rtol=1e-5)
     assert abs(mine.loss.item() - data["loss"].item()) < 1e-5
+
+
+_COMMON = r"""
+import sys, torch
+import torch.distributed.checkpoint as dcp
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm, disable_generation_cache
+from lm_engine.checkpointing.model import _ModelSaver
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+blocks = [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": 4, "num_key_value_heads": 2, "add_bias": False}] * 2
+mlps = [{"mlp_type": "MLP", "activation_function": "swiglu", "intermediate_size": 128, "add_bias": False},
+        {"mlp_type": "MoE", "activation_function": "swiglu", "intermediate_size": 64, "add_bias": False, "num_experts": 4, "num_experts_per_tok": 2}]
+c = rm.GPTBaseConfig(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                     rope_theta=500000, sequence_mixer_blocks=blocks, mlp_blocks=mlps, tie_word_embeddings=False)
+from transformers import AutoModelForCausalLM
+class Wrapper(torch.nn.Module):  # what the reference's savers see: a wrapper whose `.model` is the network
+    def __init__(self, model):
+        super().__init__()
+        self.model = model
+    def has_teacher_model(self):
+        return False
+torch.manual_seed(0)
+wrapper = Wrapper(AutoModelForCausalLM.from_config(c))
+wrapper.eval()
+"""
+
+_WRITE = _COMMON + r"""
+ids = torch.randint(0, 256, (2, 16))
+with disable_generation_cache():
+    out = wrapper.model(input_ids=ids, labels=ids)
+# the reference's own saver object through torch.distributed.checkpoint, as in its save_checkpoint (one process: no_dist)
+dcp.save({"state": _ModelSaver([wrapper])}, checkpoint_id=sys.argv[2], no_dist=True)
+torch.save({"ids": ids, "logits": out.logits.detach()}, sys.argv[3])
+"""
+
+_READ = _COMMON + r"""
+for p in wrapper.parameters():
+    torch.nn.init.zeros_(p)
+dcp.load({"state": _ModelSaver([wrapper])}, checkpoint_id=sys.argv[2], no_dist=True)
+data = torch.load(sys.argv[3])
+with disable_generation_cache():
+    out = wrapper.model(input_ids=data["ids"])
+torch.save({"logits": out.logits.detach()}, sys.argv[4])
+"""
+
+
+def _our_wrapper():
+    import torch.nn as nn
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+    from lm_engine.parallel.engine import ShardedTrainingEngine
+
+    blocks = [{"sequence_mixer_type": "softmax_attention", "num_attention_heads": 4, "num_key_value_heads": 2, "add_bias": False}] * 2
+    mlps = [{"mlp_type": "MLP", "activation_function": "swiglu", "intermediate_size": 128, "add_bias": False},
+            {"mlp_type": "MoE", "activation_function": "swiglu", "intermediate_size": 64, "add_bias": False, "num_experts": 4, "num_experts_per_tok": 2}]
+    config = GPTBaseConfig(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                           rope_theta=500000, sequence_mixer_blocks=blocks, mlp_blocks=mlps, tie_word_embeddings=False)
+
+    class Wrapper(nn.Module):
+        def __init__(self, model):
+            super().__init__()
+            self.model = model
+
+    torch.manual_seed(11)
+    wrapper = Wrapper(GPTBaseForCausalLM(config))
+    wrapper._lm_engine = ShardedTrainingEngine(wrapper, compute_dtype=torch.float32, device=torch.device("cpu"))
+    wrapper.eval()
+    return wrapper
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_distributed_checkpoints_cross_load_with_the_reference(tmp_path):
+    """Both directions through ``torch.distributed.checkpoint``: a ``model`` store written by the reference's own saver
+    object loads into this package's engine-owned model (same logits as the reference computed), and a store written by
+    this package's checkpoint code loads through the reference's saver object into the reference model (same logits as
+    this package computed)."""
+    import torch.distributed.checkpoint as dcp
+
+    from lm_engine.checkpointing.core import _placeholders, get_model_state_dict, set_model_state_dict
+
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    ref_store, ref_out = tmp_path / "ref_model", tmp_path / "ref_out.pt"
+    subprocess.run([sys.executable, "-c", _WRITE, REF, str(ref_store), str(ref_out)], check=True, cwd=str(tmp_path), env=env,
+                   timeout=600, capture_output=True)
+    data = torch.load(ref_out)
+
+    wrapper = _our_wrapper()
+    state = _placeholders(get_model_state_dict([wrapper]))
+    dcp.load({"state": state}, checkpoint_id=str(ref_store), no_dist=True)
+    set_model_state_dict([wrapper], state)
+    wrapper._lm_engine.refresh_parameters()
+    with torch.no_grad():
+        mine = wrapper.model(input_ids=data["ids"])
+    assert torch.allclose(mine.logits, data["logits"], atol=3e-6, rtol=1e-5)
+
+    # the other way round, from fresh weights of this package
+    wrapper = _our_wrapper()
+    with torch.no_grad():
+        logits = wrapper.model(input_ids=data["ids"]).logits
+    our_store, back = tmp_path / "our_model", tmp_path / "back.pt"
+    dcp.save({"state": get_model_state_dict([wrapper])}, checkpoint_id=str(our_store), no_dist=True)
+    subprocess.run([sys.executable, "-c", _READ, REF, str(our_store), str(ref_out), str(back)], check=True, cwd=str(tmp_path), env=env,
+                   timeout=600, capture_output=True)
+    assert torch.allclose(torch.load(back)["logits"], logits, atol=3e-6, rtol=1e-5)
