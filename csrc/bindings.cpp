@@ -335,6 +335,35 @@ Tensor cross_entropy_(Tensor& logits, const Tensor& labels, double logit_scale, 
   return loss;
 }
 
+// Vocabulary-parallel cross entropy, this rank's part: stats[T, 3] = (row max, sum of exp relative to it, target logit or 0).
+Tensor ce_shard_stats(const Tensor& logits, const Tensor& labels, int64_t vocab_start, int64_t ignore_index) {
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [T, V] with unit inner stride");
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == torch::kInt64 && labels.is_contiguous() && labels.numel() == logits.size(0), "labels: int64 [T]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  Tensor stats = torch::empty({logits.size(0), 3}, logits.options().dtype(torch::kFloat32));
+  b200::cross_entropy_shard_stats(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), stats.data_ptr<float>(),
+                                  (int)logits.size(0), (int)logits.size(1), logits.stride(0), vocab_start, ignore_index, cur_stream());
+  return stats;
+}
+
+// grad[T, V] (bf16) = row_scale * (exp(logits - lse) - onehot(label - vocab_start)); zero rows for ignored labels.
+Tensor ce_shard_grad(const Tensor& logits, const Tensor& labels, const Tensor& lse, const Tensor& row_scale, int64_t vocab_start,
+                     int64_t ignore_index) {
+  check_bf16(logits, "logits");
+  check_f32(lse, "lse");
+  check_f32(row_scale, "row_scale");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [T, V] with unit inner stride");
+  TORCH_CHECK(lse.is_contiguous() && row_scale.is_contiguous() && lse.numel() == logits.size(0) && row_scale.numel() == logits.size(0), "lse / row_scale: fp32 [T]");
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == torch::kInt64 && labels.is_contiguous() && labels.numel() == logits.size(0), "labels: int64 [T]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  Tensor grad = torch::empty({logits.size(0), logits.size(1)}, logits.options());
+  b200::cross_entropy_shard_grad(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), lse.data_ptr<float>(),
+                                 row_scale.data_ptr<float>(), grad.data_ptr(), (int)logits.size(0), (int)logits.size(1), logits.stride(0),
+                                 vocab_start, ignore_index, cur_stream());
+  return grad;
+}
+
 long long launch_count() { return b200::launch_counter().load(); }
 
 }  // namespace
@@ -362,6 +391,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("clip_coef", &clip_coef);
   m.def("adamw_step", &adamw_step);
   m.def("cross_entropy_", &cross_entropy_);
+  m.def("ce_shard_stats", &ce_shard_stats);
+  m.def("ce_shard_grad", &ce_shard_grad);
   m.def("launch_count", &launch_count);
   b200::register_attention(m);
   b200::register_moe(m);

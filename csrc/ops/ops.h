@@ -61,6 +61,12 @@ void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss, f
                            long long row_stride, float logit_scale, float grad_scale, long long ignore_index,
                            bool write_grad, cudaStream_t stream);
 
+// vocabulary-parallel form: per-rank (max, sum-exp, target logit) triples of a vocabulary slice, and the slice of the gradient
+void cross_entropy_shard_stats(const void* logits, const long long* labels, float* stats, int T, int V, long long row_stride,
+                               long long vocab_start, long long ignore_index, cudaStream_t stream);
+void cross_entropy_shard_grad(const void* logits, const long long* labels, const float* lse, const float* row_scale, void* grad, int T,
+                              int V, long long row_stride, long long vocab_start, long long ignore_index, cudaStream_t stream);
+
 // fp8 GEMM (gemm/gemm_fp8.cu): a_fmt / b_fmt 0 = e4m3, 1 = e5m2; scale_a / scale_b device fp32 scalars or null.
 void gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
               bool b_mn, int a_fmt, int b_fmt, int epi, float alpha, const float* scale_a, const float* scale_b, int* status,

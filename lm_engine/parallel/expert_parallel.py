@@ -58,16 +58,30 @@ def dropped_entries(device: torch.device) -> int:
     return 0 if counter is None else int(counter.item())
 
 
-def _capacity_rows(entries_per_rank: int, local_experts: int, selected_all: torch.Tensor | None = None,
-                   num_experts: int | None = None) -> int | None:
+def _capacity_rows(entries_per_rank: int, local_experts: int) -> int | None:
     if _CAPACITY_FACTOR is None:
-        if selected_all is None:
-            return None
-        # rows of the fullest rank, identical on every rank because all of them hold the same routing table
-        counts = torch.bincount(selected_all.long(), minlength=num_experts)[:num_experts]
-        padded = (counts + TILE - 1) // TILE * TILE
-        return max(TILE, int(padded.view(-1, local_experts).sum(dim=1).max().item()))
+        return None
     return int(_CAPACITY_FACTOR * entries_per_rank + 0.5) + local_experts * (TILE - 1)
+
+
+class _RowCount:
+    """Exact sizing: the tile-padded row count of the fullest rank, computed on the device from the routing table that
+    every rank holds for the whole group (so all ranks get the same number) and copied to pinned host memory without
+    blocking. ``value()`` waits for that copy only: whatever was queued behind it keeps the GPU busy meanwhile."""
+
+    def __init__(self, selected_all: torch.Tensor, num_experts: int, local_experts: int) -> None:
+        counts = torch.zeros(num_experts, dtype=torch.int32, device=selected_all.device)
+        counts.index_add_(0, selected_all, torch.ones_like(selected_all))
+        padded = (counts + (TILE - 1)) // TILE * TILE
+        fullest = padded.view(-1, local_experts).sum(dim=1).max().to(torch.int32).reshape(1)
+        self.host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        self.host.copy_(fullest, non_blocking=True)
+        self.ready = torch.cuda.Event()
+        self.ready.record()
+
+    def value(self) -> int:
+        self.ready.synchronize()
+        return max(TILE, int(self.host[0]))
 
 
 def _count_dropped(layout) -> None:
@@ -203,17 +217,19 @@ class _ExpertParallelFn(torch.autograd.Function):
         entries = T * top_k
 
         selected_all = torch.cat(_all_gather_plain(selected_experts.reshape(-1).to(torch.int32)))
+        exact = _RowCount(selected_all, num_experts, local) if _CAPACITY_FACTOR is None else None
+        # everything that does not depend on the row count is queued before the host waits for it
         weights_all = torch.cat(_all_gather_plain(router_weights.reshape(-1).float()))
-        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
-                                      capacity_rows=_capacity_rows(entries, local, selected_all, num_experts))
-        _count_dropped(layout)
-        rows = layout.rows
-
         tokens = ws.buffer("tokens", T * H)
-        out_rows = ws.buffer("rows", rows * H)
         peer.barrier()  # the previous users of the buffers are done everywhere
         tokens.tensor[: T * H].view(T, H).copy_(x)
         peer.barrier()  # every rank's tokens are readable
+        capacity_rows = exact.value() if exact is not None else _capacity_rows(entries, local)
+        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
+                                      capacity_rows=capacity_rows)
+        _count_dropped(layout)
+        rows = layout.rows
+        out_rows = ws.buffer("rows", rows * H)
         te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
         # dispatch: rows are pulled from their owners by gather CTAs inside the c_fc GEMM kernel
         xg, fc = gather_then_grouped_rows(C, tokens.ptrs, layout.src_entry, H, entries, top_k, x, te, local, w_fc, False, st, copy_ctas=_GATHER_CTAS)

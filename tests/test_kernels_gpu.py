@@ -353,6 +353,33 @@ def test_attention_head_widths_between_the_kernel_widths(C, d, groups, qpg):
     assert _rel_err(qkv.grad, q32.grad) < 2e-2
 
 
+@pytest.mark.parametrize("ranks,V", [(2, 1024), (4, 50264), (8, 128256)])
+def test_vocabulary_parallel_cross_entropy_kernels(C, ranks, V):
+    """Every rank's slice of the logits goes through the statistics kernel, the triples are combined as the
+    tensor-parallel loss does, and every slice of the gradient comes from the gradient kernel: loss and gradient against
+    fp32 cross entropy over the whole vocabulary."""
+    from lm_engine.parallel.tensor_parallel import combine_shard_statistics
+
+    torch.manual_seed(0)
+    T = 257
+    logits = (torch.randn(T, V, device="cuda") * 3).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    ref_in = logits.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-100, reduction="none")
+    row_scale = torch.rand(T, device="cuda") + 0.5
+    ref.backward(row_scale)
+    per = V // ranks
+    shards = [logits[:, r * per : (r + 1) * per].contiguous() for r in range(ranks)]
+    stats = torch.stack([C.ce_shard_stats(shards[r], labels, r * per, -100) for r in range(ranks)])
+    lse, target = combine_shard_statistics(stats)
+    loss = (lse - target) * (labels != -100)
+    torch.testing.assert_close(loss, ref.detach(), atol=2e-4, rtol=1e-5)
+    grad = torch.cat([C.ce_shard_grad(shards[r], labels, lse, row_scale, r * per, -100) for r in range(ranks)], dim=1)
+    assert _rel_err(grad, ref_in.grad) < 5e-3
+    assert grad[::7].abs().sum().item() == 0
+
+
 def test_strict_mode_turns_a_pytorch_fallback_into_an_error(C):
     from lm_engine import ops
 
