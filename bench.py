@@ -60,6 +60,13 @@ def parse_args():
     p.add_argument("--expert-capacity-factor", type=float, default=None,
                    help="MoE with expert parallelism: static row buffers of this multiple of a rank's balanced share instead of the "
                         "default exact (dropless) sizing; dropped entries are counted and reported")
+    p.add_argument("--tensor-parallel", type=int, default=1,
+                   help="tensor-parallel size with sequence parallelism; the other GPUs form the sharded data-parallel group (not the headline mode)")
+    p.add_argument("--fp8", type=str, default=None, choices=["tensorwise", "mxfp8"], help="run the linear layers in fp8 with this recipe (not the headline mode)")
+    p.add_argument("--sequence-length", type=int, default=None, help="override the sequence length (not the headline config)")
+    p.add_argument("--micro-batch-size", type=int, default=None, help="override the micro-batch size (not the headline config)")
+    p.add_argument("--pipeline-parallel", type=int, default=1,
+                   help="pipeline stages (1F1B, one stage per pipeline rank); the other GPUs form the sharded data-parallel group (not the headline mode)")
     p.add_argument("--sharded-parameters", action="store_true",
                    help="distributed_args.keep_parameters_gathered=false: blocks are gathered and released one by one (not the headline mode)")
     p.add_argument("--budget-output", type=str, default=None,
@@ -183,8 +190,14 @@ def run_native(cli) -> dict:
 
     set_logger("WARNING")
     ops.require_native()
-    ops.set_strict(True)  # an op that would leave the sm_100a kernels for a PyTorch path raises instead
-    spec = SPECS[cli.config]
+    # an op that would leave the sm_100a kernels for a PyTorch path raises instead (the pipeline-parallel exploration mode
+    # only counts such sites and reports them)
+    ops.set_strict(cli.pipeline_parallel == 1 and cli.tensor_parallel == 1 and cli.fp8 is None)
+    spec = dict(SPECS[cli.config])
+    if cli.sequence_length:
+        spec["sequence_length"] = cli.sequence_length
+    if cli.micro_batch_size:
+        spec["micro_batch_size"] = cli.micro_batch_size
     moe = "num_experts" in spec
     ga = cli.gradient_accumulation_steps or spec["gradient_accumulation_steps"]
     kernels = [k.value for k in Kernel if k != Kernel.ladder_residual_overlapped_layer]
@@ -194,9 +207,19 @@ def run_native(cli) -> dict:
     extra = {"expert_parallel_world_size": expert_parallel, "expert_capacity_factor": capacity} if expert_parallel > 1 else {}
     if cli.sharded_parameters:
         extra["keep_parameters_gathered"] = False
-    args = args_from_dict(Mode.training, training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra))
+    tp_size = cli.tensor_parallel
+    if tp_size > 1:
+        extra.update(tensor_parallel_world_size=tp_size, sequence_parallel=True)
+    pp = cli.pipeline_parallel
+    if pp > 1:
+        extra.update(pipeline_parallel_world_size=pp, num_pipeline_stages=pp, pipeline_parallel_schedule="1F1B")
+    config_dict = training_config(spec, cli.layers, ga, cli.steps + cli.warmup, kernels, extra)
+    if cli.fp8:
+        config_dict["mixed_precision_args"] = dict(dtype="fp8", fp8_recipe=cli.fp8)
+    args = args_from_dict(Mode.training, config_dict)
 
-    init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel)
+    init_distributed(zero_stage=3, expert_parallel_world_size=expert_parallel, pipeline_parallel_world_size=pp,
+                     tensor_parallel_world_size=tp_size)
     world = ProcessGroupManager.get_world_size()
     assert world == cli.gpus, f"--gpus {cli.gpus} but WORLD_SIZE={world}"
     rank = ProcessGroupManager.get_global_rank()
@@ -206,14 +229,15 @@ def run_native(cli) -> dict:
 
     with enable_kernels(args.kernel_args.kernels):
         container = get_model_container(args, Mode.training)
-        container, _ = wrap_model_container_for_distributed_training(args, container)
+        container, pipeline_schedule = wrap_model_container_for_distributed_training(args, container)
         optimizers = get_optimizer_container("TorchAdamW", args.optimizer_args.class_args, container)
         schedulers = get_scheduler_container(container, optimizers, 10, 0, None, 10**6, args.lr_scheduler_args.lr_decay_style, 0.1, {})
         container.train()
 
         mb, seq = spec["micro_batch_size"], spec["sequence_length"]
         multiplier = 1.0 / (mb * seq)
-        gen = torch.Generator().manual_seed(1234 + rank)
+        # all pipeline ranks of one data-parallel replica read the same tokens
+        gen = torch.Generator().manual_seed(1234 + (rank if pp * tp_size == 1 else ProcessGroupManager.get_data_parallel_rank()))
         # a fresh micro-batch for every micro-step of every step (nothing is seen twice)
         n_device = ga * (cli.warmup + cli.steps)
         n_host = 0 if cli.skip_e2e else ga * cli.steps
@@ -230,7 +254,14 @@ def run_native(cli) -> dict:
                 return {"text": t}
 
         def step(feed):
+            if pipeline_schedule is not None:
+                from lm_engine.pretrain import train_step_with_pipeline_parallel
+
+                return train_step_with_pipeline_parallel(container, pipeline_schedule, optimizers, schedulers, feed, 1.0, seq)
             return train_step_without_pipeline_parallel(container, optimizers, schedulers, feed, 1.0, lm_loss_multiplier=multiplier)
+
+        def loss_of(metrics):  # only the last pipeline stage has one
+            return float(metrics["loss"]) if "loss" in list(metrics.keys()) else None
 
         def timed(feed, read_back: bool):
             if world > 1:
@@ -246,7 +277,7 @@ def run_native(cli) -> dict:
             for _ in range(cli.steps):
                 metrics = step(feed)
                 if read_back:
-                    last = float(metrics["loss"])  # device -> host read of the step result
+                    last = loss_of(metrics)  # device -> host read of the step result
             end.record()
             torch.cuda.synchronize()
             if world > 1:
@@ -261,14 +292,14 @@ def run_native(cli) -> dict:
         feed_device = Feed(pool_device)
         for _ in range(cli.warmup):
             metrics = step(feed_device)
-        loss_after_warmup = float(metrics["loss"])
+        loss_after_warmup = loss_of(metrics)
         ops.check_status()
 
         ms, launches, clocks, _ = timed(feed_device, read_back=False)
         e2e = None
         if not cli.skip_e2e:
             ms_e2e, _, _, last_loss = timed(Feed(pool), read_back=True)
-            tokens = cli.steps * ga * mb * seq * world
+            tokens = cli.steps * ga * mb * seq * (world // (pp * tp_size))
             e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / cli.steps,
                    "h2d_bytes_per_step": ga * mb * (seq + 1) * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss}
         ops.check_status()
@@ -290,21 +321,22 @@ def run_native(cli) -> dict:
                 with open(cli.budget_output, "w") as handle:
                     json.dump({"step_ms": t0.elapsed_time(t1), "n_gpus": world, "config": spec["name"], "sites": sites}, handle, indent=1)
 
-    tokens_per_step = ga * mb * seq * world
+    tokens_per_step = ga * mb * seq * (world // (pp * tp_size))
     ms_per_step = ms / cli.steps
     value = tokens_per_step / (ms_per_step / 1e3)
-    tflops_model = get_model_tflops(container[0].config, ga * mb * world, seq)
+    tflops_model = get_model_tflops(container[0].config, ga * mb * (world // (pp * tp_size)), seq)
     peak, peak_src = measured_peak_tflops()
     tflops_per_gpu = tflops_model / world / (ms_per_step / 1e3)
     result = {
         "impl": "native", "metric": ("pretraining tokens/s (40-expert top-8 MoE, expert parallel)" if moe else
                                      "pretraining tokens/s (8B dense, ZeRO-3 sharded data parallel)"), "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": cli.steps, "warmup": cli.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cli.fp8 is None else f"fp8 ({cli.fp8}) linears, bf16 elsewhere", "data": "synthetic uniform-random tokens, random-init weights",
         "config": {"model": spec["name"] + ("" if cli.layers is None else f"-DEBUG-{cli.layers}-layers"),
-                   "global_batch": ga * mb * world, "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
-                   "parallelism": (f"ep{expert_parallel} x " if moe else "") +
-                   f"fsdp{world} (ZeRO-3 sharded fp32 master/AdamW/gradients; " +
+                   "global_batch": ga * mb * (world // (pp * tp_size)), "seq_len": seq, "micro_batch_per_gpu": mb, "gradient_accumulation_steps": ga,
+                   "parallelism": (f"ep{expert_parallel} x " if moe else "") + (f"pp{pp} (1F1B, {ga} micro-batches) x " if pp > 1 else "") +
+                   (f"tp{tp_size} (sequence parallel) x " if tp_size > 1 else "") +
+                   f"fsdp{world // (pp * tp_size)} (ZeRO-3 sharded fp32 master/AdamW/gradients; " +
                    ("blocks gathered and released one by one)" if cli.sharded_parameters else "gathered bf16 weights kept for the step)"),
                    "optimizer": "AdamW fp32 master", "l2": "working set per step >> 126 MB L2 (inputs larger than L2)",
                    "kernels": kernels, "gradient_checkpointing": None},
@@ -370,7 +402,9 @@ def main() -> None:
         result = run_reference(cli, SPECS[cli.config], REPO_ROOT)
     else:
         result = run_native(cli)
-    headline = cli.config == "dense" and cli.layers is None and cli.gradient_accumulation_steps is None and not cli.sharded_parameters
+    headline = (cli.config == "dense" and cli.layers is None and cli.gradient_accumulation_steps is None and not cli.sharded_parameters
+                and cli.pipeline_parallel == 1 and cli.tensor_parallel == 1 and cli.fp8 is None and cli.sequence_length is None
+                and cli.micro_batch_size is None)
     if headline and not cli.no_moe and cli.child_output is None:
         # the metric names both models: the MoE record rides along under "moe"; the headline `value` stays the dense one
         moe = moe_record(cli)

@@ -28,6 +28,22 @@ inline EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
+// The encoder is a driver entry point and needs the device's context current on the calling thread. A thread that has
+// made no runtime call yet (an autograd worker whose first operation is a GEMM on device 0: the device guard sees
+// "already device 0" and calls nothing) has none, and the encoder answers CUDA_ERROR_INVALID_CONTEXT. Binding the primary
+// context with a harmless runtime call and encoding again fixes that; the normal path pays nothing.
+inline CUresult encode_tiled(CUtensorMap* m, CUtensorMapDataType type, cuuint32_t rank, void* base, const cuuint64_t* dims,
+                             const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estr, CUtensorMapSwizzle swizzle) {
+  CUresult r = tensor_map_encoder()(m, type, rank, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    cudaFree(nullptr);
+    r = tensor_map_encoder()(m, type, rank, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r;
+}
+
 // 2-D tensor map over a row-major matrix of 16-bit elements.
 //   inner      : number of contiguous elements per row
 //   outer      : number of rows
@@ -42,10 +58,8 @@ inline CUtensorMap make_tensor_map_2d_b16(const void* base, uint64_t inner, uint
   cuuint64_t strides[1] = {row_stride * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
   return m;
 }
@@ -60,9 +74,7 @@ inline CUtensorMap make_tensor_map_2d_u8(const void* base, uint64_t inner, uint6
   cuuint64_t strides[1] = {row_stride};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (u8) failed with code " + std::to_string(int(r)));
   return m;
 }
@@ -77,9 +89,8 @@ inline CUtensorMap make_tensor_map_2d_f32(const void* base, uint64_t inner, uint
   cuuint64_t strides[1] = {row_stride * 4};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (f32) failed with code " + std::to_string(int(r)));
   return m;
 }
@@ -96,10 +107,8 @@ inline CUtensorMap make_tensor_map_3d_b16(const void* base, uint64_t inner, uint
   cuuint64_t strides[2] = {stride_outer * 2, stride_outer2 * 2};
   cuuint32_t box[3] = {box_inner, box_outer, box_outer2};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = tensor_map_encoder()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
-                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
   return m;
 }

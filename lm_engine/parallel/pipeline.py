@@ -139,7 +139,27 @@ def _make_transfer_groups(world: int) -> dict:
                 group = dist.new_group([peers[a], peers[b]]) if nccl and peers[a] != peers[b] else None
                 if peers == mine:
                     out[(a, b, direction)] = group
+    if nccl:
+        _connect_transfer_groups(out, mine)
     return out
+
+
+def _connect_transfer_groups(groups: dict, peers: tuple[int, ...]) -> None:
+    """One tiny blocking transfer over every group this rank belongs to, in one global order of the keys. The first
+    point-to-point operation on a group creates its communicator, which blocks the host until the peer joins: done
+    here, where both ends walk the same list, instead of inside the schedule, where one end may be a whole forward and
+    backward pass away from its matching call (the pipeline ranks' action lists are not symmetric)."""
+    me = dist.get_rank()
+    token = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
+    for (a, b, direction) in sorted(groups):
+        group = groups[(a, b, direction)]
+        if group is None:
+            continue
+        if peers[a] == me:
+            dist.send(token, dst=peers[b], group=group)
+        elif peers[b] == me:
+            dist.recv(token, src=peers[a], group=group)
+    torch.cuda.synchronize()
 
 
 class _Mailbox:

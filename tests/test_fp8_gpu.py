@@ -154,3 +154,44 @@ def test_mx_linear_runs_the_block_scaled_kernels_and_matches_the_emulation():
     assert relative(w.grad, we.grad) < 1e-2
     xr, wr = x.detach().float(), w.detach().float()
     assert relative(y, xr @ wr.t() + bias.detach().float()) < 0.05  # and close to the unquantised product
+
+
+def test_mxfp8_training_follows_the_bf16_loss_curve():
+    """50 optimizer steps of a small decoder on a fixed batch: the run whose linears use the MXFP8 kernels (forward, data
+    gradient and weight gradient) stays within a few percent of the bf16 run at every step and ends as low."""
+    from lm_engine import ops
+    from lm_engine.fp8 import FP8Manager
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    attn = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)
+    mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=512, add_bias=False)
+    config = GPTBaseConfig(vocab_size=512, hidden_size=256, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                           tie_word_embeddings=False, sequence_mixer_blocks=[attn] * 2, mlp_blocks=[mlp] * 2)
+    torch.manual_seed(3)
+    ids = torch.randint(0, 512, (4, 128), device="cuda")  # 512 tokens: every product's sizes are multiples of 128
+
+    def curve(mx: bool) -> list[float]:
+        torch.manual_seed(4)
+        model = GPTBaseForCausalLM(config).cuda().bfloat16()
+        if mx:
+            manager = FP8Manager([model], recipe="mxfp8")
+            assert manager.converted == 8
+        optimizer = torch.optim.AdamW(model.parameters(), lr=2e-3, weight_decay=0.0)
+        before = sum(ops.fallback_counts().values())
+        losses = []
+        for _ in range(50):
+            loss = model(input_ids=ids, labels=ids).loss
+            loss.backward()
+            optimizer.step()
+            optimizer.zero_grad(set_to_none=True)
+            losses.append(float(loss))
+        if mx:
+            assert not any(key.startswith("mx_linear") for key in ops.fallback_counts()), "the MX linears left the block-scaled kernels"
+        del before
+        return losses
+
+    bf16, mx = curve(False), curve(True)
+    ops.check_status()
+    assert bf16[-1] < 0.5 * bf16[0], "the task is expected to be learnable in 50 steps"
+    for step, (a, b) in enumerate(zip(bf16, mx)):
+        assert abs(a - b) < 0.08 * max(a, 0.2), (step, a, b)
