@@ -159,14 +159,25 @@ __global__ void __launch_bounds__(THREADS)
   }
 }
 
-// out[c] (+)= sum_r partial[r, c]
-__global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols,
-                                  int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// out[c] (+)= sum_r partial[r, c]. Block = 32 columns x 8 row lanes: every row lane sums its rows with coalesced
+// 128-byte reads, shared memory folds the eight partial sums.
+__global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols,
+                                                         int accumulate) {
+  __shared__ float fold[8][33];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + x;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[(size_t)r * cols + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < cols) {
+    for (int r = y; r < rows; r += 8) s += partial[(size_t)r * cols + c];
+  }
+  fold[y][x] = s;
+  __syncthreads();
+  if (y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += fold[k][x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 }  // namespace
@@ -217,7 +228,7 @@ void rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd
   else if (nv <= 2048) BWD(512, 4);
   else BWD(1024, 4);
 #undef BWD
-  column_sum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(partial, dw, rows, H, accumulate_dw ? 1 : 0);
+  column_sum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(partial, dw, rows, H, accumulate_dw ? 1 : 0);
   count_launch(2);
   check_cuda(cudaGetLastError(), "rmsnorm_bwd launch");
 }
@@ -334,7 +345,7 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* h, const voi
   if (nv <= 256) launch_noalloc_bwd<256, 1>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
   else if (nv <= 512) launch_noalloc_bwd<256, 2>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
   else launch_noalloc_bwd<256, 4>(rows, DY, HH, W, rstd, DR, DH, partial, T, H, s);
-  column_sum_kernel<<<(H + 255) / 256, 256, 0, s>>>(partial, dw, rows, H, accumulate_dw ? 1 : 0);
+  column_sum_kernel<<<(H + 31) / 32, 256, 0, s>>>(partial, dw, rows, H, accumulate_dw ? 1 : 0);
   count_launch(2);
   e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -220,6 +220,10 @@ class FP8Manager:
                 if _eligible(module) and not name.endswith(("lm_head", "output")):
                     module.forward = forward.__get__(module, type(module))
                     self.converted += 1
+                elif type(module).__name__ in ("ColumnParallelLinear", "RowParallelLinear") and not name.endswith(("lm_head", "output")):
+                    # tensor-parallel linears keep their collectives and hand the local product to the recipe
+                    module.linear_function = _tp_product(recipe)
+                    self.converted += 1
 
     @staticmethod
     def precompute_float8_dynamic_scale_for_fsdp(model_container) -> None:
@@ -228,6 +232,20 @@ class FP8Manager:
     @staticmethod
     def sync_float8_amax_and_scale_history(model_container) -> None:
         """Nothing to do: scaling is dynamic (no amax history)."""
+
+
+def _tp_product(recipe: str):
+    def product(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+        tokens = x.numel() // x.shape[-1]
+        if recipe == "mxfp8":
+            if tokens % MX_BLOCK == 0 and weight.shape[0] % MX_BLOCK == 0 and weight.shape[1] % MX_BLOCK == 0:
+                return mx_linear(x, weight, bias)
+        elif x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and tokens % 16 == 0 and weight.shape[0] % 16 == 0 \
+                and weight.shape[1] % 16 == 0:
+            return fp8_linear(x, weight, bias)
+        return ops.linear(x, weight, bias)
+
+    return product
 
 
 def _fp8_forward(self, x: torch.Tensor) -> torch.Tensor:

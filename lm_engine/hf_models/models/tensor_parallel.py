@@ -133,13 +133,13 @@ class ColumnParallelLinear(nn.Module):
         init_zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.sequence_parallel and x.is_cuda:
+        if self.sequence_parallel and x.is_cuda and not hasattr(self, "linear_function"):
             from ...parallel import fused_tp
 
             if fused_tp.fused_ok(x, self.weight, x.shape[0] * tp.tp_world()):
                 return fused_tp.ag_linear(x, self.weight, self.bias)  # all-gather inside the GEMM kernel
         x = tp.column_parallel_input(x, self.sequence_parallel)
-        return ops.linear(x, self.weight, self.bias)
+        return getattr(self, "linear_function", ops.linear)(x, self.weight, self.bias)  # an fp8 recipe replaces the product
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features_per_rank={self.out_features_per_rank}, bias={self.bias is not None}"
@@ -169,13 +169,13 @@ class RowParallelLinear(nn.Module):
         init_zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.sequence_parallel and x.is_cuda:
+        if self.sequence_parallel and x.is_cuda and not hasattr(self, "linear_function"):
             from ...parallel import fused_tp
 
             if fused_tp.fused_ok(x, self.weight, x.shape[0]):
                 y = fused_tp.linear_rs(x, self.weight)  # reduce-scatter inside the GEMM epilogue
                 return y if self.bias is None else y + self.bias
-        y = ops.linear(x, self.weight, None)
+        y = getattr(self, "linear_function", ops.linear)(x, self.weight, None)
         if self.overlap_reduction and self.bias is None:
             return tp.row_parallel_output_async(y, self.sequence_parallel)
         y = tp.row_parallel_output(y, self.sequence_parallel)
