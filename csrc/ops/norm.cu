@@ -214,14 +214,25 @@ void rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd
                  float* partial, float* dw, bool accumulate_dw, int T, int H, cudaStream_t stream) {
   if (T == 0) return;
   if (H % 8 != 0 || H > 32768) throw std::runtime_error("rmsnorm: H must be a multiple of 8 and <= 32768");
-  const int rows = rmsnorm_bwd_partial_rows(T);
+  int rows = rmsnorm_bwd_partial_rows(T);
   auto DY = reinterpret_cast<const uint4*>(dy);
   auto HH = reinterpret_cast<const uint4*>(h);
   auto W = reinterpret_cast<const uint4*>(w);
   auto DR = reinterpret_cast<const uint4*>(dres);
   auto DH = reinterpret_cast<uint4*>(dh);
   const int nv = H / 8;
-#define BWD(TH, V) rmsnorm_bwd_kernel<TH, V><<<rows, TH, 0, stream>>>(DY, HH, W, rstd, DR, DH, partial, T, H)
+  // one wave of CTAs: as many as are resident at a time (a partly filled second wave would double the kernel's time)
+#define BWD(TH, V)                                                                                                        \
+  do {                                                                                                                    \
+    static int resident = 0;                                                                                              \
+    if (resident == 0) {                                                                                                  \
+      int per_sm = 0;                                                                                                     \
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_bwd_kernel<TH, V>, TH, 0);                            \
+      resident = sm_count() * (per_sm > 0 ? per_sm : 1);                                                                  \
+    }                                                                                                                     \
+    if (rows > resident) rows = resident;                                                                                 \
+    rmsnorm_bwd_kernel<TH, V><<<rows, TH, 0, stream>>>(DY, HH, W, rstd, DR, DH, partial, T, H);                            \
+  } while (0)
   if (nv <= 256) BWD(256, 1);
   else if (nv <= 512) BWD(256, 2);
   else if (nv <= 1024) BWD(256, 4);

@@ -21,6 +21,12 @@ def _rel_err(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+def _worst_row_err(a, b):
+    """Largest relative error of any single row (a whole-tensor norm can hide one bad row among thousands)."""
+    a, b = a.float().reshape(-1, a.shape[-1]), b.float().reshape(-1, b.shape[-1])
+    return ((a - b).norm(dim=-1) / (b.norm(dim=-1) + 1e-3 * b.norm() / b.shape[0] ** 0.5 + 1e-12)).max().item()
+
+
 @pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("a_mn", [False, True])
 @pytest.mark.parametrize("b_mn", [False, True])
@@ -119,6 +125,54 @@ def test_gemm_pair_unaligned_output_takes_the_register_path(C):
     assert st.item() == 0
     assert _rel_err(out, a.float() @ b.float().t()) < 6e-3
     assert buf[:, N:].abs().sum().item() == 0
+
+
+def _with_canaries(rows, cols, dtype, pad=64):
+    """A [rows, cols] view in the middle of a larger buffer filled with a canary value; returns (view, check)."""
+    canary = 7.0
+    buf = torch.full((rows + 2 * pad, cols + 2 * pad), canary, device="cuda", dtype=dtype)
+    view = buf[pad : pad + rows, pad : pad + cols]
+
+    def check():
+        mask = torch.ones_like(buf, dtype=torch.bool)
+        mask[pad : pad + rows, pad : pad + cols] = False
+        assert bool((buf[mask] == canary).all()), "a kernel wrote outside of its output"
+
+    return view, check
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 256), (1031, 264, 512)])
+def test_bulk_store_epilogues_stay_inside_their_output(C, shape):
+    """Outputs whose edges do not fall on tile boundaries, surrounded by canaries: the bulk tensor stores and reductions of
+    the GEMM epilogues (bf16 store, fp32 accumulate, SwiGLU) and of the block-scaled GEMM must clip at the tensor's edge."""
+    M, N, K = shape
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    out, check = _with_canaries(M, N, torch.bfloat16)
+    C.gemm(a, b, out, False, False, False, 1.0, st, 0, 2)
+    check()
+    assert _rel_err(out, a.float() @ b.float().t()) < 6e-3
+    acc, check32 = _with_canaries(M, N, torch.float32)
+    acc.zero_()
+    C.gemm(a, b, acc, False, False, True, 1.0, st, 0, 2)
+    check32()
+    assert _rel_err(acc, a.float() @ b.float().t()) < 1e-5
+    inter = 384
+    w = torch.randn(2 * inter, K, device="cuda", dtype=torch.bfloat16) * K**-0.5
+    fc, check_fc = _with_canaries(M, 2 * inter, torch.bfloat16)
+    act, check_act = _with_canaries(M, inter, torch.bfloat16)
+    C.gemm_swiglu(a, w, fc, act, st)
+    check_fc()
+    check_act()
+    aq, asf = C.quantize_mx(a, False, 0)
+    bq, bsf = C.quantize_mx(b, False, 0)
+    mx, check_mx = _with_canaries(M, N, torch.bfloat16)
+    C.gemm_mxfp8(aq, asf, bq, bsf, mx, False, False, 0, 0, False, 1.0, st)
+    check_mx()
+    torch.cuda.synchronize()
+    assert st.item() == 0
 
 
 @pytest.mark.parametrize("T,H,I", [(256, 256, 128), (1000, 512, 384), (4096, 1024, 2048)])
@@ -312,11 +366,13 @@ def test_attention_fwd_bwd(C, groups, qpg, d, lengths):
     q32 = qkv.float().requires_grad_(True)
     ref = _attention_reference(q32, cu, groups, qpg, d, scale)
     assert _rel_err(out, ref) < 1e-2
+    assert _worst_row_err(out, ref) < 4e-2  # every token on its own, not only the tensor as a whole
     dout = torch.randn_like(out)
     ref.backward(dout.float())
     dqkv = C.attn_bwd(dout, qkv, out, lse, cu, max(lengths), groups, qpg, d, scale, True, st)
     torch.cuda.synchronize()
     assert st.item() == 0
+    assert _worst_row_err(dqkv, q32.grad) < 6e-2
     g = q32.grad.view(T, groups, qpg + 2, d)
     mine = dqkv.float().view(T, groups, qpg + 2, d)
     assert _rel_err(mine[:, :, qpg + 1], g[:, :, qpg + 1]) < 2e-2  # dV
