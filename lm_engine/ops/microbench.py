@@ -45,6 +45,8 @@ def bench_gemm(args) -> None:
     shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes] if args.shapes else [
         (8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 8192, 8192), (4096, 128256, 4096)]
     trace = torch.zeros(8 * 148, dtype=torch.int64, device="cuda") if args.trace else None
+    if args.swiglu_only:
+        shapes = []
     for M, N, K in shapes:
         flops = 2.0 * M * N * K
         for layout in args.layouts:
@@ -130,7 +132,7 @@ def bench_gemm(args) -> None:
                 record["cublas_ms"], record["cublas_tflops"] = round(ms, 4), round(flops / ms / 1e9, 1)
             record["status"] = int(st.item())
             _emit(record)
-    if args.swiglu:
+    if args.swiglu or args.swiglu_only:
         # c_fc GEMM with the SwiGLU activation in its epilogue against GEMM followed by the stand-alone kernel
         T, H, I = args.tokens, args.hidden, args.intermediate
         x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
@@ -144,7 +146,7 @@ def bench_gemm(args) -> None:
             return C.swiglu_fwd(fc)
 
         ms_f = _time(lambda: C.gemm_swiglu(x, w, fc, act, st), args.iters, args.warmup, flush)
-        ms_u = _time(unfused, args.iters, args.warmup, flush)
+        ms_u = ms_f if args.swiglu_only else _time(unfused, args.iters, args.warmup, flush)
         _emit(dict(op="gemm_swiglu", tokens=T, hidden=H, intermediate=I, fused_ms=round(ms_f, 4), fused_tflops=round(flops / ms_f / 1e9, 1),
                    gemm_then_swiglu_ms=round(ms_u, 4), status=int(st.item())))
 
@@ -362,6 +364,7 @@ def main() -> None:
     parser.add_argument("--trace", action="store_true", help="gemm: report where the MMA and epilogue threads of the CTA-pair kernel wait")
     parser.add_argument("--interleave", action="store_true", help="gemm: candidates and the library take turns launch by launch after heating the GPU to its power-capped clock")
     parser.add_argument("--heat-ms", type=float, default=1500.0, help="gemm --interleave: length of the warm-up under load")
+    parser.add_argument("--swiglu-only", action="store_true", help="gemm: run nothing but the c_fc GEMM with the SwiGLU epilogue (the form to put under a profiler)")
     parser.add_argument("--swiglu", action="store_true", help="gemm: also time the c_fc GEMM with the SwiGLU epilogue")
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)

@@ -307,6 +307,9 @@ class ShardedTrainingEngine:
                         # where the fused optimizer stores the updated values on every rank (element offset in the arena)
                         seg.broadcast = (arena.ptrs, arena.multicast_ptr, arena.offset_of(seg.compute) // seg.compute.element_size())
         self._materialise_buffers(model)
+        sharded = [u for u in self.units if not u.resident]
+        for before, after in zip(sharded[:-1], sharded[1:]):
+            before.next_sharded, after.prev_sharded = after, before
 
     def _peer_storage(self, total_numel: int):
         """With peer-memory collectives every unit's compute and gradient buffers are slices of two symmetric arenas
@@ -393,24 +396,69 @@ class ShardedTrainingEngine:
                     module._buffers[name] = b.to(self.device)
 
     # ------------------------------------------------------------------ parameters that exist in full only while used
-    def _take_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def _take_buffer(self, numel: int, dtype: torch.dtype, stream=None) -> torch.Tensor:
+        """A pooled buffer; the stream that is going to use it first waits for the buffer's last user."""
         free = self._buffer_pool.setdefault((numel, dtype), [])
-        return free.pop() if free else torch.empty(numel, dtype=dtype, device=self.device)
+        if not free:
+            return torch.empty(numel, dtype=dtype, device=self.device)
+        buf, last_use = free.pop()
+        if last_use is not None:
+            (stream if stream is not None else torch.cuda.current_stream()).wait_event(last_use)
+        return buf
 
     def _give_buffer(self, buf: torch.Tensor) -> None:
-        self._buffer_pool.setdefault((buf.numel(), buf.dtype), []).append(buf)
+        last_use = None
+        if self.device.type == "cuda":
+            last_use = torch.cuda.Event()
+            last_use.record()  # on the current stream: whoever used the buffer last
+        self._buffer_pool.setdefault((buf.numel(), buf.dtype), []).append((buf, last_use))
+
+    def _collective_stream(self):
+        """Side stream of the sharded-parameter mode: gathers of the next block and reductions of the previous one run
+        here, under the compute of the current block (CUDA only; CPU ranks run everything in order)."""
+        if self.device.type != "cuda":
+            return None
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        return self._side_stream
+
+    @torch.no_grad()
+    def start_gather(self, unit: "FlatUnit | None") -> None:
+        """Begin the all-gather of a sharded unit on the side stream (no-op on CPU, for resident or already gathered
+        units). ``gather_unit`` picks the result up."""
+        side = self._collective_stream()
+        if unit is None or side is None or unit.resident or unit.compute is not None or getattr(unit, "pending_gather", None) is not None:
+            return
+        buf = self._take_buffer(unit.numel, self.compute_dtype, stream=side)
+        now = torch.cuda.Event()
+        now.record()  # the shard was last written by the optimizer on the compute stream
+        side.wait_event(now)
+        with torch.cuda.stream(side):
+            lo, hi = unit.shard_range
+            buf[lo:hi].copy_(unit.compute_shard)
+            all_gather_in_place(buf, unit.shard_numel, unit.rank, self.shard_group)
+            done = torch.cuda.Event()
+            done.record()
+        unit.pending_gather = (buf, done)
 
     @torch.no_grad()
     def gather_unit(self, unit: FlatUnit, for_backward: bool = False) -> None:
         """Make the full parameters of a sharded unit available (all-gather of the ranks' shards into a pooled
-        buffer); for a backward pass also a zeroed full-size fp32 gradient buffer behind ``param.main_grad``."""
+        buffer, possibly started earlier on the side stream); for a backward pass also a zeroed full-size fp32 gradient
+        buffer behind ``param.main_grad``."""
         if unit.resident:
             return
         if unit.compute is None:
-            buf = self._take_buffer(unit.numel, self.compute_dtype)
-            lo, hi = unit.shard_range
-            buf[lo:hi].copy_(unit.compute_shard)
-            all_gather_in_place(buf, unit.shard_numel, unit.rank, self.shard_group)
+            pending = getattr(unit, "pending_gather", None)
+            if pending is not None:
+                buf, done = pending
+                torch.cuda.current_stream().wait_event(done)
+                unit.pending_gather = None
+            else:
+                buf = self._take_buffer(unit.numel, self.compute_dtype)
+                lo, hi = unit.shard_range
+                buf[lo:hi].copy_(unit.compute_shard)
+                all_gather_in_place(buf, unit.shard_numel, unit.rank, self.shard_group)
             unit.compute = buf
             for slot in unit.slots:
                 slot.param.data = buf[slot.offset : slot.offset + slot.numel].view(slot.shape)
@@ -422,7 +470,8 @@ class ShardedTrainingEngine:
     @torch.no_grad()
     def release_unit(self, unit: FlatUnit) -> None:
         """Give the full buffers back. Gradients of the pass that just ended are summed over the ranks first and this
-        rank's slice is added to its persistent gradient shard."""
+        rank's slice is added to its persistent gradient shard (on the side stream where there is one, so that the
+        reduction runs under the backward pass of the next block)."""
         if unit.resident:
             return
         if unit.grad is not None:
@@ -431,10 +480,25 @@ class ShardedTrainingEngine:
                 if g is not None:
                     slot.param.main_grad.add_(g.to(torch.float32))
                     slot.param.grad = None
-            reduced = reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
-            unit.grad_shard.add_(reduced)
-            self._give_buffer(unit.grad)
+            side = self._collective_stream()
+            if side is None:
+                reduced = reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
+                unit.grad_shard.add_(reduced)
+                self._give_buffer(unit.grad)
+            else:
+                ready = torch.cuda.Event()
+                ready.record()  # every gradient of the unit is in the buffer (and older clears of the shard are done)
+                side.wait_event(ready)
+                with torch.cuda.stream(side):
+                    reduced = reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
+                    unit.grad_shard.add_(reduced)
+                    self._give_buffer(unit.grad)
+                    self._side_done = torch.cuda.Event()
+                    self._side_done.record()
             unit.grad = None
+            for slot in unit.slots:
+                if hasattr(slot.param, "main_grad"):
+                    del slot.param.main_grad
         if unit.compute is not None:
             self._give_buffer(unit.compute)
             unit.compute = None
@@ -446,14 +510,19 @@ class ShardedTrainingEngine:
 
         def before_forward(mod, args):
             self.gather_unit(unit)
+            self.start_gather(getattr(unit, "next_sharded", None))  # the next block's weights arrive under this block's compute
 
         def after_forward(mod, args, output):
-            if not unit.in_backward:  # a forward pass re-run inside the backward pass (activation checkpointing) keeps them
-                self.release_unit(unit)
+            if unit.in_backward:  # a forward pass re-run inside the backward pass (activation checkpointing) keeps them
+                return
+            if torch.is_grad_enabled() and getattr(unit, "next_sharded", None) is None:
+                return  # the last block is the first one the backward pass needs: keep it
+            self.release_unit(unit)
 
         def before_backward(mod, grad_output):
             unit.in_backward = True
             self.gather_unit(unit, for_backward=True)
+            self.start_gather(getattr(unit, "prev_sharded", None))
 
         def after_backward(mod, grad_input, grad_output):
             unit.in_backward = False
@@ -565,6 +634,8 @@ class ShardedTrainingEngine:
                 continue
             if not unit.resident:
                 self.release_unit(unit)  # normally done by the backward hook already
+                if self._side_done is not None:
+                    torch.cuda.current_stream().wait_event(self._side_done)  # the unit's reduction on the side stream
             elif self.shard_world > 1 and self.peer is None:
                 reduce_scatter_in_place(unit.grad, unit.shard_numel, unit.rank, self.shard_group, False)
             if self.replica_world > 1:
