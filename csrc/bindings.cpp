@@ -113,6 +113,23 @@ void gemm_swiglu(const Tensor& x, const Tensor& w, Tensor& fc, Tensor& act, cons
                          fc.stride(0), act.stride(0), status_ptr(status), cur_stream());
 }
 
+// dfc = [d(up) | d(gate)] and act = up * silu(gate) from dy, the down-projection weight w [H, I] and the saved projection fc.
+void gemm_swiglu_bwd(const Tensor& dy, const Tensor& w, const Tensor& fc, Tensor& dfc, Tensor& act, const c10::optional<Tensor>& status) {
+  check_bf16(dy, "dy");
+  check_bf16(w, "w");
+  check_bf16(fc, "fc");
+  check_bf16(dfc, "dfc");
+  check_bf16(act, "act");
+  const Tensor* operands[] = {&dy, &w, &fc, &dfc, &act};  // dfc / act are non-const references: no common initializer_list type
+  for (const Tensor* t : operands) TORCH_CHECK(t->dim() == 2 && t->stride(1) == 1, "gemm_swiglu_bwd operands must be matrices with a unit inner stride");
+  const int64_t M = dy.size(0), K = dy.size(1), I = w.size(1);
+  TORCH_CHECK(w.size(0) == K && fc.size(0) == M && fc.size(1) == 2 * I && dfc.size(0) == M && dfc.size(1) == 2 * I && act.size(0) == M && act.size(1) == I,
+              "gemm_swiglu_bwd: shape mismatch");
+  const c10::cuda::CUDAGuard guard(dy.device());
+  b200::gemm_bf16_swiglu_bwd(dy.data_ptr(), w.data_ptr(), fc.data_ptr(), dfc.data_ptr(), act.data_ptr(), (int)M, (int)I, (int)K, dy.stride(0),
+                             w.stride(0), fc.stride(0), dfc.stride(0), act.stride(0), status_ptr(status), cur_stream());
+}
+
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, double eps,
                                 bool want_sum) {
   check_bf16(x, "x");
@@ -375,6 +392,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("max_ctas") = 0, py::arg("variant") = 0);
   m.def("set_gemm_variant", &set_gemm_variant);
   m.def("gemm_tuning", &gemm_tuning, py::arg("group") = 0, py::arg("k_skew") = 0, py::arg("direct_store") = false, py::arg("trace") = py::none(), py::arg("split_k") = 0);
+  m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd, "down-projection data gradient with the SwiGLU backward in its epilogue", py::arg("dy"), py::arg("w"),
+        py::arg("fc"), py::arg("dfc"), py::arg("act"), py::arg("status") = py::none());
   m.def("gemm_swiglu", &gemm_swiglu, "c_fc GEMM with the SwiGLU activation in its epilogue", py::arg("x"), py::arg("w"), py::arg("fc"), py::arg("act"), py::arg("status") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("eps"),
         py::arg("want_sum") = true);

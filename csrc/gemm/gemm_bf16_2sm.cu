@@ -26,6 +26,12 @@
 // accumulator columns [0,128) and [128,256) of one tile hold up and gate of the same 128 channels; the epilogue
 // writes both halves of the projection (backward needs them) and up * silu(gate), computed from the bf16-rounded
 // values exactly as the stand-alone kernel does, without the projection making a round trip through HBM.
+//
+// SwiGLU-backward epilogue (data gradient of the gated MLP's down-projection): the accumulator is d(act) = dy W; the
+// epilogue reads up and gate of the same rows and channels from the saved projection (plain 16-byte loads, one full
+// 128-byte line per thread and operand) and writes d(up) = d(act) * silu(gate), d(gate) = d(act) * up * silu'(gate) and
+// the recomputed act = up * silu(gate) (the weight gradient of the down-projection needs it), so d(act) never exists in
+// memory. d(act) is rounded to bf16 first, which makes the three outputs bit-identical to GEMM + stand-alone kernel.
 #include <cuda.h>
 
 #include "../common/launch.h"
@@ -51,13 +57,15 @@ constexpr int STAGING_BYTES = 4 * 2 * BOX_BYTES;  // two boxes for each of the f
 constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES + 1024 + 256;
 constexpr int TRACE_WORDS = 8;
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ACC = 3, EPI_SWIGLU = 4 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ACC = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5 };
 
 struct KernelOpts {
   int group;        // > 0: panels of `group` 256-row tiles, rows fastest; < 0: panels of -group 256-column tiles, columns fastest
   int tma_store;    // epilogue leaves through shared memory and bulk tensor stores / reductions
   int k_skew;       // k-block at which tile (i, j) starts its walk over K is (i + j) * k_skew mod k_blocks
-  int swiglu_i;     // EPI_SWIGLU: intermediate size I (N == 2 I)
+  int swiglu_i;     // EPI_SWIGLU: intermediate size I (N == 2 I); EPI_SWIGLU_BWD: I == N
+  const __nv_bfloat16* fc;  // EPI_SWIGLU_BWD: the saved projection [M, 2 I] = [up | gate]
+  long long ldfc;   // its row stride in elements
   int split_k;      // >= 1; > 1 only with the bulk-reduction epilogues: each tile is computed as that many partial sums over K
   long long* trace; // TRACE builds: TRACE_WORDS cycle counters per CTA
 };
@@ -398,6 +406,82 @@ __global__ void __launch_bounds__(THREADS, 1)
         continue;
       }
 
+      if (EPI == EPI_SWIGLU_BWD) {
+        const int I = opts.swiglu_i;
+        uint8_t* box_a = stage0;
+        uint8_t* box_b = stage0 + BOX_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = tc.ni * BN + c * 64;
+          if (col0 >= I) break;
+          uint32_t yp[32];
+          if (TRACE) t0 = clock64();
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          if (TRACE) wait_store += clock64() - t0;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t v[32];
+            B200_TMEM_LD_32(v, t_row + c * 64 + half * 32);
+            uint4 u4[4], g4[4];
+            if (row < M) {
+              const uint4* up = reinterpret_cast<const uint4*>(opts.fc + (long long)row * opts.ldfc + col0 + half * 32);
+              const uint4* gp = reinterpret_cast<const uint4*>(opts.fc + (long long)row * opts.ldfc + I + col0 + half * 32);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                u4[j] = up[j];
+                g4[j] = gp[j];
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) u4[j] = g4[j] = make_uint4(0, 0, 0, 0);
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t uu[4] = {u4[j].x, u4[j].y, u4[j].z, u4[j].w}, gg[4] = {g4[j].x, g4[j].y, g4[j].z, g4[j].w};
+              uint32_t du[4], dg[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 a = unpack_bf16x2(uu[e]), b = unpack_bf16x2(gg[e]);
+                const float2 q = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[8 * j + 2 * e]) * alpha, __uint_as_float(v[8 * j + 2 * e + 1]) * alpha));
+                const float s0 = 1.f / (1.f + __expf(-b.x)), s1 = 1.f / (1.f + __expf(-b.y));
+                const float act0 = b.x * s0, act1 = b.y * s1;
+                const float dact0 = s0 * (1.f + b.x * (1.f - s0)), dact1 = s1 * (1.f + b.y * (1.f - s1));
+                du[e] = pack_bf16x2(q.x * act0, q.y * act1);
+                dg[e] = pack_bf16x2(q.x * a.x * dact0, q.y * a.y * dact1);
+                yp[half * 16 + j * 4 + e] = pack_bf16x2(a.x * act0, a.y * act1);
+              }
+              box_write(box_a, lane, half * 4 + j, make_uint4(du[0], du[1], du[2], du[3]));
+              box_write(box_b, lane, half * 4 + j, make_uint4(dg[0], dg[1], dg[2], dg[3]));
+            }
+          }
+          if (c == BN / 64 - 1 || col0 + 64 >= I) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M) {
+            tma_store_2d(&tmC, box_a, col0, row0);
+            tma_store_2d(&tmC, box_b, I + col0, row0);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) box_write(box_a, lane, j, make_uint4(yp[4 * j], yp[4 * j + 1], yp[4 * j + 2], yp[4 * j + 3]));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M) {
+            tma_store_2d(&tmC2, box_a, col0, row0);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
+
       if (opts.tma_store) {
         constexpr bool kBf16 = EPI == EPI_BF16 || EPI == EPI_BF16_ACC;
         constexpr int kColsPerBox = kBf16 ? 64 : 32;
@@ -654,6 +738,8 @@ void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, l
   a.opts.tma_store = c_ok ? 1 : 0;
   a.opts.k_skew = g_tuning.k_skew;
   a.opts.swiglu_i = 0;
+  a.opts.fc = nullptr;
+  a.opts.ldfc = 0;
   a.opts.split_k = 1;
   if (c_ok && (epi == EPI_F32_ACC || epi == EPI_BF16_ACC) && max_ctas <= 0)
     a.opts.split_k = g_tuning.split_k > 0 ? g_tuning.split_k : default_split(M, N, K, sm_count() / 2);
@@ -687,9 +773,36 @@ void gemm_bf16_swiglu(const void* A, const void* W, void* fc, void* act, int M, 
   a.opts.tma_store = 1;
   a.opts.k_skew = g_tuning.k_skew;
   a.opts.swiglu_i = I;
+  a.opts.fc = nullptr;
+  a.opts.ldfc = 0;
   a.opts.split_k = 1;
   a.opts.trace = nullptr;
   launch_variant<0, 0, EPI_SWIGLU, false>(a);
+}
+
+// d(fc)[M, 2I] and act[M, I] from dy[M, K] . W[K, I] (W row-major [K, I], i.e. the down-projection weight [H, I]) and the saved
+// projection fc[M, 2I] = [up | gate]:  d(up) = d(act) silu(gate), d(gate) = d(act) up silu'(gate), act = up silu(gate).
+void gemm_bf16_swiglu_bwd(const void* dy, const void* W, const void* fc, void* dfc, void* act, int M, int I, int K, long long lddy,
+                          long long ldw, long long ldfc, long long lddfc, long long ldact, int* status, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return;
+  if ((lddy & 7) || (ldw & 7) || (ldfc & 7) || (lddfc & 7) || (ldact & 7) || (I % 64) != 0 || M < 2 * BM ||
+      (reinterpret_cast<uintptr_t>(fc) & 15) != 0)
+    throw std::runtime_error("gemm_bf16_swiglu_bwd: needs I % 64 == 0, M >= 256, 16-byte aligned fc and leading dimensions that are multiples of 8");
+  LaunchArgs a;
+  a.tmA = make_tensor_map_2d_b16(dy, K, M, lddy, BK, BM);
+  a.tmB = make_tensor_map_2d_b16(W, I, K, ldw, 64, BK);  // MN-major: rows are k, columns are the intermediate channels
+  a.tmC = make_tensor_map_2d_b16(dfc, 2 * (long long)I, M, lddfc, 64, 32);
+  a.tmC2 = make_tensor_map_2d_b16(act, I, M, ldact, 64, 32);
+  a.C = dfc; a.M = M; a.N = I; a.K = K; a.ldc = lddfc; a.alpha = 1.f; a.status = status; a.max_ctas = 0; a.stream = stream;
+  a.opts.group = g_tuning.group != 0 ? g_tuning.group : default_group(M, I);
+  a.opts.tma_store = 1;
+  a.opts.k_skew = g_tuning.k_skew;
+  a.opts.swiglu_i = I;
+  a.opts.fc = reinterpret_cast<const __nv_bfloat16*>(fc);
+  a.opts.ldfc = ldfc;
+  a.opts.split_k = 1;
+  a.opts.trace = nullptr;
+  launch_variant<0, 1, EPI_SWIGLU_BWD, false>(a);
 }
 
 }  // namespace b200

@@ -19,6 +19,10 @@ void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, l
 // (needs I % 128 == 0 and M >= 256).
 void gemm_bf16_swiglu(const void* A, const void* W, void* fc, void* act, int M, int I, int K, long long lda, long long ldw,
                       long long ldfc, long long ldact, int* status, cudaStream_t stream);
+// d(fc)[M, 2I] and act[M, I] from d(act) = dy[M, K] . W[K, I] and the saved projection fc = [up | gate]: the SwiGLU backward in the
+// epilogue of the down-projection's data-gradient GEMM (needs I % 64 == 0 and M >= 256).
+void gemm_bf16_swiglu_bwd(const void* dy, const void* W, const void* fc, void* dfc, void* act, int M, int I, int K, long long lddy,
+                          long long ldw, long long ldfc, long long lddfc, long long ldact, int* status, cudaStream_t stream);
 // Process-wide knobs of the CTA-pair kernel (0 / null = built-in choice); meant for micro-benchmarks.
 struct PairGemmTuning {
   int group = 0;               // tile raster: > 0 row panels of that many 256-row tiles, < 0 column panels

@@ -95,12 +95,20 @@ class FusedDenseBlockFn(torch.autograd.Function):
         dy = dy.contiguous()
 
         # ---- MLP
-        dact = torch.empty(T, w_proj.shape[1], device=x.device, dtype=x.dtype)
-        with site("bwd.mlp_c_proj.dgrad"):
-            C.gemm(dy, w_proj, dact, False, True, False, 1.0, st, 0)
-        with site("bwd.swiglu"):
-            dfc, act = C.swiglu_bwd(dact, fc, True)
-        del dact
+        inter = w_proj.shape[1]
+        if hasattr(C, "gemm_swiglu_bwd") and inter % 64 == 0 and T >= 256:
+            # data gradient of the down-projection with the SwiGLU backward in its epilogue: d(act) never reaches memory
+            dfc = torch.empty(T, 2 * inter, device=x.device, dtype=x.dtype)
+            act = torch.empty(T, inter, device=x.device, dtype=x.dtype)
+            with site("bwd.mlp_c_proj.dgrad+swiglu"):
+                C.gemm_swiglu_bwd(dy, w_proj, fc, dfc, act, st)
+        else:
+            dact = torch.empty(T, inter, device=x.device, dtype=x.dtype)
+            with site("bwd.mlp_c_proj.dgrad"):
+                C.gemm(dy, w_proj, dact, False, True, False, 1.0, st, 0)
+            with site("bwd.swiglu"):
+                dfc, act = C.swiglu_bwd(dact, fc, True)
+            del dact
         with site("bwd.mlp_c_proj.wgrad"):
             g_proj = _wgrad(C, dy, act, w_proj, st)
         del act

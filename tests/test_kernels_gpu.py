@@ -127,6 +127,33 @@ def test_gemm_pair_unaligned_output_takes_the_register_path(C):
     assert buf[:, N:].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("T,H,I", [(256, 256, 128), (1000, 512, 384), (4096, 1024, 2048)])
+def test_gemm_with_swiglu_backward_epilogue(C, T, H, I):
+    torch.manual_seed(7)
+    dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(H, I, device="cuda", dtype=torch.bfloat16) * (H**-0.5)  # the down-projection weight [out, in]
+    fc = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    dfc = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    act = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    C.gemm_swiglu_bwd(dy, w, fc, dfc, act, st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    # fp32 reference under autograd
+    f32 = fc.float().requires_grad_(True)
+    up, gate = f32[:, :I], f32[:, I:]
+    y = up * torch.nn.functional.silu(gate)
+    dact = dy.float() @ w.float()
+    y.backward(dact)
+    assert _rel_err(act, y) < 1e-2
+    assert _rel_err(dfc, f32.grad) < 1e-2
+    # same bits as the two-kernel path
+    dact16 = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    C.gemm(dy, w, dact16, False, True, False, 1.0, st, 0, 2)
+    dfc2, act2 = C.swiglu_bwd(dact16, fc, True)
+    assert torch.equal(dfc, dfc2) and torch.equal(act, act2)
+
+
 def _with_canaries(rows, cols, dtype, pad=64):
     """A [rows, cols] view in the middle of a larger buffer filled with a canary value; returns (view, check)."""
     canary = 7.0
