@@ -325,6 +325,16 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint
         "r"((ARR)[31])                                                                                              \
       : "memory")
 
+#define B200_TMEM_ST_16(ADDR, ARR)                                                                                  \
+  asm volatile(                                                                                                     \
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                               \
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                                    \
+      :                                                                                                             \
+      : "r"(ADDR), "r"((ARR)[0]), "r"((ARR)[1]), "r"((ARR)[2]), "r"((ARR)[3]), "r"((ARR)[4]), "r"((ARR)[5]),        \
+        "r"((ARR)[6]), "r"((ARR)[7]), "r"((ARR)[8]), "r"((ARR)[9]), "r"((ARR)[10]), "r"((ARR)[11]), "r"((ARR)[12]), \
+        "r"((ARR)[13]), "r"((ARR)[14]), "r"((ARR)[15])                                                              \
+      : "memory")
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -340,6 +350,12 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
   __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v);
   return __bfloat1622float2(b);
 }
+
+// sigmoid and SiLU with the approximate exponential and reciprocal (two MUFU operations and two FMA-pipe operations per
+// value instead of an IEEE division); every kernel that evaluates SwiGLU uses these, so that a fused epilogue and the
+// stand-alone kernel produce the same bits.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_fast(float x) { return x * sigmoid_fast(x); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

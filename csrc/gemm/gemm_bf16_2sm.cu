@@ -28,8 +28,8 @@
 // values exactly as the stand-alone kernel does, without the projection making a round trip through HBM.
 //
 // SwiGLU-backward epilogue (data gradient of the gated MLP's down-projection): the accumulator is d(act) = dy W; the
-// epilogue reads up and gate of the same rows and channels from the saved projection (plain 16-byte loads, one full
-// 128-byte line per thread and operand) and writes d(up) = d(act) * silu(gate), d(gate) = d(act) * up * silu'(gate) and
+// epilogue reads up and gate of the same rows and channels from the saved projection (plain 16-byte loads requested
+// 32 columns ahead of the arithmetic) and writes d(up) = d(act) * silu(gate), d(gate) = d(act) * up * silu'(gate) and
 // the recomputed act = up * silu(gate) (the weight gradient of the down-projection needs it), so d(act) never exists in
 // memory. d(act) is rounded to bf16 first, which makes the three outputs bit-identical to GEMM + stand-alone kernel.
 #include <cuda.h>
@@ -128,7 +128,7 @@ __device__ __forceinline__ void umma_commit_2sm(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return silu_fast(x); }
 
 struct TileCoord {
   int mi, ni;  // tile indices (256-row, 256-column units)
@@ -410,10 +410,21 @@ __global__ void __launch_bounds__(THREADS, 1)
         const int I = opts.swiglu_i;
         uint8_t* box_a = stage0;
         uint8_t* box_b = stage0 + BOX_BYTES;
+        const int tile_col0 = tc.ni * BN;
+        const int halves = min(BN, I - tile_col0) / 32;  // 32-column halves of this tile (I % 64 == 0: an even number)
+        // rows past M read the last row instead (their results never leave: the bulk stores clip at M)
+        const __nv_bfloat16* fc_row = opts.fc + (long long)min(row, M - 1) * opts.ldfc + tile_col0;
+        // up / gate of the NEXT 32 columns are requested before the current ones are worked on, so that their trip from
+        // L2 or HBM is covered by about a thousand instructions of arithmetic
+        uint4 un[4], gn[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          un[j] = __ldg(reinterpret_cast<const uint4*>(fc_row) + j);
+          gn[j] = __ldg(reinterpret_cast<const uint4*>(fc_row + I) + j);
+        }
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          const int col0 = tc.ni * BN + c * 64;
-          if (col0 >= I) break;
+        for (int c = 0; c < halves / 2; ++c) {
+          const int col0 = tile_col0 + c * 64;
           uint32_t yp[32];
           if (TRACE) t0 = clock64();
           if (lane == 0) tma_store_wait_read<0>();
@@ -421,22 +432,29 @@ __global__ void __launch_bounds__(THREADS, 1)
           if (TRACE) wait_store += clock64() - t0;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
+            const int h = 2 * c + half;
             uint32_t v[32];
-            B200_TMEM_LD_32(v, t_row + c * 64 + half * 32);
+            B200_TMEM_LD_32(v, t_row + h * 32);
             uint4 u4[4], g4[4];
-            if (row < M) {
-              const uint4* up = reinterpret_cast<const uint4*>(opts.fc + (long long)row * opts.ldfc + col0 + half * 32);
-              const uint4* gp = reinterpret_cast<const uint4*>(opts.fc + (long long)row * opts.ldfc + I + col0 + half * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              u4[j] = un[j];
+              g4[j] = gn[j];
+            }
+            if (h + 1 < halves) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                u4[j] = up[j];
-                g4[j] = gp[j];
+                un[j] = __ldg(reinterpret_cast<const uint4*>(fc_row + (h + 1) * 32) + j);
+                gn[j] = __ldg(reinterpret_cast<const uint4*>(fc_row + I + (h + 1) * 32) + j);
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) u4[j] = g4[j] = make_uint4(0, 0, 0, 0);
             }
             tmem_ld_wait();
+            if (h + 1 == halves) {
+              // last read of this accumulator: hand the TMEM buffer back before the arithmetic and the stores
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t uu[4] = {u4[j].x, u4[j].y, u4[j].z, u4[j].w}, gg[4] = {g4[j].x, g4[j].y, g4[j].z, g4[j].w};
@@ -445,7 +463,7 @@ __global__ void __launch_bounds__(THREADS, 1)
               for (int e = 0; e < 4; ++e) {
                 const float2 a = unpack_bf16x2(uu[e]), b = unpack_bf16x2(gg[e]);
                 const float2 q = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[8 * j + 2 * e]) * alpha, __uint_as_float(v[8 * j + 2 * e + 1]) * alpha));
-                const float s0 = 1.f / (1.f + __expf(-b.x)), s1 = 1.f / (1.f + __expf(-b.y));
+                const float s0 = sigmoid_fast(b.x), s1 = sigmoid_fast(b.y);
                 const float act0 = b.x * s0, act1 = b.y * s1;
                 const float dact0 = s0 * (1.f + b.x * (1.f - s0)), dact1 = s1 * (1.f + b.y * (1.f - s1));
                 du[e] = pack_bf16x2(q.x * act0, q.y * act1);
@@ -455,11 +473,6 @@ __global__ void __launch_bounds__(THREADS, 1)
               box_write(box_a, lane, half * 4 + j, make_uint4(du[0], du[1], du[2], du[3]));
               box_write(box_b, lane, half * 4 + j, make_uint4(dg[0], dg[1], dg[2], dg[3]));
             }
-          }
-          if (c == BN / 64 - 1 || col0 + 64 >= I) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -801,8 +814,9 @@ void gemm_bf16_swiglu_bwd(const void* dy, const void* W, const void* fc, void* d
   a.opts.fc = reinterpret_cast<const __nv_bfloat16*>(fc);
   a.opts.ldfc = ldfc;
   a.opts.split_k = 1;
-  a.opts.trace = nullptr;
-  launch_variant<0, 1, EPI_SWIGLU_BWD, false>(a);
+  a.opts.trace = g_tuning.trace;
+  if (a.opts.trace != nullptr) launch_variant<0, 1, EPI_SWIGLU_BWD, true>(a);
+  else launch_variant<0, 1, EPI_SWIGLU_BWD, false>(a);
 }
 
 }  // namespace b200

@@ -18,6 +18,9 @@ void attn_varlen_bwd(const void* dout, const void* qkv, long long qkv_stride, co
                      const int* cu_seqlens, int num_docs, int T, int groups, int qpg, int head_dim, float scale,
                      bool causal, int* status, cudaStream_t stream);
 
+// Cycle counters of the first CTA of every following attn_varlen_bwd launch go to `words` (16 int64; nullptr turns it off).
+void attn_bwd_set_trace(long long* words);
+
 // Stick-breaking attention forward (sb_attention_fwd.cu): same buffers; rem: [groups * qpg, T] fp32 = 1 - sum of weights.
 void sb_attn_varlen_fwd(const void* qkv, long long qkv_stride, void* out, long long out_stride, float* rem, const int* cu_seqlens,
                         int num_docs, int T, int groups, int qpg, int head_dim, float scale, int* status, cudaStream_t stream);

@@ -93,7 +93,18 @@ Tensor sb_attn_bwd(const Tensor& dout, const Tensor& drem, const Tensor& qkv, co
 
 }  // namespace
 
+// trace: int64 [16] on the device, or None to switch the counters off.
+void attn_bwd_trace(const c10::optional<Tensor>& trace) {
+  if (trace.has_value()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 16 && trace->is_contiguous(), "trace: int64 [16] on the device");
+    attn_bwd_set_trace(reinterpret_cast<long long*>(trace->data_ptr<int64_t>()));
+  } else {
+    attn_bwd_set_trace(nullptr);
+  }
+}
+
 void register_attention(pybind11::module_& m) {
+  m.def("attn_bwd_trace", &attn_bwd_trace, pybind11::arg("trace") = pybind11::none());
   m.def("sb_attn_fwd", &sb_attn_fwd);
   m.def("sb_attn_bwd", &sb_attn_bwd);
   m.def("attn_fwd", &attn_fwd);

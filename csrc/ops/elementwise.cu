@@ -9,7 +9,7 @@ namespace b200 {
 
 namespace {
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return silu_fast(x); }
 
 inline int ew_grid(long long work_items, int threads) {
   long long blocks = (work_items + threads - 1) / threads;
@@ -61,7 +61,7 @@ __global__ void swiglu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __r
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 a = unpack_bf16x2(uu[e]), b = unpack_bf16x2(gg[e]), q = unpack_bf16x2(dd[e]);
-      const float s0 = 1.f / (1.f + __expf(-b.x)), s1 = 1.f / (1.f + __expf(-b.y));
+      const float s0 = sigmoid_fast(b.x), s1 = sigmoid_fast(b.y);
       const float act0 = b.x * s0, act1 = b.y * s1;
       const float dact0 = s0 * (1.f + b.x * (1.f - s0)), dact1 = s1 * (1.f + b.y * (1.f - s1));
       du[e] = pack_bf16x2(q.x * act0, q.y * act1);

@@ -161,7 +161,7 @@ __global__ void moe_swiglu_bwd_kernel(const uint4* __restrict__ fc, const uint4*
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 a = unpack_bf16x2(uu[e]), b = unpack_bf16x2(gg[e]), q = unpack_bf16x2(dd[e]);
-      const float s0 = 1.f / (1.f + __expf(-b.x)), s1 = 1.f / (1.f + __expf(-b.y));
+      const float s0 = sigmoid_fast(b.x), s1 = sigmoid_fast(b.y);
       const float silu0 = b.x * s0, silu1 = b.y * s1;
       const float ds0 = s0 * (1.f + b.x * (1.f - s0)), ds1 = s1 * (1.f + b.y * (1.f - s1));
       const float y0 = a.x * silu0, y1 = a.y * silu1;

@@ -45,7 +45,7 @@ def bench_gemm(args) -> None:
     shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes] if args.shapes else [
         (8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 8192, 8192), (4096, 128256, 4096)]
     trace = torch.zeros(8 * 148, dtype=torch.int64, device="cuda") if args.trace else None
-    if args.swiglu_only:
+    if args.swiglu_only or args.swiglu_bwd:
         shapes = []
     for M, N, K in shapes:
         flops = 2.0 * M * N * K
@@ -149,6 +149,55 @@ def bench_gemm(args) -> None:
         ms_u = ms_f if args.swiglu_only else _time(unfused, args.iters, args.warmup, flush)
         _emit(dict(op="gemm_swiglu", tokens=T, hidden=H, intermediate=I, fused_ms=round(ms_f, 4), fused_tflops=round(flops / ms_f / 1e9, 1),
                    gemm_then_swiglu_ms=round(ms_u, 4), status=int(st.item())))
+    if args.swiglu_bwd:
+        # data gradient of the down-projection with the SwiGLU backward in its epilogue against GEMM + stand-alone kernel
+        T, H, I = args.tokens, args.hidden, args.intermediate
+        dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(H, I, device="cuda", dtype=torch.bfloat16) * 0.02
+        fc = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+        dfc = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+        act = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+        dact = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * T * I * H
+
+        def unfused():
+            C.gemm(dy, w, dact, False, True, False, 1.0, st, 0, 2)
+            return C.swiglu_bwd(dact, fc, True)
+
+        record = dict(op="gemm_swiglu_bwd", tokens=T, hidden=H, intermediate=I)
+        samples = {"fused": [], "gemm_then_swiglu_bwd": [], "gemm_alone": []}
+        calls = {"fused": lambda: C.gemm_swiglu_bwd(dy, w, fc, dfc, act, st), "gemm_then_swiglu_bwd": unfused,
+                 "gemm_alone": lambda: C.gemm(dy, w, dact, False, True, False, 1.0, st, 0, 2)}
+        for _ in range(args.warmup):
+            for fn in calls.values():
+                fn()
+        for _ in range(args.iters):  # the three take turns, so that clock drift under the power cap hits them alike
+            for key, fn in calls.items():
+                flush.zero_() if flush is not None else None
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                e1.synchronize()
+                samples[key].append(e0.elapsed_time(e1))
+        for key, values in samples.items():
+            values.sort()
+            record[f"{key}_ms"] = round(values[len(values) // 2], 4)
+        record["fused_tflops"] = round(flops / record["fused_ms"] / 1e9, 1)
+        if trace is not None:
+            C.gemm_tuning(0, 0, False, trace, 0)
+            C.gemm_swiglu_bwd(dy, w, fc, dfc, act, st)
+            torch.cuda.synchronize()
+            C.gemm_tuning(0, 0, False, None, 0)
+            t = trace.view(148, 8)[0::2].double()
+            total, epi_total = t[:, 3].clamp(min=1), t[:, 5].clamp(min=1)
+            record["trace"] = dict(mma_wait_operands=round((t[:, 1] / total).mean().item(), 3),
+                                   mma_wait_accumulator=round((t[:, 2] / total).mean().item(), 3),
+                                   epilogue_wait_accumulator=round((t[:, 4] / epi_total).mean().item(), 3),
+                                   epilogue_wait_store=round((t[:, 7] / epi_total).mean().item(), 3),
+                                   mma_cycles=int(total.mean().item()), tiles_per_pair=round(t[:, 6].mean().item(), 2))
+        record["status"] = int(st.item())
+        _emit(record)
 
 
 def bench_mxfp8(args) -> None:
@@ -206,7 +255,21 @@ def bench_attention(args) -> None:
         if args.direction in ("all", "bwd"):
             ms = _time(lambda: C.attn_bwd(dout, qkv, out, lse, cu, L, groups, qpg, d, d**-0.5, True, st), args.iters, args.warmup, flush)
             record["bwd_ms"], record["bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
-        if not args.profile:
+            if args.trace:
+                # cycle counters of the backward kernel's first CTA (the one with the most query tiles): clocks per
+                # (head, query tile) step that its arithmetic threads and its MMA thread spend in each phase / wait
+                words = torch.zeros(16, dtype=torch.int64, device="cuda")
+                C.attn_bwd_trace(words)
+                C.attn_bwd(dout, qkv, out, lse, cu, L, groups, qpg, d, d**-0.5, True, st)
+                torch.cuda.synchronize()
+                C.attn_bwd_trace(None)
+                w = words.tolist()
+                steps = max(w[15], 1)
+                names = ["wait_S", "P_from_S", "wait_dQ", "dQ_to_staging+issue", "wait_reduction_read", "wait_dP", "step_barrier",
+                         "dS_from_dP", "arithmetic_total", "mma_wait_P", "mma_wait_Q", "mma_wait_dS", "mma_wait_dQ_drained", "mma_wait_dO", "mma_total"]
+                record["bwd_trace_clocks_per_step"] = {name: round(w[i] / steps, 1) for i, name in enumerate(names)}
+                record["bwd_trace_steps"] = steps
+        if not args.profile and not args.trace:
             try:
                 from flash_attn import flash_attn_varlen_func
 
@@ -222,7 +285,7 @@ def bench_attention(args) -> None:
                 record["flash_attn2_bwd_ms"], record["flash_attn2_bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
             except ImportError:
                 pass
-        if hasattr(C, "sb_attn_bwd") and not args.profile:
+        if hasattr(C, "sb_attn_bwd") and not args.profile and not args.trace:
             # stick-breaking attention on the same buffer (strictly causal, same matrix products as the softmax kernels)
             sb_out, sb_rem = C.sb_attn_fwd(qkv, cu, groups, qpg, d, d**-0.5, st)
             d_rem = torch.randn_like(sb_rem)
@@ -365,6 +428,7 @@ def main() -> None:
     parser.add_argument("--interleave", action="store_true", help="gemm: candidates and the library take turns launch by launch after heating the GPU to its power-capped clock")
     parser.add_argument("--heat-ms", type=float, default=1500.0, help="gemm --interleave: length of the warm-up under load")
     parser.add_argument("--swiglu-only", action="store_true", help="gemm: run nothing but the c_fc GEMM with the SwiGLU epilogue (the form to put under a profiler)")
+    parser.add_argument("--swiglu-bwd", action="store_true", help="gemm: time only the down-projection data gradient with the SwiGLU backward in its epilogue")
     parser.add_argument("--swiglu", action="store_true", help="gemm: also time the c_fc GEMM with the SwiGLU epilogue")
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
