@@ -3,7 +3,7 @@
 // One CTA owns 128 keys of one document and one key/value head. K and V stay resident in shared memory;
 // the CTA walks the query heads of the group and, for each, the query tiles that can see these keys:
 //   S^T  = K Q^T,  dP^T = V dO^T                      (tcgen05, fp32 in TMEM)
-//   P^T  = exp2(S^T * scale*log2e - lse*log2e)         (256 threads: row = key, two warps share a row and split its columns)
+//   P^T  = exp2(S^T * scale*log2e - lse*log2e)         (256 arithmetic threads: row = key, two warps share a row and split its columns)
 //   dS^T = P^T o (dP^T - delta) * scale
 //   dV  += P^T dO,  dK += dS^T Q,  dQ_tile = dS K       (tcgen05; dQ is added to an fp32 buffer by bulk tensor reductions)
 // P^T never visits shared memory: it is written as bf16 over the S^T columns of tensor memory it was computed from and
@@ -16,7 +16,7 @@
 // arithmetic warps). The staging holds half a tile: the drain warps write the first 64 columns, keep the other 64 in
 // registers (which frees the tensor-memory columns at once) and write them when the first reduction has read the boxes.
 // Q is double-buffered, so S(i+1) is issued as soon as dV(i) has consumed P(i). Order of a step i:
-//   MMA thread       dV(i) S(i+1) | dK(i) dQ(i) | dP(i+1) (once dQ(i) has left the columns of dP(i))
+//   MMA thread       dV(i) S(i+1) | dQ(i) dK(i) | dP(i+1) (once dQ(i) has left the columns of dP(i))
 //   arithmetic warps P(i) from S(i) | dS(i) from dP(i)
 //   drain warps      dQ(i): first half to the boxes, reduce, second half to the boxes, reduce
 // dO(i+1) is loaded as soon as dV(i) has retired, Q(i+2) as soon as dK(i) has.
@@ -59,7 +59,7 @@ struct BwdSmem {
 
 enum {
   B_KV = 0, B_Q_FULL = 1 /* two */, B_Q_EMPTY = 3 /* two */, B_DO_FULL = 5, B_DO_EMPTY = 6, B_S_FULL = 7, B_DP_FULL = 8,
-  B_P_READY = 9, B_DS_READY = 10, B_DQ_FULL = 11, B_DQ_DRAINED = 12, B_COUNT = 13
+  B_P_READY = 9, B_DS_READY = 10, B_DQ_FULL = 11, B_DQ_DRAINED = 12, B_ROWS = 13, B_COUNT = 14
 };
 
 template <int D, bool TRACE>
@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
     s_tile[0] = start;
     s_tile[1] = found < 0 ? -1 : len;
     s_tile[2] = kt;
-    for (int b = 0; b < B_COUNT; ++b) mbar_init(&bars[b], (b == B_P_READY || b == B_DS_READY) ? SOFTMAX_THREADS : (b == B_DQ_DRAINED ? DRAIN_WARPS * 32 : 1));
+    for (int b = 0; b < B_COUNT; ++b) mbar_init(&bars[b], (b == B_P_READY || b == B_DS_READY || b == B_ROWS) ? SOFTMAX_THREADS : (b == B_DQ_DRAINED ? DRAIN_WARPS * 32 : 1));
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -332,7 +332,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
         for (int c = 0; c < PB; ++c) B200_TMEM_LD_32(o[c], tmem_dP + lane_addr + c * 32);
         tmem_ld_wait();
         to_boxes(o);
-        reduce(0);
       }
       {
         uint32_t o[PB][32];  // the second half waits in registers: the tensor-memory columns are free from here on
@@ -341,6 +340,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive(&bars[B_DQ_DRAINED]);
+        reduce(0);  // may block while the engine's queue is full: only after the columns have been handed back
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         to_boxes(o);
@@ -383,13 +383,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
 
     // (head, query tile) of the current step, advanced without divisions
     int qh = 0, qt = first_q_tile;
+    // The statistics of step i are published through the mbarrier B_ROWS (completion i): written by all arithmetic
+    // threads, step 0 here and step i + 1 at the start of dS(i), when every thread is known to have finished dS(i - 1),
+    // the last reader of that buffer (dP(i) is issued only after dS(i - 1) of all threads has been consumed by dQ(i - 1)).
     if (n_iter > 0) stage_rows(0, qt * BT, fetch_row(grp * qpg, qt * BT));
-    if (named_barrier_or(1, SOFTMAX_THREADS, false)) ok = false;
+    mbar_arrive(&bars[B_ROWS]);
     const bool tr = tracing && st == 0;
     long long tw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0;
     const long long t_begin = tr ? clock64() : 0;
 
-    bool got = true;  // false once one of this thread's waits gave up; every thread learns of it at the next barrier
+    bool got = true;  // false once one of this thread's waits gave up
     for (int it = 0; it < n_iter && ok; ++it) {
       const int q0 = qt * BT;
       int next_qh = qh, next_qt = qt + 1;
@@ -407,6 +410,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
         const int first_visible = kv_valid ? (causal ? kv_local - q0 : 0) : BT;  // query columns below this see nothing of this key
         if (tr) t0 = clock64();
         if (!mbar_wait(&bars[B_S_FULL], it & 1, abort_flag)) {
+          raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
+          got = false;
+        }
+        if (got && !mbar_wait(&bars[B_ROWS], it & 1, abort_flag)) {
           raise_status(status, kStatusWaitTimeoutEpilogue, abort_flag);
           got = false;
         }
@@ -454,6 +461,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
         }
         if (tr) { tw[5] += clock64() - t0; t0 = clock64(); }
         tc_fence_after_sync();
+        if (it + 1 < n_iter) {
+          stage_rows((it + 1) & 1, next_qt * BT, next_row);
+          mbar_arrive(&bars[B_ROWS]);
+        }
 #pragma unroll
         for (int cc = 0; cc < PART_CHUNKS; ++cc) {
           const int c = (part * PART_COLS) / 32 + cc;  // 32-column chunk of the tile
@@ -485,10 +496,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)  // 14 warps: four on two of t
         mbar_arrive(&bars[B_DS_READY]);
         if (tr) { tw[7] += clock64() - t0; t0 = clock64(); }
       }
-      // statistics of the next step; the barrier publishes them and lets every thread learn of a wait that gave up
-      if (it + 1 < n_iter) stage_rows((it + 1) & 1, next_qt * BT, next_row);
-      if (named_barrier_or(1, SOFTMAX_THREADS, !got)) { ok = false; break; }
-      if (tr) { tw[6] += clock64() - t0; t0 = clock64(); }
+      if (!got) break;  // this thread's wait gave up and raised the flag: the other threads' waits end on it
       qh = next_qh;
       qt = next_qt;
     }

@@ -265,9 +265,9 @@ def bench_attention(args) -> None:
                 C.attn_bwd_trace(None)
                 w = words.tolist()
                 steps = max(w[15], 1)
-                names = ["wait_S", "P_from_S", "wait_dQ", "dQ_to_staging+issue", "wait_reduction_read", "wait_dP", "step_barrier",
-                         "dS_from_dP", "arithmetic_total", "mma_wait_P", "mma_wait_Q", "mma_wait_dS", "mma_wait_dQ_drained", "mma_wait_dO", "mma_total"]
-                record["bwd_trace_clocks_per_step"] = {name: round(w[i] / steps, 1) for i, name in enumerate(names)}
+                names = ["wait_S", "P_from_S", None, None, None, "wait_dP", None, "dS_from_dP", "arithmetic_total",
+                         "mma_wait_P", "mma_wait_Q", "mma_wait_dS", "mma_wait_dQ_drained", "mma_wait_dO", "mma_total"]
+                record["bwd_trace_clocks_per_step"] = {name: round(w[i] / steps, 1) for i, name in enumerate(names) if name}
                 record["bwd_trace_steps"] = steps
         if not args.profile and not args.trace:
             try:
