@@ -20,7 +20,7 @@ from ... import ops
 from ...enums import Kernel
 from ...kernels import is_kernel_allowed
 from ...utils import ProcessGroupManager
-from ..loss import add_aux_loss
+from ..loss import add_aux_loss, add_router_statistics
 from ..parameter import mark_parameter_as_mup_learning_rate, mark_parameter_as_no_weight_decay
 from .activations import get_activation_function, is_glu
 from .basic import ParameterizedLinear, init_zeros_
@@ -167,13 +167,16 @@ class MoE(nn.Module):
         if x.is_cuda and logits.dim() == 2 and is_kernel_allowed(Kernel.scattermoe):
             from ...ops.sequence import topk_route
 
-            weights, experts, _ = topk_route(logits, self.top_k)  # one kernel: top-k + softmax of the selected logits
+            # one kernel: top-k, softmax of the selected logits and (while training) the tokens per expert
+            weights, experts, counts = topk_route(logits, self.top_k, want_counts=self.training)
+            self._tokens_per_expert = counts
             return logits, weights.type_as(x), experts
         if self.top_k == 1:
             top_logits, experts = logits.max(dim=-1, keepdim=True)
         else:
             top_logits, experts = logits.topk(self.top_k, dim=-1)
         weights = F.softmax(top_logits.float(), dim=-1).type_as(x)
+        self._tokens_per_expert = None
         return logits, weights, experts
 
     # ------------------------------------------------------------------ experts
@@ -215,19 +218,22 @@ class MoE(nn.Module):
         if self.shared_intermediate_size is not None:
             out = out + self.c_proj_shared(self.act(self.c_fc_shared(x)))
         out = self.dropout(out.reshape(shape))
-        add_aux_loss(self._aux_loss(logits, selected) if self.training else 0)
+        if self.training:
+            self._router_statistics(logits, selected)
         return out
 
-    def _aux_loss(self, logits: torch.Tensor, selected: torch.Tensor) -> torch.Tensor:
+    def _router_statistics(self, logits: torch.Tensor, selected: torch.Tensor) -> None:
+        """Load-balancing and z loss of this layer, handed to the loss module unfinished (see `add_router_statistics`)."""
         logits = logits.reshape(-1, logits.shape[-1])
         probs = torch.softmax(logits, dim=-1)
-        freq = torch.bincount(selected.flatten(), minlength=self.num_experts).float()
-        if ProcessGroupManager.is_initialized() and ProcessGroupManager.get_data_parallel_world_size() > 1:
-            freq = freq.clone()
-            dist.all_reduce(freq, group=ProcessGroupManager.get_data_parallel_group())
-        balance = self.num_experts * (F.normalize(probs.sum(0), p=1, dim=0) * F.normalize(freq, p=1, dim=0)).sum()
+        counts = getattr(self, "_tokens_per_expert", None)
+        self._tokens_per_expert = None
+        if counts is None:
+            # no host synchronisation (bincount needs one to size its output)
+            counts = torch.zeros(self.num_experts, device=logits.device, dtype=torch.float32)
+            counts.index_add_(0, selected.flatten(), torch.ones(selected.numel(), device=logits.device, dtype=torch.float32))
         z = (torch.logsumexp(logits, dim=-1) ** 2).mean()
-        return (balance + 0.1 * z).type_as(logits)
+        add_router_statistics(probs.sum(0), counts.float(), z, logits.dtype)
 
     def get_num_active_parameters(self) -> int:
         total = sum(p.numel() for p in self.parameters())

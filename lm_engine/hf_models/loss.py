@@ -9,6 +9,7 @@ variant under tensor parallelism.
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 import torch.nn.functional as F
 
 from .. import ops
@@ -16,11 +17,15 @@ from ..enums import Kernel
 from ..kernels import is_kernel_allowed
 
 _AUX_LOSS: torch.Tensor | float = 0
+# Router statistics of the MoE layers of the current forward pass, turned into their auxiliary losses when the loss is
+# asked for: (probability mass per expert [E] (differentiable), tokens per expert [E], z term, dtype of the logits).
+_ROUTER_STATISTICS: list[tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.dtype]] = []
 
 
 def clear_aux_loss() -> None:
     global _AUX_LOSS
     _AUX_LOSS = 0
+    _ROUTER_STATISTICS.clear()
 
 
 def add_aux_loss(aux_loss: torch.Tensor | float) -> None:
@@ -28,7 +33,34 @@ def add_aux_loss(aux_loss: torch.Tensor | float) -> None:
     _AUX_LOSS = _AUX_LOSS + aux_loss
 
 
+def add_router_statistics(probability_mass: torch.Tensor, tokens_per_expert: torch.Tensor, z_term: torch.Tensor,
+                          dtype: torch.dtype) -> None:
+    """One MoE layer's share of the load-balancing loss, left unfinished: the token counts of all layers are summed over
+    the data-parallel group by ONE collective in `get_aux_loss` instead of one per layer (the counts carry no gradient,
+    so the value and the gradients are those of the per-layer formulation,
+    lm_engine/hf_models/modeling_utils/mlp_blocks/moe.py:259-290 in the reference)."""
+    _ROUTER_STATISTICS.append((probability_mass, tokens_per_expert, z_term, dtype))
+
+
+def _finish_router_statistics() -> torch.Tensor:
+    from ..utils import ProcessGroupManager
+
+    probability_mass = torch.stack([p for p, _, _, _ in _ROUTER_STATISTICS])           # [layers, experts]
+    tokens = torch.stack([f for _, f, _, _ in _ROUTER_STATISTICS]).float()             # [layers, experts]
+    z = torch.stack([z for _, _, z, _ in _ROUTER_STATISTICS])                          # [layers]
+    dtype = _ROUTER_STATISTICS[0][3]
+    _ROUTER_STATISTICS.clear()
+    if ProcessGroupManager.is_initialized() and ProcessGroupManager.get_data_parallel_world_size() > 1:
+        dist.all_reduce(tokens, group=ProcessGroupManager.get_data_parallel_group())
+    num_experts = probability_mass.shape[-1]
+    balance = num_experts * (F.normalize(probability_mass, p=1, dim=-1) * F.normalize(tokens, p=1, dim=-1)).sum(-1)
+    return (balance + 0.1 * z).to(dtype).sum()  # rounded per layer, as if every layer had added its own term
+
+
 def get_aux_loss() -> torch.Tensor | float:
+    global _AUX_LOSS
+    if _ROUTER_STATISTICS:
+        _AUX_LOSS = _AUX_LOSS + _finish_router_statistics()
     return _AUX_LOSS
 
 

@@ -444,7 +444,8 @@ class MoE_TP(MoE):
             # the auxiliary loss is computed identically on every rank: its gradient must not be summed tp times by
             # the reduce-scatter behind the gathered logits
             aux_logits = _ScaleGradient.apply(logits, 1.0 / tp.tp_world()) if self.sequence_parallel else logits
-            add_aux_loss(self._aux_loss(aux_logits, selected))
+            self._tokens_per_expert = None
+            self._router_statistics(aux_logits, selected)
         return out
 
 

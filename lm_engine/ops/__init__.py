@@ -155,7 +155,8 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight)
+        with site("linear.fwd"):
+            y = gemm(x2, weight)
         if bias is not None:
             y = y + bias
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -169,13 +170,15 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, weight, b_mn=True).view_as(x)
+            with site("linear.dgrad"):
+                dx = gemm(dy2, weight, b_mn=True).view_as(x)
         if ctx.needs_input_grad[1]:
             target = _weight_grad_target(weight)
-            if target is not None:
-                gemm(dy2, x2, target, a_mn=True, b_mn=True, accumulate=True)
-            else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            with site("linear.wgrad"):
+                if target is not None:
+                    gemm(dy2, x2, target, a_mn=True, b_mn=True, accumulate=True)
+                else:
+                    dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db
@@ -193,7 +196,8 @@ class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, eps, residual):
         xc = x.contiguous()
-        outs = native().rmsnorm_fwd(xc, None if residual is None else residual.contiguous(), weight, eps, True)
+        with site("rmsnorm.fwd"):
+            outs = native().rmsnorm_fwd(xc, None if residual is None else residual.contiguous(), weight, eps, True)
         if residual is None:
             y, rstd = outs
             h = xc
@@ -216,7 +220,8 @@ class _RMSNormFn(torch.autograd.Function):
         else:
             buf, acc = torch.empty(weight.numel(), device=weight.device, dtype=torch.float32), False
         dres = None if dh_stream is None else dh_stream.contiguous()
-        dh = native().rmsnorm_bwd(dy.contiguous(), h, weight, rstd, dres, buf, acc)
+        with site("rmsnorm.bwd"):
+            dh = native().rmsnorm_bwd(dy.contiguous(), h, weight, rstd, dres, buf, acc)
         if target is None:
             dw = buf.to(weight.dtype)
         if ctx.has_residual:

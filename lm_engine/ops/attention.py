@@ -13,6 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import native, native_available, note_fallback, status_word
+from .timeline import site
 
 
 def split_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int):
@@ -55,7 +56,8 @@ class _FusedQKVAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, cu_seqlens, max_seqlen, groups, qpg, d, scale, causal):
         C = native()
-        out, lse = C.attn_fwd(qkv, cu_seqlens, int(max_seqlen), groups, qpg, d, float(scale), causal, status_word(qkv.device))
+        with site("attention.fwd"):
+            out, lse = C.attn_fwd(qkv, cu_seqlens, int(max_seqlen), groups, qpg, d, float(scale), causal, status_word(qkv.device))
         ctx.save_for_backward(qkv, out, lse, cu_seqlens)
         ctx.meta = (int(max_seqlen), groups, qpg, d, float(scale), causal)
         return out
@@ -64,7 +66,8 @@ class _FusedQKVAttentionFn(torch.autograd.Function):
     def backward(ctx, dout):
         qkv, out, lse, cu_seqlens = ctx.saved_tensors
         max_seqlen, groups, qpg, d, scale, causal = ctx.meta
-        dqkv = native().attn_bwd(dout.contiguous(), qkv, out, lse, cu_seqlens, max_seqlen, groups, qpg, d, scale, causal, status_word(qkv.device))
+        with site("attention.bwd"):
+            dqkv = native().attn_bwd(dout.contiguous(), qkv, out, lse, cu_seqlens, max_seqlen, groups, qpg, d, scale, causal, status_word(qkv.device))
         return dqkv, None, None, None, None, None, None, None
 
 

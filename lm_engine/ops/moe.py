@@ -18,6 +18,8 @@ from dataclasses import dataclass
 
 import torch
 
+from .timeline import site
+
 from . import _weight_grad_target, native, native_available, status_word
 
 TILE = 128
@@ -145,14 +147,19 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         C = native()
         st = status_word(x.device)
         T, H = x.shape
-        layout = build_grouped_layout(selected_experts.reshape(-1), num_experts)
+        with site("moe.fwd.layout"):
+            layout = build_grouped_layout(selected_experts.reshape(-1), num_experts)
         te = layout.tile_expert  # tiles past the used rows carry num_experts and are skipped by every kernel below
-        xg, fc = gather_then_grouped_rows(C, [x.data_ptr()], layout.src_entry, H, T * top_k, top_k, x, te, num_experts, w_fc, False, st)
-        act = C.swiglu_fwd(fc, te, num_experts)
-        y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
+        with site("moe.fwd.gather+c_fc"):
+            xg, fc = gather_then_grouped_rows(C, [x.data_ptr()], layout.src_entry, H, T * top_k, top_k, x, te, num_experts, w_fc, False, st)
+        with site("moe.fwd.swiglu"):
+            act = C.swiglu_fwd(fc, te, num_experts)
+        with site("moe.fwd.c_proj"):
+            y = C.grouped_rows(act, w_proj, layout.tile_expert, False, st)
         del act
         weights32 = router_weights.reshape(-1).float().contiguous()
-        out = C.moe_combine([y.data_ptr()], layout.dest_row, weights32, T, H, top_k, layout.rows, x)
+        with site("moe.fwd.combine"):
+            out = C.moe_combine([y.data_ptr()], layout.dest_row, weights32, T, H, top_k, layout.rows, x)
         # the gathered rows are kept for the weight gradient of c_fc (one [rows, H] buffer per layer instead of a second gather)
         ctx.save_for_backward(x, w_fc, w_proj, weights32, fc, layout.dest_row, layout.src_entry, layout.tile_expert, layout.padded_offsets, xg)
         ctx.meta = (num_experts, top_k, layout.rows, router_weights.dtype, router_weights.shape)
@@ -169,15 +176,21 @@ class _ScatteredExpertsFn(torch.autograd.Function):
         entries = T * top_k
 
         # dY of the second GEMM without the routing weight, and the activation recomputed from the saved c_fc output
-        dyg, dact = gather_then_grouped_rows(C, [dout.data_ptr()], src_entry, H, entries, top_k, x, tile_expert, num_experts, w_proj, True, st)  # [rows, I] = dyg @ w_proj[e]
-        act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights32, rows, tile_expert, num_experts)
+        with site("moe.bwd.gather+c_proj.dgrad"):
+            dyg, dact = gather_then_grouped_rows(C, [dout.data_ptr()], src_entry, H, entries, top_k, x, tile_expert, num_experts, w_proj, True, st)  # [rows, I] = dyg @ w_proj[e]
+        with site("moe.bwd.swiglu"):
+            act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights32, rows, tile_expert, num_experts)
         del dact
         d_weights = per_entry.view(w_shape).to(w_dtype)
-        g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
+        with site("moe.bwd.c_proj.wgrad"):
+            g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)  # dW2[e] = dyg^T (w * act)
         del dyg, act
-        g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
-        dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)  # [rows, H] = dfc @ w_fc[e]
-        dx = C.moe_combine([dxg.data_ptr()], dest_row, None, T, H, top_k, rows, x)
+        with site("moe.bwd.c_fc.wgrad"):
+            g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
+        with site("moe.bwd.c_fc.dgrad"):
+            dxg = C.grouped_rows(dfc, w_fc, tile_expert, True, st)  # [rows, H] = dfc @ w_fc[e]
+        with site("moe.bwd.combine"):
+            dx = C.moe_combine([dxg.data_ptr()], dest_row, None, T, H, top_k, rows, x)
         return dx, g_fc, g_proj, d_weights, None, None, None
 
 

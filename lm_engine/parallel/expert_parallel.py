@@ -24,6 +24,8 @@ from __future__ import annotations
 import os
 
 import torch
+
+from ..ops.timeline import site
 import torch.distributed as dist
 
 from .. import ops
@@ -216,30 +218,41 @@ class _ExpertParallelFn(torch.autograd.Function):
         local = w_fc.shape[0]
         entries = T * top_k
 
-        selected_all = torch.cat(_all_gather_plain(selected_experts.reshape(-1).to(torch.int32)))
-        exact = _RowCount(selected_all, num_experts, local) if _CAPACITY_FACTOR is None else None
-        # everything that does not depend on the row count is queued before the host waits for it
-        weights_all = torch.cat(_all_gather_plain(router_weights.reshape(-1).float()))
+        with site("ep.fwd.routing_all_gather"):
+            # one collective for the routing table of the whole group: expert ids and the bit patterns of the fp32 weights
+            mine = torch.cat([selected_experts.reshape(-1).to(torch.int32), router_weights.reshape(-1).float().view(torch.int32)])
+            table = torch.empty(world, 2 * entries, dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(table, mine, group=ep_group())
+            selected_all = table[:, :entries].reshape(-1)
+            weights_all = table[:, entries:].reshape(-1).view(torch.float32)
+            exact = _RowCount(selected_all, num_experts, local) if _CAPACITY_FACTOR is None else None
         tokens = ws.buffer("tokens", T * H)
-        peer.barrier()  # the previous users of the buffers are done everywhere
-        tokens.tensor[: T * H].view(T, H).copy_(x)
-        peer.barrier()  # every rank's tokens are readable
-        capacity_rows = exact.value() if exact is not None else _capacity_rows(entries, local)
-        layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
-                                      capacity_rows=capacity_rows)
+        with site("ep.fwd.token_copy+barriers"):
+            peer.barrier()  # the previous users of the buffers are done everywhere
+            tokens.tensor[: T * H].view(T, H).copy_(x)
+            peer.barrier()  # every rank's tokens are readable
+        with site("ep.fwd.row_count_wait+layout"):
+            capacity_rows = exact.value() if exact is not None else _capacity_rows(entries, local)
+            layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
+                                          capacity_rows=capacity_rows)
         _count_dropped(layout)
         rows = layout.rows
         out_rows = ws.buffer("rows", rows * H)
         te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
         # dispatch: rows are pulled from their owners by gather CTAs inside the c_fc GEMM kernel
-        xg, fc = gather_then_grouped_rows(C, tokens.ptrs, layout.src_entry, H, entries, top_k, x, te, local, w_fc, False, st, copy_ctas=_GATHER_CTAS)
-        act = C.swiglu_fwd(fc, te, local)
-        C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
+        with site("ep.fwd.dispatch+c_fc"):
+            xg, fc = gather_then_grouped_rows(C, tokens.ptrs, layout.src_entry, H, entries, top_k, x, te, local, w_fc, False, st, copy_ctas=_GATHER_CTAS)
+        with site("ep.fwd.swiglu"):
+            act = C.swiglu_fwd(fc, te, local)
+        with site("ep.fwd.c_proj"):
+            C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
         del act
-        global_row = _exchange_rows(layout.dest_row, entries, rows)
-        peer.barrier()  # every rank's expert outputs are readable
+        with site("ep.fwd.row_exchange+barrier"):
+            global_row = _exchange_rows(layout.dest_row, entries, rows)
+            peer.barrier()  # every rank's expert outputs are readable
         weights32 = router_weights.reshape(-1).float().contiguous()
-        out = C.moe_combine(out_rows.ptrs, global_row, weights32, T, H, top_k, rows, x)  # combine: pull the k results per token
+        with site("ep.fwd.combine"):
+            out = C.moe_combine(out_rows.ptrs, global_row, weights32, T, H, top_k, rows, x)  # combine: pull the k results per token
 
         # the gathered rows are kept for the weight gradient: pulling them from the peers a second time costs more than the memory
         ctx.save_for_backward(x, w_fc, w_proj, weights_all, fc, layout.dest_row, layout.src_entry, layout.tile_expert,
@@ -260,23 +273,31 @@ class _ExpertParallelFn(torch.autograd.Function):
         tokens = ws.buffer("tokens", T * H)
         out_rows = ws.buffer("rows", rows * H)
 
-        peer.barrier()
-        tokens.tensor[: T * H].view(T, H).copy_(dout)
-        peer.barrier()
+        with site("ep.bwd.token_copy+barriers"):
+            peer.barrier()
+            tokens.tensor[: T * H].view(T, H).copy_(dout)
+            peer.barrier()
         local = w_fc.shape[0]
         # output gradients of the rows computed here, pulled inside the GEMM kernel as in the forward pass
-        dyg, dact = gather_then_grouped_rows(C, tokens.ptrs, src_entry, H, entries, top_k, x, tile_expert, local, w_proj, True, st, copy_ctas=_GATHER_CTAS)
+        with site("ep.bwd.dispatch+c_proj.dgrad"):
+            dyg, dact = gather_then_grouped_rows(C, tokens.ptrs, src_entry, H, entries, top_k, x, tile_expert, local, w_proj, True, st, copy_ctas=_GATHER_CTAS)
         # gradient of the routing weight of every entry served here (0 elsewhere), sent back to the token owners
-        act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights_all, rows, tile_expert, local)
+        with site("ep.bwd.swiglu"):
+            act, dfc, per_entry = weighted_swiglu_backward(C, fc, dact, dest_row, weights_all, rows, tile_expert, local)
         del dact
-        d_weights = _exchange_values(per_entry, entries).view(w_shape).to(w_dtype)
-        g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
+        with site("ep.bwd.routing_gradient_exchange"):
+            d_weights = _exchange_values(per_entry, entries).view(w_shape).to(w_dtype)
+        with site("ep.bwd.c_proj.wgrad"):
+            g_proj = _wgrad(C, dyg, act, w_proj, padded_offsets, st)
         del dyg, act
 
-        g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
-        C.grouped_rows(dfc, w_fc, tile_expert, True, st, out_rows.tensor[: rows * H].view(rows, H))
-        peer.barrier()
-        dx = C.moe_combine(out_rows.ptrs, global_row, None, T, H, top_k, rows, x)
+        with site("ep.bwd.c_fc.wgrad"):
+            g_fc = _wgrad(C, dfc, xg, w_fc, padded_offsets, st)
+        with site("ep.bwd.c_fc.dgrad"):
+            C.grouped_rows(dfc, w_fc, tile_expert, True, st, out_rows.tensor[: rows * H].view(rows, H))
+        with site("ep.bwd.barrier+combine"):
+            peer.barrier()
+            dx = C.moe_combine(out_rows.ptrs, global_row, None, T, H, top_k, rows, x)
         return dx, g_fc, g_proj, d_weights, None, None, None
 
 
