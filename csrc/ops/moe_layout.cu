@@ -178,8 +178,148 @@ std::vector<Tensor> moe_layout(const Tensor& expert_of_entry, int64_t first_expe
   return {dest_row, src_entry, tile_expert, padded_offsets, dropped};
 }
 
+
+// ---- the same layout for a whole expert-parallel group -------------------------------------------------------------------
+// Every rank of an expert-parallel group holds the routing table of the whole group, so it can work out where EVERY entry
+// lands on its owner (the rank whose experts include the entry's expert) without asking: one counting sort over all
+// experts whose row offsets restart at each owner's first expert. That gives this rank its own layout (as above) and, for
+// the combine, the (owner, row) of every entry, which used to take an all-to-all per layer.
+
+// counts[block][expert] -> first row of that (block, expert) pair on the expert's owner; this rank's padded_offsets and
+// tile_expert. One block.
+__global__ void layout_scan_group_kernel(int* __restrict__ counts, int blocks, int num_experts, int per_owner, int my_owner, int rows,
+                                         int* __restrict__ padded_offsets, int* __restrict__ tile_expert) {
+  __shared__ int total[kMaxLocal];
+  __shared__ int start[kMaxLocal + 1];  // start[e]: first row of expert e on its owner
+  __shared__ int mine[kMaxLocal + 1];   // this rank's experts: first rows, then the end of the last one
+  for (int e = threadIdx.x; e < num_experts; e += kThreads) {
+    int run = 0;
+    for (int b = 0; b < blocks; ++b) {
+      const int c = counts[(size_t)b * num_experts + e];
+      counts[(size_t)b * num_experts + e] = run;
+      run += c;
+    }
+    total[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      if (e % per_owner == 0) at = 0;
+      start[e] = min(at, rows);  // under a capacity bound the ranges past the end of the buffer are empty
+      at += (total[e] + kTile - 1) / kTile * kTile;
+      if (e / per_owner == my_owner) {
+        mine[e % per_owner] = start[e];
+        mine[e % per_owner + 1] = min(at, rows);
+      }
+    }
+  }
+  __syncthreads();
+  for (int l = threadIdx.x; l <= per_owner; l += kThreads) padded_offsets[l] = mine[l];
+  for (int e = threadIdx.x; e < num_experts; e += kThreads) {
+    for (int b = 0; b < blocks; ++b) counts[(size_t)b * num_experts + e] += start[e];
+  }
+  for (int t = threadIdx.x; t < rows / kTile; t += kThreads) {
+    const int row = t * kTile;
+    int lo = 0, hi = per_owner;  // first local expert whose end is beyond `row`
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (mine[mid + 1] > row) hi = mid; else lo = mid + 1;
+    }
+    tile_expert[t] = lo;
+  }
+}
+
+// stable placement over all experts: dest_row / src_entry for this rank's experts, owner * rows + row for every entry
+__global__ void layout_place_group_kernel(const int* __restrict__ expert_of_entry, int entries, int num_experts, int per_owner, int my_owner,
+                                          const int* __restrict__ base_rows, int rows, int* __restrict__ dest_row, int* __restrict__ src_entry,
+                                          int* __restrict__ global_row, int* __restrict__ dropped) {
+  __shared__ int wcount[kWarps][kMaxLocal];  // entries per (warp, expert), then running offsets
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kWarps * kMaxLocal; i += kThreads) (&wcount[0][0])[i] = 0;
+  __syncthreads();
+  const int warp_base = blockIdx.x * kChunk + warp * kPerWarp;
+  int key[kPerWarp / 32];
+#pragma unroll
+  for (int s = 0; s < kPerWarp / 32; ++s) {
+    const int idx = warp_base + s * 32 + lane;
+    key[s] = idx < entries ? local_expert(expert_of_entry[idx], 0, num_experts) : -1;
+    if (key[s] >= 0) atomicAdd(&wcount[warp][key[s]], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += kThreads) {
+    int run = base_rows[(size_t)blockIdx.x * num_experts + e];
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = wcount[w][e];
+      wcount[w][e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  int lost = 0;
+#pragma unroll
+  for (int s = 0; s < kPerWarp / 32; ++s) {
+    const int idx = warp_base + s * 32 + lane;
+    const int k = key[s];
+    const unsigned peers = __match_any_sync(0xffffffffu, k);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int owner = k >= 0 ? k / per_owner : -1;
+    int row = -1;
+    if (k >= 0) {
+      row = wcount[warp][k] + rank;
+      if (row >= rows) {
+        row = -1;
+        if (owner == my_owner) ++lost;
+      }
+    }
+    __syncwarp();
+    if (k >= 0 && rank == 0) wcount[warp][k] += __popc(peers);
+    __syncwarp();
+    if (idx < entries) {
+      const bool here = owner == my_owner && row >= 0;
+      dest_row[idx] = here ? row : -1;
+      if (here) src_entry[row] = idx;
+      global_row[idx] = row >= 0 ? owner * rows + row : -1;
+    }
+  }
+  if (lost > 0) atomicAdd(dropped, lost);
+}
+
+// -> (dest_row [entries], src_entry [rows], tile_expert [rows / 128], padded_offsets [per_owner + 1], dropped [1], global_row [entries])
+std::vector<Tensor> moe_layout_group(const Tensor& expert_of_entry, int64_t num_experts, int64_t per_owner, int64_t my_owner, int64_t rows) {
+  TORCH_CHECK(expert_of_entry.is_cuda() && expert_of_entry.scalar_type() == torch::kInt32 && expert_of_entry.is_contiguous(), "expert_of_entry: int32");
+  TORCH_CHECK(num_experts >= 1 && num_experts <= kMaxLocal && per_owner >= 1 && num_experts % per_owner == 0, "between 1 and 256 experts, evenly split over the owners");
+  TORCH_CHECK(my_owner >= 0 && my_owner < num_experts / per_owner, "owner index out of range");
+  TORCH_CHECK(rows > 0 && rows % kTile == 0, "rows must be a positive multiple of 128");
+  const c10::cuda::CUDAGuard guard(expert_of_entry.device());
+  const int64_t entries = expert_of_entry.numel();
+  auto opts = expert_of_entry.options();
+  Tensor dest_row = torch::empty({entries}, opts);
+  Tensor global_row = torch::empty({entries}, opts);
+  Tensor src_entry = torch::empty({rows}, opts);
+  Tensor tile_expert = torch::empty({rows / kTile}, opts);
+  Tensor padded_offsets = torch::empty({per_owner + 1}, opts);
+  Tensor dropped = torch::zeros({1}, opts);
+  const int blocks = (int)std::max<int64_t>(1, (entries + kChunk - 1) / kChunk);
+  Tensor counts = torch::empty({blocks, num_experts}, opts);
+  cudaStream_t stream = cur_stream();
+  check_cuda(cudaMemsetAsync(src_entry.data_ptr(), 0xFF, (size_t)rows * sizeof(int), stream), "src_entry memset");
+  layout_count_kernel<<<blocks, kThreads, 0, stream>>>(expert_of_entry.data_ptr<int>(), (int)entries, 0, (int)num_experts, counts.data_ptr<int>());
+  layout_scan_group_kernel<<<1, kThreads, 0, stream>>>(counts.data_ptr<int>(), blocks, (int)num_experts, (int)per_owner, (int)my_owner, (int)rows,
+                                                       padded_offsets.data_ptr<int>(), tile_expert.data_ptr<int>());
+  layout_place_group_kernel<<<blocks, kThreads, 0, stream>>>(expert_of_entry.data_ptr<int>(), (int)entries, (int)num_experts, (int)per_owner,
+                                                             (int)my_owner, counts.data_ptr<int>(), (int)rows, dest_row.data_ptr<int>(),
+                                                             src_entry.data_ptr<int>(), global_row.data_ptr<int>(), dropped.data_ptr<int>());
+  count_launch(3);
+  check_cuda(cudaGetLastError(), "moe_layout_group launch");
+  return {dest_row, src_entry, tile_expert, padded_offsets, dropped, global_row};
+}
+
 }  // namespace
 
-void register_moe_layout(py::module_& m) { m.def("moe_layout", &moe_layout); }
+void register_moe_layout(py::module_& m) {
+  m.def("moe_layout", &moe_layout);
+  m.def("moe_layout_group", &moe_layout_group);
+}
 
 }  // namespace b200

@@ -95,6 +95,26 @@ def build_grouped_layout(expert_of_entry: torch.Tensor, num_experts: int, first_
     return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows, dropped)
 
 
+def build_group_layout(expert_of_entry: torch.Tensor, num_experts: int, experts_per_owner: int, owner: int,
+                       capacity_rows: int | None = None) -> tuple[GroupedLayout, torch.Tensor | None]:
+    """`build_grouped_layout` for rank ``owner`` of an expert-parallel group whose ranks each own ``experts_per_owner``
+    consecutive experts, plus, for EVERY entry of the routing table, the row it gets on its own owner as
+    ``owner * rows + row`` (-1 if dropped there). Every rank holds the same table and the same ``rows``, so every rank
+    arrives at the same numbers and nothing has to be exchanged. Without the kernel the second value is ``None``."""
+    entries = expert_of_entry.numel()
+    rows = worst_case_rows(entries, experts_per_owner)
+    if capacity_rows is not None:
+        rows = min(rows, max(TILE, (capacity_rows + TILE - 1) // TILE * TILE))
+    if expert_of_entry.is_cuda and num_experts <= 256 and native_available() and hasattr(native(), "moe_layout_group"):
+        flat = expert_of_entry.reshape(-1).to(torch.int32).contiguous()
+        dest_row, src_entry, tile_expert, padded_offsets, dropped, global_row = native().moe_layout_group(
+            flat, num_experts, experts_per_owner, owner, rows)
+        return GroupedLayout(dest_row, src_entry, tile_expert, padded_offsets, rows, dropped), global_row
+    layout = build_grouped_layout(expert_of_entry, num_experts, first_expert=owner * experts_per_owner,
+                                  num_local_experts=experts_per_owner, capacity_rows=capacity_rows)
+    return layout, None
+
+
 def native_moe_ok(x: torch.Tensor, activation_function: str) -> bool:
     return (native_available() and x.is_cuda and x.dtype == torch.bfloat16 and activation_function == "swiglu"
             and x.shape[-1] % 8 == 0 and hasattr(native(), "grouped_rows"))

@@ -29,7 +29,7 @@ from ..ops.timeline import site
 import torch.distributed as dist
 
 from .. import ops
-from ..ops.moe import TILE, _wgrad, build_grouped_layout, gather_then_grouped_rows, weighted_swiglu_backward
+from ..ops.moe import TILE, _wgrad, build_group_layout, build_grouped_layout, gather_then_grouped_rows, weighted_swiglu_backward, worst_case_rows
 from ..utils import ProcessGroupManager
 from .symmetric import PeerBuffer, PeerGroup, get_peer_group
 
@@ -233,11 +233,12 @@ class _ExpertParallelFn(torch.autograd.Function):
             peer.barrier()  # every rank's tokens are readable
         with site("ep.fwd.row_count_wait+layout"):
             capacity_rows = exact.value() if exact is not None else _capacity_rows(entries, local)
-            layout = build_grouped_layout(selected_all, num_experts, first_expert=rank * local, num_local_experts=local,
-                                          capacity_rows=capacity_rows)
+            layout, global_rows = build_group_layout(selected_all, num_experts, local, rank, capacity_rows)
         _count_dropped(layout)
         rows = layout.rows
-        out_rows = ws.buffer("rows", rows * H)
+        # the shared row buffer is sized for the worst case once: with exact sizing `rows` changes with every batch, and
+        # growing a symmetric allocation in the middle of a run is a rendezvous of the whole group
+        out_rows = ws.buffer("rows", worst_case_rows(world * entries, local) * H)
         te = layout.tile_expert  # tiles past the used rows carry `local` and are skipped by every kernel below
         # dispatch: rows are pulled from their owners by gather CTAs inside the c_fc GEMM kernel
         with site("ep.fwd.dispatch+c_fc"):
@@ -248,7 +249,10 @@ class _ExpertParallelFn(torch.autograd.Function):
             C.grouped_rows(act, w_proj, layout.tile_expert, False, st, out_rows.tensor[: rows * H].view(rows, H))  # straight into symmetric memory
         del act
         with site("ep.fwd.row_exchange+barrier"):
-            global_row = _exchange_rows(layout.dest_row, entries, rows)
+            if global_rows is not None:  # worked out locally from the routing table of the whole group
+                global_row = global_rows[rank * entries : (rank + 1) * entries].contiguous()
+            else:
+                global_row = _exchange_rows(layout.dest_row, entries, rows)
             peer.barrier()  # every rank's expert outputs are readable
         weights32 = router_weights.reshape(-1).float().contiguous()
         with site("ep.fwd.combine"):
@@ -271,7 +275,7 @@ class _ExpertParallelFn(torch.autograd.Function):
         T, H = x.shape
         entries = T * top_k
         tokens = ws.buffer("tokens", T * H)
-        out_rows = ws.buffer("rows", rows * H)
+        out_rows = ws.buffer("rows", rows * H)  # the forward pass made it large enough for any batch
 
         with site("ep.bwd.token_copy+barriers"):
             peer.barrier()

@@ -688,3 +688,36 @@ def test_ssd_scan_matches_the_chunked_formulation(heads, groups, head_dim, state
     ref = [y_ref.detach(), final_ref.detach(), x.grad, a.grad, b.grad, c.grad, h0.grad]
     for name, g, r in zip(("y", "final", "dx", "da", "db", "dc", "dh0"), got, ref):
         assert _rel_err(g, r) < 2e-4, (name, _rel_err(g, r))
+
+
+@pytest.mark.parametrize("world,per_owner,capacity", [(2, 20, None), (4, 10, None), (8, 5, None), (4, 10, 0.5)])
+def test_group_layout_equals_every_owners_own_layout(C, world, per_owner, capacity):
+    """The layout a rank works out for the whole expert-parallel group from the shared routing table: its own part equals
+    the single-rank layout bit for bit, and the (owner, row) it predicts for every entry is the row that owner's own
+    layout gives the entry (-1 where the owner has to drop it)."""
+    from lm_engine.ops.moe import build_group_layout, build_grouped_layout
+
+    torch.manual_seed(7)
+    num_experts = world * per_owner
+    entries = 4096 * 8
+    # skewed routing: some experts get far more than their share
+    weights = torch.rand(num_experts, device="cuda") ** 3
+    expert_of_entry = torch.multinomial(weights, entries, replacement=True).to(torch.int32)
+    capacity_rows = None if capacity is None else int(capacity * entries / world)
+    own = [build_grouped_layout(expert_of_entry, num_experts, first_expert=o * per_owner, num_local_experts=per_owner,
+                                capacity_rows=capacity_rows) for o in range(world)]
+    rows = own[0].rows
+    owner_of_entry = (expert_of_entry // per_owner).long()
+    expected = torch.stack([l.dest_row for l in own]).gather(0, owner_of_entry.unsqueeze(0)).squeeze(0)
+    expected = torch.where(expected >= 0, owner_of_entry.to(torch.int32) * rows + expected, torch.full_like(expected, -1))
+    for o in range(world):
+        layout, global_row = build_group_layout(expert_of_entry, num_experts, per_owner, o, capacity_rows)
+        assert layout.rows == rows
+        assert torch.equal(layout.dest_row, own[o].dest_row)
+        assert torch.equal(layout.src_entry, own[o].src_entry)
+        assert torch.equal(layout.tile_expert, own[o].tile_expert)
+        assert torch.equal(layout.padded_offsets, own[o].padded_offsets)
+        assert torch.equal(layout.dropped, own[o].dropped)
+        assert torch.equal(global_row, expected)
+    if capacity is not None:
+        assert int(sum(l.dropped for l in own).item()) > 0, "the capacity case is meant to drop entries"
