@@ -274,10 +274,15 @@ def run_native(cli) -> dict:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             last = None
+            walls = []
+            wall0 = time.perf_counter()
             for _ in range(cli.steps):
                 metrics = step(feed)
                 if read_back:
                     last = loss_of(metrics)  # device -> host read of the step result
+                    wall1 = time.perf_counter()  # the read-back has synchronised: this is the step's wall time
+                    walls.append(round((wall1 - wall0) * 1e3, 1))
+                    wall0 = wall1
             end.record()
             torch.cuda.synchronize()
             if world > 1:
@@ -287,7 +292,7 @@ def run_native(cli) -> dict:
             t = torch.tensor([ms], dtype=torch.float64, device=device)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return t.item(), ops.launch_count() - launches0, clocks, last
+            return t.item(), ops.launch_count() - launches0, clocks, (last, walls) if read_back else last
 
         feed_device = Feed(pool_device)
         for _ in range(cli.warmup):
@@ -298,10 +303,11 @@ def run_native(cli) -> dict:
         ms, launches, clocks, _ = timed(feed_device, read_back=False)
         e2e = None
         if not cli.skip_e2e:
-            ms_e2e, _, _, last_loss = timed(Feed(pool), read_back=True)
+            ms_e2e, _, _, (last_loss, step_walls) = timed(Feed(pool), read_back=True)
             tokens = cli.steps * ga * mb * seq * (world // (pp * tp_size))
             e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / cli.steps,
-                   "h2d_bytes_per_step": ga * mb * (seq + 1) * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss}
+                   "h2d_bytes_per_step": ga * mb * (seq + 1) * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss,
+                   "wall_ms_of_each_step": step_walls}
         ops.check_status()
 
         if cli.budget_output is not None:

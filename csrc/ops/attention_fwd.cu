@@ -8,8 +8,9 @@
 //   warp 0      TMA producer: Q once, then K tiles and V tiles of 128 keys through two separate 2-stage rings
 //   warp 1      MMA issuer : S = Q K^T into one of two TMEM buffers, O += P V into a third
 //   warps 2..9  256 softmax threads, two per query row (TMEM lane), each owning half of the key columns: online softmax with lazy
-//               rescaling of O (only when the running maximum grew by more than 2^8), P written as bf16
-//               into 128B-swizzled shared memory where the second MMA reads it, final O / l and lse
+//               rescaling of O (only when the running maximum grew by more than 2^8), P written as bf16 over
+//               the S columns of tensor memory it was computed from (the second MMA reads its A operand there,
+//               so P never visits shared memory), final O / l and lse
 // All waits are bounded; a timeout raises the status word and the CTA unwinds.
 #include "../common/launch.h"
 #include "../common/ptx.cuh"
@@ -32,18 +33,16 @@ struct FwdSmem {
   static constexpr int Q_BYTES = BLOCK_M * D * 2;
   static constexpr int K_BYTES = BLOCK_N * D * 2;
   static constexpr int V_BYTES = BLOCK_N * D * 2;
-  static constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * K_BYTES;
-  static constexpr int OFF_P = OFF_V + KV_STAGES * V_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
   static constexpr int OFF_X = OFF_BAR + 256;  // row statistics exchanged between the two threads of a row: [2][2][128] floats
   static constexpr int TOTAL = OFF_X + 2 * 2 * BLOCK_M * 4 + 1024;
 };
 
 // barrier indices
-enum { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_S_EMPTY = 11, B_P_READY = 13, B_PV_DONE = 14, B_COUNT = 15 };
+enum { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_P_READY = 11, B_PV_DONE = 12, B_COUNT = 13 };
 
 template <int D>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -56,7 +55,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
-  uint8_t* sP = smem + L::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -97,7 +95,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&bars[B_V_FULL + s], 1);
       mbar_init(&bars[B_V_EMPTY + s], 1);
       mbar_init(&bars[B_S_FULL + s], 1);
-      mbar_init(&bars[B_S_EMPTY + s], SOFTMAX_WARPS * 32);
     }
     mbar_init(&bars[B_P_READY], SOFTMAX_WARPS * 32);
     mbar_init(&bars[B_PV_DONE], 1);
@@ -163,13 +160,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       constexpr uint32_t idesc_s = umma_idesc_bf16(BLOCK_M, BLOCK_N, 0, 0);  // S = Q K^T, both K-major
       constexpr uint32_t idesc_o = umma_idesc_bf16(BLOCK_M, D, 0, 1);        // O = P V, V is MN-major
       const uint32_t q_base = smem_u32(sQ);
-      const uint32_t p_base = smem_u32(sP);
       bool ok = mbar_wait(&bars[B_Q], 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
         const int st = j % KV_STAGES;
         if (!mbar_wait(&bars[B_K_FULL + st], (j / KV_STAGES) & 1, abort_flag)) return false;
-        if (!mbar_wait(&bars[B_S_EMPTY + st], ((j / 2) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
+        // No wait for the S buffer: it last held S(j-2) and then P(j-2), which O += P V(j-2) has read; that product was
+        // issued by this thread before this one (and only after the softmax threads had finished with S(j-2)), and the
+        // tensor cores retire in order.
         const uint32_t k_base = smem_u32(sK + st * L::K_BYTES);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -198,9 +196,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const uint32_t v_base = smem_u32(sV + st * L::V_BYTES);
 #pragma unroll
         for (int k = 0; k < BLOCK_N / 16; ++k) {
-          const uint64_t da = umma_smem_desc_sw128(p_base + (k / 4) * (BLOCK_M * 128) + (k % 4) * 32, 16, 1024);
+          // 16 keys per step; the bf16 P of keys [64 h, 64 h + 64) sits in the first 32 of this tile's S columns [64 h, 64 h + 64)
           const uint64_t db = umma_smem_desc_sw128(v_base + k * 16 * 128, BLOCK_N * 128, 1024);
-          umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);
+          umma_f16_ts(tmem_O, tmem_S0 + st * BLOCK_N + (k / 4) * 64 + (k % 4) * 8, db, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&bars[B_V_EMPTY + st]);
         umma_commit(&bars[B_PV_DONE]);
@@ -228,8 +226,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < HALF_N / 32; ++c) B200_TMEM_LD_32((s + c * 32), tmem_S0 + lane_addr + st * BLOCK_N + half * HALF_N + c * 32);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[B_S_EMPTY + st]);
 
       const int kv0 = j * BLOCK_N + half * HALF_N;
       const bool needs_mask = (j * BLOCK_N + BLOCK_N > doc_len) || (causal && j * BLOCK_N + BLOCK_N - 1 > q0);
@@ -283,36 +279,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const float row_sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       l_sum = l_sum * alpha + row_sum;
 
-      if (j > 0) {
-        // P buffer free again and O stable: PV of the previous tile retired
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+        // O must be stable: PV of the previous tile retired
         if (!mbar_wait(&bars[B_PV_DONE], (j - 1) & 1, abort_flag)) {
           failed = true;
           *abort_flag = 1;
           continue;
         }
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-          for (int cc = 0; cc < D / 64; ++cc) {
-            const int c = half * (D / 64) + cc;
-            uint32_t o[32];
-            B200_TMEM_LD_32(o, tmem_O + lane_addr + c * 32);
-            tmem_ld_wait();
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;
+          uint32_t o[32];
+          B200_TMEM_LD_32(o, tmem_O + lane_addr + c * 32);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            B200_TMEM_ST_32(tmem_O + lane_addr + c * 32, o);
-          }
-          tmem_st_wait();
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          B200_TMEM_ST_32(tmem_O + lane_addr + c * 32, o);
         }
       }
-      // P (bf16) -> shared memory, K-major with the 128-byte swizzle the MMA expects; this thread's 64 keys = one K block
-      {
-        uint8_t* row_base = sP + half * (BLOCK_M * 128) + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-          *reinterpret_cast<uint4*>(row_base + ((ch ^ (r & 7)) * 16)) = make_uint4(p[ch * 4], p[ch * 4 + 1], p[ch * 4 + 2], p[ch * 4 + 3]);
-      }
-      fence_proxy_async_smem();
+      // P (bf16 pairs) over the first 32 of the 64 S columns this thread has read: the A operand of the second product
+      B200_TMEM_ST_32(tmem_S0 + lane_addr + st * BLOCK_N + half * HALF_N, p);
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[B_P_READY]);
     }
