@@ -38,7 +38,11 @@ _WORKSPACES: dict[int, "_Workspace"] = {}
 # Sizing of the per-rank row buffers (expert inputs, projections, outputs):
 #   None (default)  exact and dropless: every rank derives, from the routing table it already holds for the whole group,
 #                   the tile-padded row count of the fullest rank and reads it back (one small device-to-host read per
-#                   MoE layer and forward pass); buffers then hold what the busiest rank needs, nothing is ever dropped
+#                   MoE layer and forward pass); buffers then hold what the busiest rank needs, nothing is ever dropped.
+#                   The size actually used is the largest need seen so far in the run (all layers share it), rounded up
+#                   to `_ROW_QUANTUM`: a buffer size that changed with every batch and layer kept the caching allocator
+#                   mapping new memory in the middle of the run (stalls of about a second at 4 GPUs), a size that only
+#                   ever grows settles after a few steps
 #   a factor >= 1   static bound without a host read: ``factor x (a rank's balanced share of the routed entries)`` rows
 #                   (plus tile padding); entries beyond it are dropped (they contribute nothing to their token) and
 #                   counted on the device in ``_DROPPED``
@@ -46,6 +50,8 @@ _CAPACITY_FACTOR: float | None = None
 # CTAs of the fused dispatch + GEMM kernel that pull rows from the peers (each keeps about 190 KB in flight)
 _GATHER_CTAS = int(os.environ.get("LM_ENGINE_MOE_GATHER_CTAS", "32"))
 _DROPPED: dict[torch.device, torch.Tensor] = {}
+_ROW_QUANTUM = 2048
+_ROW_HIGH_WATER: dict[tuple, int] = {}  # (device, routed entries of the group, local experts) -> rows
 
 
 def set_expert_capacity_factor(factor: float | None) -> None:
@@ -232,7 +238,12 @@ class _ExpertParallelFn(torch.autograd.Function):
             tokens.tensor[: T * H].view(T, H).copy_(x)
             peer.barrier()  # every rank's tokens are readable
         with site("ep.fwd.row_count_wait+layout"):
-            capacity_rows = exact.value() if exact is not None else _capacity_rows(entries, local)
+            if exact is not None:
+                need = (exact.value() + _ROW_QUANTUM - 1) // _ROW_QUANTUM * _ROW_QUANTUM
+                key = (x.device, world * entries, local)  # the same on every rank, like the count itself
+                capacity_rows = _ROW_HIGH_WATER[key] = max(_ROW_HIGH_WATER.get(key, 0), need)
+            else:
+                capacity_rows = _capacity_rows(entries, local)
             layout, global_rows = build_group_layout(selected_all, num_experts, local, rank, capacity_rows)
         _count_dropped(layout)
         rows = layout.rows
