@@ -196,6 +196,8 @@ class ZeroTopologyArgs(BaseArgs):
 class DistributedArgs(BaseArgs):
     # ZeRO stage: 0 (replicate), 2 (shard grads + optimizer), 3 (shard params too)
     stage: int = 3
+    # fp32 master shards, optimizer state and a staging copy of the gradient shard in pinned host memory; the optimizer
+    # step runs on the CPU (12 bytes per parameter / N leave the device, at the price of two PCIe transfers per step)
     cpu_offload: bool = False
     gradient_checkpointing_method: GradientCheckpointingMethod | None = None
     gradient_checkpointing_args: dict = {}

@@ -193,7 +193,7 @@ def _scatter_unit_quantity(unit, full: torch.Tensor, source: str, optimizer) -> 
     lo, _ = unit.shard_range
     for seg in unit.segments:
         state = optimizer.state.setdefault(seg.master, {})
-        piece = full[lo + seg.start : lo + seg.start + seg.numel]
+        piece = full[lo + seg.start : lo + seg.start + seg.numel].to(seg.master.device)  # the host under cpu_offload
         if source not in state:
             state[source] = piece.clone()
         else:

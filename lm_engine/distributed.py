@@ -46,8 +46,6 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
     comm_dtype = None if dist_args.communication_dtype is None else string_to_torch_dtype(dist_args.communication_dtype)
     if dist_args.stage not in (0, 2, 3):
         raise ValueError(f"unexpected ZeRO stage ({dist_args.stage})")
-    if dist_args.cpu_offload:
-        log_rank_0(logging.WARN, "cpu_offload is ignored: optimizer state shards stay in device memory")
 
     device = ProcessGroupManager.get_device()
     group_of = get_group_function(args.optimizer_args.params_group_method)
@@ -68,6 +66,7 @@ def wrap_model_container_for_distributed_training(args, model_container: ModelCo
         engine = ShardedTrainingEngine(
             wrapper,
             resident_parameters=_keep_parameters_gathered(dist_args, wrapper, dtype),
+            cpu_offload=dist_args.cpu_offload,
             compute_dtype=dtype,
             zero_stage=dist_args.stage,
             device=device,

@@ -71,12 +71,16 @@ class Segment:
 class FlatUnit:
     def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], group_of: Callable[[str, nn.Parameter], str],
                  group_order: list[str], shard_world: int, shard_rank: int, compute_dtype: torch.dtype,
-                 device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None, resident: bool = True) -> None:
+                 device: torch.device, storage: Callable[[int, torch.dtype], torch.Tensor] | None = None, resident: bool = True,
+                 offload: bool = False) -> None:
         self.name = name
         self.local_only = False  # True: this rank's own parameters (expert parallelism), no collective touches them
         # False: only this rank's shard of the compute copy and of the gradients is kept; the full buffers exist while
         # the unit's forward / backward pass runs (see ShardedTrainingEngine.gather_unit / release_unit)
         self.resident = resident
+        # True: the fp32 master shard (and with it the optimizer's moments) and a staging copy of the gradient shard live in
+        # pinned host memory; the optimizer runs on the CPU and its result is copied into the device's compute shard
+        self.offload = offload
         self.module = None
         self.world = shard_world
         self.rank = shard_rank
@@ -99,21 +103,30 @@ class FlatUnit:
         lo = self.rank * self.shard_numel
         self.shard_range = (lo, lo + self.shard_numel)
 
-        aliased = compute_dtype == torch.float32
+        aliased = compute_dtype == torch.float32 and not offload
         new = storage if storage is not None else (lambda n, dtype: torch.zeros(n, dtype=dtype, device=device))
+
+        def host(n: int) -> torch.Tensor:
+            t = torch.zeros(n, dtype=torch.float32)
+            return t.pin_memory() if device.type == "cuda" else t
+
         if resident:
             self.compute = new(self.numel, compute_dtype)
             # fp32 training keeps no separate master: the shard region of the compute buffer is the master
-            self.master = self.compute[lo : lo + self.shard_numel] if aliased else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            if offload:
+                self.master = host(self.shard_numel)
+            else:
+                self.master = self.compute[lo : lo + self.shard_numel] if aliased else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
             self.compute_shard = self.compute[lo : lo + self.shard_numel]
             self.grad = new(self.numel, torch.float32)
             self.grad_shard = self.grad[lo : lo + self.shard_numel]
         else:
             self.compute = None  # gathered on demand
-            self.master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.master = host(self.shard_numel) if offload else torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
             self.compute_shard = self.master if aliased else torch.zeros(self.shard_numel, dtype=compute_dtype, device=device)
             self.grad = None  # full-size only during the unit's backward pass
             self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+        self.grad_host = host(self.shard_numel) if offload else None
         self.master_is_alias = aliased
 
         self.segments: list[Segment] = []
@@ -123,7 +136,7 @@ class FlatUnit:
                 continue
             seg = Segment(self, g, s0 - lo, s1 - s0)
             seg.master = nn.Parameter(self.master[seg.start : seg.start + seg.numel], requires_grad=True)
-            seg.master.grad = self.grad_shard[seg.start : seg.start + seg.numel]
+            seg.master.grad = (self.grad_host if offload else self.grad_shard)[seg.start : seg.start + seg.numel]
             seg.compute = None if aliased else self.compute_shard[s0 - lo : s1 - lo]
             seg.master._lm_engine_segment = seg
             self.segments.append(seg)
@@ -173,7 +186,7 @@ class FlatUnit:
         if self.master_is_alias and self.resident:
             return self.compute[slot.offset : slot.offset + slot.numel].view(slot.shape).float().clone()
         if self.world == 1:
-            full = self.master
+            full = self.master.to(self.device)
         else:
             full = torch.empty(self.numel, dtype=torch.float32, device=self.device)
             full[self.shard_range[0] : self.shard_range[1]].copy_(self.master)
@@ -198,8 +211,12 @@ class ShardedTrainingEngine:
         frozen_prefixes: tuple[str, ...] = (),
         sequence_parallel: bool = False,
         resident_parameters: bool = True,
+        cpu_offload: bool = False,
     ) -> None:
         self.model = model
+        # True: fp32 master shards and optimizer state in pinned host memory, optimizer step on the CPU (what the reference
+        # gets from FSDP's CPUOffloadPolicy, lm_engine/distributed.py:225 there): 12 bytes per parameter / N leave the device
+        self.cpu_offload = cpu_offload
         # False: the parameters of every block exist in full only while that block runs (ZeRO-3 as the reference's
         # `reshard_after_forward`): per block an all-gather before its forward and before its backward pass and a
         # reduce-scatter of its gradients after its backward pass; between those only the 1 / N shards are held
@@ -287,20 +304,21 @@ class ShardedTrainingEngine:
         materialised: set[int] = set()
         for unit_name, module, params, local_only in split_plan:
             if local_only:
-                unit = FlatUnit(unit_name, params, group_of, self.group_order, 1, 0, self.compute_dtype, self.device, None)
+                unit = FlatUnit(unit_name, params, group_of, self.group_order, 1, 0, self.compute_dtype, self.device, None,
+                                offload=self.cpu_offload)
             elif sharded(module, local_only):
                 unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
-                                self.compute_dtype, self.device, None, resident=False)
+                                self.compute_dtype, self.device, None, resident=False, offload=self.cpu_offload)
                 unit.module = module
                 self._install_gather_hooks(unit, module)
             else:
                 unit = FlatUnit(unit_name, params, group_of, self.group_order, self.shard_world, self.shard_rank,
-                                self.compute_dtype, self.device, storage)
+                                self.compute_dtype, self.device, storage, offload=self.cpu_offload)
             unit.local_only = local_only
             self._materialise(unit, module if id(module) not in materialised else None)
             materialised.add(id(module))
             self.units.append(unit)
-            if self.peer is not None and not local_only and unit.resident:
+            if self.peer is not None and not local_only and unit.resident and not unit.offload:
                 arena = self.arenas[self.compute_dtype]
                 for seg in unit.segments:
                     if seg.compute is not None:
@@ -721,7 +739,7 @@ class ShardedTrainingEngine:
         for unit in self.units:
             if not unit.master_is_alias and not masters_already_cast:
                 dst = unit.compute_shard
-                if dst.is_cuda and ops.native_available() and dst.dtype == torch.bfloat16:
+                if dst.is_cuda and unit.master.is_cuda and ops.native_available() and dst.dtype == torch.bfloat16:
                     ops.native().cast_f32_to_bf16(unit.master, dst)
                 else:
                     dst.copy_(unit.master)
@@ -758,12 +776,19 @@ class ShardedTrainingEngine:
             for unit in self.units:
                 unit.grad_shard.mul_(factor.to(unit.grad_shard.device))
         with site("step.adamw(+broadcast)"):
+            if self.cpu_offload:
+                # reduced, unscaled gradient shards to pinned host memory; the optimizer (clip coefficient and 1 / dp
+                # applied there) then runs on the CPU and copies its result into the device's compute shard
+                for unit in self.units:
+                    unit.grad_host.copy_(unit.grad_shard, non_blocking=True)
+                if self.device.type == "cuda":
+                    torch.cuda.current_stream(self.device).synchronize()
             optimizer.step()
         if lr_scheduler is not None:
             lr_scheduler.step()
         with site("step.refresh_parameters"):
             self.refresh_parameters(masters_already_cast=fused, broadcast_done=fused and getattr(optimizer, "last_step_broadcast", False))
-        if fused and (self.shard_world == 1 or all(not u.resident or u.local_only for u in self.units)):
+        if fused and not self.cpu_offload and (self.shard_world == 1 or all(not u.resident or u.local_only for u in self.units)):
             pass  # the fused kernel cleared every gradient element it consumed
         else:
             with site("step.zero_grad"):

@@ -50,7 +50,8 @@ def tiny_config(micro_batch_size: int, steps: int, ga: int = 1, stage: int = 3, 
         mixed_precision_args=dict(dtype="fp32"),
         distributed_args=dict(stage=stage, tensor_parallel_world_size=tp, sequence_parallel=sp, pipeline_parallel_world_size=pp,
                               num_pipeline_stages=stages, pipeline_parallel_schedule=schedule, **({"expert_parallel_world_size": ep} if ep > 1 else {}),
-                              **({"keep_parameters_gathered": False} if os.environ.get("TINY_SHARDED_PARAMETERS") == "1" else {})),
+                              **({"keep_parameters_gathered": False} if os.environ.get("TINY_SHARDED_PARAMETERS") == "1" else {}),
+                              **({"cpu_offload": True} if os.environ.get("TINY_CPU_OFFLOAD") == "1" else {})),
     )
 
 
@@ -119,6 +120,14 @@ def main() -> None:
         curve.append({"loss": metrics["loss"] if has_loss else None, "grad_norm": grad_norm})
     from lm_engine.utils import is_tracking_rank
 
+    if os.environ.get("TINY_REPORT_STORAGE") == "1" and curve:
+        # where the fp32 master shards and the optimizer's moments live (the cpu_offload test looks at this)
+        engine = getattr(container[0], "_lm_engine", None)
+        if engine is not None:
+            segment = engine.units[0].segments[0]
+            state = optimizers[0].state.get(segment.master, {})
+            curve[-1]["master_device"] = str(engine.units[0].master.device)
+            curve[-1]["optimizer_state_device"] = str(state["exp_avg"].device) if "exp_avg" in state else None
     if is_tracking_rank():
         with open(out_path, "w") as handle:
             json.dump(curve, handle)

@@ -212,3 +212,27 @@ def test_packed_documents_through_the_scan_kernels_match_the_per_document_loops(
     for name, g in grads.items():
         r = ref_grads[name]
         assert (g - r).norm().item() <= 3e-3 * r.norm().item() + 1e-6, name
+
+
+def test_cpu_offload_keeps_masters_on_the_host_and_trains_the_same(tmp_path):
+    """``distributed_args.cpu_offload`` on a GPU: the fp32 master shards and the optimizer's moments sit in pinned host
+    memory, the optimizer runs on the CPU, and the loss curve equals the one of the run that keeps them on the device."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    script = os.path.join(os.path.dirname(__file__), "scripts", "tiny_pretrain.py")
+    curves = []
+    for offload in (False, True):
+        out = tmp_path / f"curve_{int(offload)}.json"
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29691", TINY_CPU_OFFLOAD="1" if offload else "0",
+                   TINY_REPORT_STORAGE="1")
+        subprocess.run([sys.executable, script, str(out), "8", "12", "3"], check=True, env=env, timeout=600, capture_output=True)
+        curves.append(json.loads(out.read_text()))
+    plain, offloaded = curves
+    assert offloaded[-1].get("master_device") == "cpu" and offloaded[-1].get("optimizer_state_device") == "cpu"
+    assert plain[-1].get("master_device", "cuda").startswith("cuda")
+    for a, b in zip(plain, offloaded):
+        assert abs(a["loss"] - b["loss"]) < 1e-4 * max(1.0, abs(a["loss"]))
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-3 * max(1.0, abs(a["grad_norm"]))
