@@ -285,7 +285,7 @@ def bench_attention(args) -> None:
                 record["flash_attn2_bwd_ms"], record["flash_attn2_bwd_tflops"] = round(ms, 4), round(2.5 * flops / ms / 1e9, 1)
             except ImportError:
                 pass
-        if hasattr(C, "sb_attn_bwd") and not args.profile and not args.trace:
+        if hasattr(C, "sb_attn_bwd") and (args.stickbreaking or (not args.profile and not args.trace)):
             # stick-breaking attention on the same buffer (strictly causal, same matrix products as the softmax kernels)
             sb_out, sb_rem = C.sb_attn_fwd(qkv, cu, groups, qpg, d, d**-0.5, st)
             d_rem = torch.randn_like(sb_rem)
@@ -424,6 +424,7 @@ def main() -> None:
     parser.add_argument("--split-k", nargs="*", type=int, default=[0], help="gemm --accumulate: splits of K to sweep (0 = built-in, 1 = none)")
     parser.add_argument("--direct-store", action="store_true", help="gemm: also time the register-store epilogue")
     parser.add_argument("--accumulate", action="store_true", help="gemm: fp32 accumulate into the output (weight-gradient form)")
+    parser.add_argument("--stickbreaking", action="store_true", help="attention: run the stick-breaking kernels also under --profile / --trace")
     parser.add_argument("--trace", action="store_true", help="gemm: report where the MMA and epilogue threads of the CTA-pair kernel wait")
     parser.add_argument("--interleave", action="store_true", help="gemm: candidates and the library take turns launch by launch after heating the GPU to its power-capped clock")
     parser.add_argument("--heat-ms", type=float, default=1500.0, help="gemm --interleave: length of the warm-up under load")
