@@ -5,7 +5,9 @@
 //
 // Same machinery as the softmax kernel (attention_fwd.cu): q, k, v read in place from the fused projection buffer through
 // one strided TMA map, one CTA per 128 query rows of one document and one head, warp 0 = TMA, warp 1 = tcgen05 MMA
-// (S = Q K^T into two TMEM buffers, O += A V into a third), warps 2-5 = one thread per query row. The differences:
+// (S = Q K^T into two TMEM buffers, O += A V into a third; the bf16 weights A are written over the S columns they were
+// computed from and read there as the A operand of the second product), warps 2-5 = one thread per query row. The
+// differences:
 //   * key tiles are visited from the diagonal towards the start of the document, because the weight of key j depends on
 //     all keys between j and i: every row keeps the product of (1 - sigma(z_ik)) over the keys seen so far, and
 //     A[i, j] = sigma(z_ij) * product before the product shrinks by (1 - sigma(z_ij));
@@ -30,17 +32,15 @@ struct FwdSmem {
   static constexpr int Q_BYTES = BLOCK_M * D * 2;
   static constexpr int K_BYTES = BLOCK_N * D * 2;
   static constexpr int V_BYTES = BLOCK_N * D * 2;
-  static constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * K_BYTES;
-  static constexpr int OFF_P = OFF_V + KV_STAGES * V_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
 // barrier indices
-enum { B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = 3, B_S_FULL = 5, B_S_EMPTY = 7, B_P_READY = 9, B_PV_DONE = 10, B_COUNT = 11 };
+enum { B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = 3, B_S_FULL = 5, B_P_READY = 7, B_PV_DONE = 8, B_COUNT = 9 };
 
 template <int D>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -53,7 +53,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
-  uint8_t* sP = smem + L::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -91,7 +90,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&bars[B_KV_FULL + s], 1);
       mbar_init(&bars[B_KV_EMPTY + s], 1);
       mbar_init(&bars[B_S_FULL + s], 1);
-      mbar_init(&bars[B_S_EMPTY + s], 128);
     }
     mbar_init(&bars[B_P_READY], 128);
     mbar_init(&bars[B_PV_DONE], 1);
@@ -152,13 +150,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       constexpr uint32_t idesc_s = umma_idesc_bf16(BLOCK_M, BLOCK_N, 0, 0);  // S = Q K^T, both K-major
       constexpr uint32_t idesc_o = umma_idesc_bf16(BLOCK_M, D, 0, 1);        // O = P V, V is MN-major
       const uint32_t q_base = smem_u32(sQ);
-      const uint32_t p_base = smem_u32(sP);
       bool ok = mbar_wait(&bars[B_Q], 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
         const int st = j % KV_STAGES;
         if (!mbar_wait(&bars[B_KV_FULL + st], (j / KV_STAGES) & 1, abort_flag)) return false;
-        if (!mbar_wait(&bars[B_S_EMPTY + st], ((j / 2) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
+        // No wait for the S buffer: it last held S(j-2) and then the weights of tile j-2, which O += A V(j-2) has read;
+        // that product was issued by this thread before this one, and the tensor cores retire in order.
         const uint32_t k_base = smem_u32(sK + st * L::K_BYTES);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -182,9 +180,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const uint32_t v_base = smem_u32(sV + st * L::V_BYTES);
 #pragma unroll
         for (int k = 0; k < BLOCK_N / 16; ++k) {
-          const uint64_t da = umma_smem_desc_sw128(p_base + (k / 4) * (BLOCK_M * 128) + (k % 4) * 32, 16, 1024);
+          // 16 keys per step: their bf16 weights are 8 columns of the tile's S buffer
           const uint64_t db = umma_smem_desc_sw128(v_base + k * 16 * 128, BLOCK_N * 128, 1024);
-          umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);
+          umma_f16_ts(tmem_O, tmem_S0 + st * BLOCK_N + k * 8, db, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&bars[B_KV_EMPTY + st]);
         umma_commit(&bars[B_PV_DONE]);
@@ -213,8 +211,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < BLOCK_N / 32; ++c) B200_TMEM_LD_32((s + c * 32), tmem_S0 + lane_addr + st * BLOCK_N + c * 32);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[B_S_EMPTY + st]);
 
       const int kv0 = (n_tiles - 1 - j) * BLOCK_N;
       uint32_t p[BLOCK_N / 2];
@@ -241,25 +237,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       a_total += row_sum;
 
-      if (j > 0) {
-        // P buffer free again: the product of the previous tile retired
-        if (!mbar_wait(&bars[B_PV_DONE], (j - 1) & 1, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-      }
-      // P (bf16) -> shared memory, K-major with the 128-byte swizzle the MMA expects
-#pragma unroll
-      for (int kb = 0; kb < BLOCK_N / 64; ++kb) {
-        uint8_t* row_base = sP + kb * (BLOCK_M * 128) + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const int pi = kb * 32 + ch * 4;
-          *reinterpret_cast<uint4*>(row_base + ((ch ^ (r & 7)) * 16)) = make_uint4(p[pi], p[pi + 1], p[pi + 2], p[pi + 3]);
-        }
-      }
-      fence_proxy_async_smem();
+      // weights (bf16 pairs) over the first 64 of the 128 S columns this thread has read: the A operand of the second product
+      B200_TMEM_ST_32(tmem_S0 + lane_addr + st * BLOCK_N, p);
+      B200_TMEM_ST_32(tmem_S0 + lane_addr + st * BLOCK_N + 32, (p + 32));
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[B_P_READY]);
     }
