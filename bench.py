@@ -383,7 +383,9 @@ def moe_record(cli) -> dict | None:
         env.pop(key, None)
     out_path = os.path.join(tempfile.gettempdir(), f"bench-moe-{os.getpid()}-{rank}.json")
     steps = cli.moe_steps or max(3, cli.steps // 4)
-    cmd = [sys.executable, os.path.abspath(__file__), "--config", "moe", "--gpus", str(cli.gpus), "--steps", str(steps), "--warmup", "3",
+    # six warm-up steps for both arms: with dropless exact sizing the row buffers grow to the largest need seen so far, and
+    # they have to have stopped growing before the timed steps (a step that grows them costs about twice a normal one)
+    cmd = [sys.executable, os.path.abspath(__file__), "--config", "moe", "--gpus", str(cli.gpus), "--steps", str(steps), "--warmup", "6",
            "--impl", cli.impl, "--reference-compile", "off", "--child-output", out_path]
     if cli.skip_e2e:
         cmd.append("--skip-e2e")

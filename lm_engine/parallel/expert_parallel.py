@@ -39,8 +39,8 @@ _WORKSPACES: dict[int, "_Workspace"] = {}
 #   None (default)  exact and dropless: every rank derives, from the routing table it already holds for the whole group,
 #                   the tile-padded row count of the fullest rank and reads it back (one small device-to-host read per
 #                   MoE layer and forward pass); buffers then hold what the busiest rank needs, nothing is ever dropped.
-#                   The size actually used is the largest need seen so far in the run (all layers share it), rounded up
-#                   to `_ROW_QUANTUM`: a buffer size that changed with every batch and layer kept the caching allocator
+#                   The size actually used is the largest need seen so far in the run (all layers share it) plus one
+#                   eighth of headroom when it grows, rounded up to `_ROW_QUANTUM`: a buffer size that changed with every batch and layer kept the caching allocator
 #                   mapping new memory in the middle of the run (stalls of about a second at 4 GPUs), a size that only
 #                   ever grows settles after a few steps
 #   a factor >= 1   static bound without a host read: ``factor x (a rank's balanced share of the routed entries)`` rows
@@ -241,7 +241,11 @@ class _ExpertParallelFn(torch.autograd.Function):
             if exact is not None:
                 need = (exact.value() + _ROW_QUANTUM - 1) // _ROW_QUANTUM * _ROW_QUANTUM
                 key = (x.device, world * entries, local)  # the same on every rank, like the count itself
-                capacity_rows = _ROW_HIGH_WATER[key] = max(_ROW_HIGH_WATER.get(key, 0), need)
+                capacity_rows = _ROW_HIGH_WATER.get(key, 0)
+                if need > capacity_rows:
+                    # one eighth of headroom, so that the next slightly larger batch does not grow the buffers again
+                    capacity_rows = (need + need // 8 + _ROW_QUANTUM - 1) // _ROW_QUANTUM * _ROW_QUANTUM
+                    _ROW_HIGH_WATER[key] = capacity_rows
             else:
                 capacity_rows = _capacity_rows(entries, local)
             layout, global_rows = build_group_layout(selected_all, num_experts, local, rank, capacity_rows)
