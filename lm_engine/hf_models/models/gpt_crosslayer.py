@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ...ops.attention import attention_varlen_reference
+from ...ops.attention import attention_fused_qkv
 from ...utils import divide_if_divisible
 from ..cache import GenerationCache
 from ..config import GPTBaseConfig, GPTCrossLayerConfig
@@ -79,7 +79,14 @@ class CrossLayerAttention(nn.Module):
             if self.position_embedding_type == "rope":
                 cos, sin = ctx.rope_cos_sin
                 q = apply_rotary_pos_emb(q, (cos, sin))
-            out = attention_varlen_reference(q, key, value, ctx.cu_seqlens, self.softmax_scale, True, p_drop).reshape(T, -1)
+            # One buffer laid out like a fused projection (per key/value group: its query heads, then k, then v), so that
+            # the packed-sequence attention kernels serve this model too; the keys and values may come from another
+            # layer (reference: lm_engine/hf_models/models/gpt_crosslayer/sequence_mixers in the reference calls flash
+            # attention on the separate tensors).
+            groups, qpg = self.num_key_value_heads, self.num_heads // self.num_key_value_heads
+            fused = torch.cat([q.view(T, groups, qpg, self.head_dim), key.reshape(T, groups, 1, self.head_dim).to(q.dtype),
+                               value.reshape(T, groups, 1, self.head_dim).to(q.dtype)], dim=2).reshape(T, groups * (qpg + 2) * self.head_dim)
+            out = attention_fused_qkv(fused, ctx.cu_seqlens, ctx.max_seqlen, groups, qpg, self.head_dim, self.softmax_scale, True, p_drop)
         else:
             b, s, _ = q.shape
             q = q.view(b, s, self.num_heads, self.head_dim).transpose(1, 2)
