@@ -11,8 +11,9 @@ import pytest
 SCRIPT = os.path.join(os.path.dirname(__file__), "scripts", "ckpt_resume.py")
 
 
-def _run(world: int, port: int, *script_args: str):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+def _run(world: int, port: int, *script_args: str, cpu_offload: bool = False):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="",
+               TINY_CPU_OFFLOAD="1" if cpu_offload else "0")
     if world == 1:
         cmd = [sys.executable, SCRIPT, *script_args]
     else:
@@ -69,3 +70,17 @@ def test_tensor_parallel_checkpoint_resumes_and_unshards(tmp_path, world):
     for key, value in from_ref.items():
         assert from_tp[key].shape == value.shape, key
         assert (from_tp[key] - value).abs().max().item() < 1e-4, key
+
+
+@pytest.mark.parametrize("resume_world,resume_offload", [(2, True), (1, False)])
+def test_checkpoint_of_a_cpu_offload_run_resumes_with_and_without_it(tmp_path, resume_world, resume_offload):
+    """``cpu_offload`` changes where the master shards and the optimizer state live, not what a checkpoint holds: a run
+    saved with it resumes with it, and on another number of ranks without it, with the uninterrupted losses."""
+    save_dir = tmp_path / "ckpt"
+    a, b = tmp_path / "a.json", tmp_path / "b.json"
+    _run(2, 29721, "save", str(save_dir), str(a), "sync", cpu_offload=True)
+    _run(resume_world, 29723, "resume", str(save_dir), str(b), "sync", cpu_offload=resume_offload)
+    first, second = json.loads(a.read_text()), json.loads(b.read_text())
+    assert len(first["losses"]) == len(second["losses"]) == 2
+    for x, y in zip(first["losses"], second["losses"]):
+        assert abs(x - y) < 2e-5 * max(1.0, abs(x)), (first, second)
