@@ -70,10 +70,34 @@ class FusedAdamW(Optimizer):
                     ops.native().adamw_step(p.data, state["exp_avg"], state["exp_avg_sq"], p.grad, target, group["lr"], beta1,
                                             beta2, group["eps"], group["weight_decay"], state["step"], self.grad_scale,
                                             self.grad_mul, True)
+                elif not p.is_cuda and self.decoupled and hasattr(torch, "_fused_adamw_") and p.dtype == torch.float32:
+                    # cpu_offload: the master shard, its moments and the staged gradient live on the host
+                    self.last_step_broadcast = False
+                    self._step_host(p, state, group, target)
                 else:
                     self.last_step_broadcast = False
                     self._step_torch(p, state, group, target)
         return loss
+
+    def _step_host(self, p, state, group, target) -> None:
+        """One pass of PyTorch's fused CPU AdamW over a host-resident segment (instead of a dozen element-wise passes),
+        then the copy of the result into the device's compute shard."""
+        g = p.grad
+        factor = self.grad_mul
+        if self.grad_scale is not None:
+            if getattr(self, "_host_scale_of", None) is not self.grad_scale or self._host_scale_step != state["step"]:
+                # one device-to-host read of the clipping coefficient per optimizer step, not per segment
+                self._host_scale, self._host_scale_of, self._host_scale_step = float(self.grad_scale), self.grad_scale, state["step"]
+            factor = factor * self._host_scale
+        if factor != 1.0:
+            g.mul_(factor)
+        beta1, beta2 = group["betas"]
+        step = torch.tensor(float(state["step"]))
+        torch._fused_adamw_([p], [g], [state["exp_avg"]], [state["exp_avg_sq"]], [], [step], lr=group["lr"], beta1=beta1, beta2=beta2,
+                            weight_decay=group["weight_decay"], eps=group["eps"], amsgrad=False, maximize=False)
+        if target is not None:
+            target.copy_(p)
+        g.zero_()
 
     def _step_torch(self, p, state, group, target) -> None:
         beta1, beta2 = group["betas"]
