@@ -334,6 +334,10 @@ class GPTCrossLayerConfig(CommonConfig):
                 raise ValueError("a layer can only share with itself or an earlier layer")
             if sharing_pattern[parent] != parent:
                 raise ValueError("a layer can only share with a layer that owns its keys/values")
+            mine, theirs = self.sequence_mixer_blocks[i], self.sequence_mixer_blocks[parent]
+            if getattr(mine, "sequence_mixer_type", None) != getattr(theirs, "sequence_mixer_type", None):
+                # rotary embeddings are applied to the keys of softmax layers only: a stick-breaking layer cannot read them
+                raise ValueError("layers that share keys/values need the same sequence_mixer_type")
         self.sharing_pattern = sharing_pattern
 
 

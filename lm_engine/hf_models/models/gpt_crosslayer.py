@@ -50,16 +50,22 @@ class CrossLayerAttention(nn.Module):
     def __init__(self, config: GPTCrossLayerConfig, layer_idx: int, use_padding_free_transformer: bool) -> None:
         super().__init__()
         block = config.sequence_mixer_blocks[layer_idx]
-        if block.sequence_mixer_type != "softmax_attention":
-            raise ValueError("cross-layer attention is defined for softmax attention layers only")
+        if block.sequence_mixer_type not in ("softmax_attention", "stickbreaking_attention"):
+            raise ValueError("cross-layer attention is defined for softmax and stick-breaking attention layers")
+        # stick-breaking layers (arXiv 2410.17980) share keys and values across layers the same way; they use no
+        # positional embedding and carry the parameters of the stand-alone mixer (``head_bias``, ``norm``)
+        self.stickbreaking = block.sequence_mixer_type == "stickbreaking_attention"
         self.hidden_size = config.hidden_size
         self.num_heads = block.num_attention_heads
         self.num_key_value_heads = block.num_key_value_heads
         self.head_dim = divide_if_divisible(self.hidden_size, self.num_heads, "")
-        self.position_embedding_type = config.position_embedding_type
+        self.position_embedding_type = "nope" if self.stickbreaking else config.position_embedding_type
         self.attention_multiplier = block.attention_multiplier
         self.layer_idx = layer_idx
-        self.softmax_dropout_p = block.softmax_dropout
+        self.softmax_dropout_p = getattr(block, "softmax_dropout", 0)
+        if self.stickbreaking:
+            self.head_bias = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
+            self.norm = nn.GroupNorm(self.num_heads, self.hidden_size)
         std = config.initializer_range / (math.sqrt(config.m_width) if config.init_method == "mup" else 1)
         self.q_attn = ParameterizedLinear(self.hidden_size, self.hidden_size, bias=block.add_bias, std=std)
         self.c_proj = ParameterizedLinear(self.hidden_size, self.hidden_size, bias=block.add_bias,
@@ -70,8 +76,57 @@ class CrossLayerAttention(nn.Module):
     def softmax_scale(self) -> float:
         return self.attention_multiplier if self.attention_multiplier is not None else 1.0 / math.sqrt(self.head_dim)
 
+    # ------------------------------------------------------------------ stick-breaking
+    def _stickbreaking_kernel_ok(self, q: torch.Tensor) -> bool:
+        from ... import ops
+        from ...enums import Kernel
+        from ...kernels import is_kernel_allowed
+        from ...ops.attention import padded_head_dim
+
+        return (q.is_cuda and q.dtype == torch.bfloat16 and padded_head_dim(self.head_dim) is not None and ops.native_available()
+                and hasattr(ops.native(), "sb_attn_fwd") and is_kernel_allowed(Kernel.stickbreaking_attention))
+
+    def _stickbreaking_mix(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """q ``[hq, n_q, d]``, k / v ``[hkv, n_k, d]`` of one document -> ``[n_q, hidden]`` (before the GroupNorm)."""
+        from ..layers.stickbreaking import stickbreaking_attention
+
+        group = self.num_heads // self.num_key_value_heads
+        out, rem = stickbreaking_attention(q, k.repeat_interleave(group, dim=0), v.repeat_interleave(group, dim=0), self.softmax_scale)
+        out = out + rem[..., None] * self.head_bias[:, None, :].to(out.dtype)
+        return out.transpose(0, 1).reshape(q.shape[1], self.hidden_size)
+
+    def _forward_stickbreaking(self, q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, ctx: SequenceContext) -> torch.Tensor:
+        if ctx.packed:
+            T = q.shape[0]
+            q = q.view(T, self.num_heads, self.head_dim)
+            if self._stickbreaking_kernel_ok(q):
+                from ...ops.attention import pad_fused_qkv, padded_head_dim
+                from ..layers.stickbreaking import _FusedStickBreaking
+
+                groups, qpg = self.num_key_value_heads, self.num_heads // self.num_key_value_heads
+                fused = torch.cat([q.view(T, groups, qpg, self.head_dim), key.reshape(T, groups, 1, self.head_dim).to(q.dtype),
+                                   value.reshape(T, groups, 1, self.head_dim).to(q.dtype)], dim=2).reshape(T, groups * (qpg + 2) * self.head_dim)
+                width = padded_head_dim(self.head_dim)
+                if width != self.head_dim:
+                    fused = pad_fused_qkv(fused, groups, qpg, self.head_dim, width)
+                out, rem = _FusedStickBreaking.apply(fused.contiguous(), ctx.cu_seqlens_int32(), groups, qpg, width, self.softmax_scale)
+                out = out.view(T, self.num_heads, width)[:, :, : self.head_dim]
+                mixed = out + rem.t().unsqueeze(-1).to(out.dtype) * self.head_bias.to(out.dtype)
+                mixed = mixed.reshape(T, self.hidden_size)
+            else:
+                bounds = ctx.cu_seqlens.tolist()
+                mixed = torch.cat([self._stickbreaking_mix(q[s:e].transpose(0, 1), key[s:e].transpose(0, 1), value[s:e].transpose(0, 1))
+                                   for s, e in zip(bounds[:-1], bounds[1:]) if e > s], dim=0)
+            return self.norm(mixed)
+        b, s, _ = q.shape
+        q = q.view(b, s, self.num_heads, self.head_dim).transpose(1, 2)  # key / value arrive as [b, hkv, n_k, d]
+        mixed = torch.stack([self._stickbreaking_mix(q[i], key[i], value[i]) for i in range(b)])
+        return self.norm(mixed.view(b * s, self.hidden_size)).view(b, s, self.hidden_size)
+
     def forward(self, hidden_states: torch.Tensor, key: torch.Tensor, value: torch.Tensor, ctx: SequenceContext) -> torch.Tensor:
         q = self.q_attn(hidden_states)
+        if self.stickbreaking:
+            return self.dropout(self.c_proj(self._forward_stickbreaking(q, key, value, ctx)))
         p_drop = self.softmax_dropout_p if self.training else 0.0
         if ctx.packed:
             T = q.shape[0]
@@ -105,8 +160,8 @@ class GPTCrossLayerBlock(nn.Module):
         super().__init__()
         self.m_residual = config.m_residual
         self.layer_idx = layer_idx
-        self.position_embedding_type = config.position_embedding_type
         block = config.sequence_mixer_blocks[layer_idx]
+        self.position_embedding_type = "nope" if block.sequence_mixer_type == "stickbreaking_attention" else config.position_embedding_type
         self.kv_proj = None
         if config.sharing_pattern[layer_idx] == layer_idx:
             self.kv_proj = KeyValueProjection(config.hidden_size, block.num_attention_heads, block.num_key_value_heads,

@@ -190,3 +190,40 @@ def test_greedy_generation_is_consistent_with_forward():
     out = model.generate(prompt, max_new_tokens=6, eos_token_id=-1)
     logits = model(input_ids=out[:, :-1]).logits
     assert torch.equal(logits.argmax(-1)[:, 4:], out[:, 5:])
+
+
+def test_crosslayer_with_stickbreaking_layers():
+    """Stick-breaking layers share keys / values across layers like softmax layers do: the conversion of a gpt_base model
+    with stick-breaking mixers computes the same function, packed equals padded with sharing, greedy decoding with the
+    cache repeats the full forward pass, and mixed sharing groups are refused."""
+    from lm_engine.hf_models import GPTCrossLayerConfig, GPTCrossLayerForCausalLM, convert_gpt_base_to_gpt_crosslayer
+
+    sb = dict(sequence_mixer_type="stickbreaking_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)
+    torch.manual_seed(0)
+    base = GPTBaseForCausalLM(GPTBaseConfig(**_kw(layers=4, mixers=[sb] * 4, position_embedding_type="nope"))).eval()
+    with torch.no_grad():
+        for name, p in base.named_parameters():
+            if name.endswith("head_bias"):
+                p.normal_(std=0.5)  # zero-initialised: make the remainder term visible
+    ids = torch.randint(0, 128, (2, 12))
+    with torch.no_grad():
+        ref = base(input_ids=ids, labels=ids)
+        _, same = convert_gpt_base_to_gpt_crosslayer(base.config, base)
+        out = same.eval()(input_ids=ids, labels=ids)
+        assert torch.allclose(out.logits, ref.logits, atol=1e-5) and torch.allclose(out.loss, ref.loss, atol=1e-6)
+        config, shared = convert_gpt_base_to_gpt_crosslayer(base.config, base, sharing_pattern=[0, 0, 2, 2])
+        shared.eval()
+        packed = GPTCrossLayerForCausalLM(config, use_padding_free_transformer=True).eval()
+        packed.load_state_dict(shared.state_dict())
+        assert torch.allclose(packed(input_ids=ids.tolist()).logits, shared(input_ids=ids).logits.reshape(-1, 128), atol=1e-5)
+        greedy = shared.generate(ids[:, :4], max_new_tokens=4)
+        again = shared(input_ids=greedy[:, :-1]).logits.argmax(-1)
+        assert torch.equal(again[:, 3:], greedy[:, 4:])
+    # gradients reach the shared projection and the stick-breaking parameters
+    shared.train()
+    shared(input_ids=ids, labels=ids).loss.backward()
+    grads = {n: p.grad for n, p in shared.named_parameters()}
+    assert float(grads["transformer.h.0.kv_proj.kv_attn.weight"].abs().sum()) > 0
+    assert float(grads["transformer.h.1.sequence_mixer.head_bias"].abs().sum()) > 0
+    with pytest.raises(ValueError):
+        GPTCrossLayerConfig(**_kw(layers=2, mixers=[_attn(), sb]), sharing_pattern=[0, 0])
