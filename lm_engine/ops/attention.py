@@ -27,8 +27,16 @@ def split_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int):
 
 
 def attention_varlen_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
-                               scale: float | None, causal: bool = True, dropout_p: float = 0.0) -> torch.Tensor:
-    """q ``[T, hq, d]``, k/v ``[T, hkv, d]`` -> ``[T, hq, d]``; documents delimited by ``cu_seqlens``."""
+                               scale: float | None, causal: bool = True, dropout_p: float = 0.0,
+                               sliding_window: int | None = None, softcap: float = 0.0) -> torch.Tensor:
+    """q ``[T, hq, d]``, k/v ``[T, hkv, d]`` -> ``[T, hq, d]``; documents delimited by ``cu_seqlens``.
+
+    ``sliding_window`` (a query sees the keys at most that many positions before it, and after it when not causal) and
+    ``softcap`` (scores become ``softcap * tanh(scores / softcap)``) follow the flash-attention meaning of the reference's
+    helper (lm_engine/hf_models/modeling_utils/sequence_mixer_blocks/flash_attention_utils.py:65-81); they are evaluated
+    with explicit score matrices."""
+    if sliding_window is not None or softcap:
+        return _attention_varlen_windowed(q, k, v, cu_seqlens, scale, causal, dropout_p, sliding_window, softcap)
     bounds = cu_seqlens.tolist()
     outs = []
     hq, hkv = q.shape[1], k.shape[1]
@@ -43,6 +51,33 @@ def attention_varlen_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
             vi = vi.repeat_interleave(hq // hkv, dim=1)
         o = F.scaled_dot_product_attention(qi, ki, vi, is_causal=causal, scale=scale, dropout_p=dropout_p)
         outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, dim=0)
+
+
+def _attention_varlen_windowed(q, k, v, cu_seqlens, scale, causal, dropout_p, sliding_window, softcap) -> torch.Tensor:
+    bounds = cu_seqlens.tolist()
+    outs = []
+    hq, hkv, d = q.shape[1], k.shape[1], q.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        if e == s:
+            continue
+        n = e - s
+        qi, ki, vi = q[s:e].transpose(0, 1).float(), k[s:e].transpose(0, 1).float(), v[s:e].transpose(0, 1).float()
+        if hq != hkv:
+            ki, vi = ki.repeat_interleave(hq // hkv, dim=0), vi.repeat_interleave(hq // hkv, dim=0)
+        scores = torch.einsum("hqd,hkd->hqk", qi, ki) * scale
+        if softcap:
+            scores = softcap * torch.tanh(scores / softcap)
+        i = torch.arange(n, device=q.device)[:, None]
+        j = torch.arange(n, device=q.device)[None, :]
+        allowed = (j <= i) if causal else torch.ones(n, n, dtype=torch.bool, device=q.device)
+        if sliding_window is not None:
+            allowed = allowed & (j >= i - sliding_window) & (j <= i + sliding_window)
+        probs = torch.softmax(scores.masked_fill(~allowed, float("-inf")), dim=-1)
+        if dropout_p:
+            probs = F.dropout(probs, dropout_p)
+        outs.append(torch.einsum("hqk,hkd->hqd", probs, vi).transpose(0, 1).to(q.dtype))
     return torch.cat(outs, dim=0)
 
 
@@ -90,9 +125,18 @@ def pad_fused_qkv(qkv: torch.Tensor, groups: int, qpg: int, d: int, dp: int) -> 
 
 
 def attention_fused_qkv(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, groups: int, qpg: int, d: int,
-                        scale: float | None = None, causal: bool = True, dropout_p: float = 0.0) -> torch.Tensor:
-    """Attention over a fused projection ``[T, groups*(qpg+2)*d]`` -> ``[T, groups*qpg*d]``."""
+                        scale: float | None = None, causal: bool = True, dropout_p: float = 0.0,
+                        sliding_window: int | None = None, softcap: float = 0.0) -> torch.Tensor:
+    """Attention over a fused projection ``[T, groups*(qpg+2)*d]`` -> ``[T, groups*qpg*d]``.
+
+    A sliding window or a score cap is not in the kernels: such a call is counted as a fallback (an error in strict mode)
+    and evaluated by the PyTorch formulation."""
     scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if sliding_window is not None or softcap:
+        note_fallback("attention", "sliding window / score cap", qkv)
+        q, k, v = split_fused_qkv(qkv, groups, qpg, d)
+        out = attention_varlen_reference(q, k, v, cu_seqlens, scale, causal, dropout_p, sliding_window, softcap)
+        return out.reshape(qkv.shape[0], groups * qpg * d)
     if dropout_p == 0.0 and _native_attention_ok(qkv, d):
         return _FusedQKVAttentionFn.apply(qkv, cu_seqlens.to(torch.int32), max_seqlen, groups, qpg, d, scale, causal)
     dp = padded_head_dim(d)

@@ -227,3 +227,28 @@ def test_crosslayer_with_stickbreaking_layers():
     assert float(grads["transformer.h.1.sequence_mixer.head_bias"].abs().sum()) > 0
     with pytest.raises(ValueError):
         GPTCrossLayerConfig(**_kw(layers=2, mixers=[_attn(), sb]), sharing_pattern=[0, 0])
+
+
+def test_sliding_window_and_score_cap_of_the_attention_op():
+    """The two flash-attention options of the reference's helper, evaluated by the PyTorch formulation: a window as wide as
+    the document and a huge cap change nothing; a narrow window equals attention over the last keys only; the cap equals
+    the explicit tanh formula."""
+    from lm_engine.ops.attention import attention_fused_qkv, attention_varlen_reference
+
+    torch.manual_seed(0)
+    T, groups, qpg, d = 24, 2, 2, 8
+    qkv = torch.randn(T, groups * (qpg + 2) * d)
+    cu = torch.tensor([0, 10, 24], dtype=torch.int32)
+    plain = attention_fused_qkv(qkv, cu, 14, groups, qpg, d)
+    assert torch.allclose(attention_fused_qkv(qkv, cu, 14, groups, qpg, d, sliding_window=64, softcap=1e6), plain, atol=1e-5)
+    windowed = attention_fused_qkv(qkv, cu, 14, groups, qpg, d, sliding_window=2)
+    view = qkv.view(T, groups, qpg + 2, d)
+    q, k, v = view[:, :, :qpg].reshape(T, groups * qpg, d), view[:, :, qpg], view[:, :, qpg + 1]
+    for token, (lo, hi) in ((5, (3, 6)), (13, (11, 14)), (10, (10, 11))):  # the third one is the first token of its document
+        for head in range(groups * qpg):
+            scores = (k[lo:hi, head // qpg] @ q[token, head]) * d**-0.5
+            expected = torch.softmax(scores, 0) @ v[lo:hi, head // qpg]
+            assert torch.allclose(windowed.view(T, groups * qpg, d)[token, head], expected, atol=1e-5)
+    capped = attention_varlen_reference(q, k, v, cu, None, True, 0.0, None, 0.5).view(T, groups * qpg, d)
+    scores = (k[:4, 0] @ q[3, 0]) * d**-0.5
+    assert torch.allclose(capped[3, 0], torch.softmax(0.5 * torch.tanh(scores / 0.5), 0) @ v[:4, 0], atol=1e-5)
