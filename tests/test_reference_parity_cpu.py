@@ -174,3 +174,66 @@ def test_distributed_checkpoints_cross_load_with_the_reference(tmp_path):
     subprocess.run([sys.executable, "-c", _READ, REF, str(our_store), str(ref_out), str(back)], check=True, cwd=str(tmp_path), env=env,
                    timeout=600, capture_output=True)
     assert torch.allclose(torch.load(back)["logits"], logits, atol=3e-6, rtol=1e-5)
+
+
+_HYBRID = dict(
+    initializer_range=0.1, layer_norm_epsilon=1e-5, hidden_size=512, num_layers=4, max_position_embeddings=512,
+    normalization_function="rmsnorm", position_embedding_type="rope", rope_theta=10000, vocab_size=50304, tie_word_embeddings=False,
+    m_width=9, m_emb=12, m_residual=0.22, init_method="mup", rope_dim=64,
+    sequence_mixer_blocks=[dict(sequence_mixer_type="softmax_attention", num_attention_heads=16), dict(sequence_mixer_type="mamba2"),
+                           dict(sequence_mixer_type="rnn"), dict(sequence_mixer_type="gru")],
+    mlp_blocks=[dict(activation_function="swiglu", mlp_type="MLP"),
+                dict(activation_function="swiglu", mlp_type="MoE", shared_intermediate_size=512),
+                dict(activation_function="swiglu", mlp_type="MLP"), dict(activation_function="swiglu", mlp_type="MLP")])
+
+_GROUPS = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+from lm_engine.optimization.params_group import get_mup_group_with_names, get_normal_group_with_names
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+from transformers import AutoModelForCausalLM
+with torch.device("meta"):
+    network = AutoModelForCausalLM.from_config(rm.GPTBaseConfig(**json.loads(sys.argv[2])))
+class Wrapper(torch.nn.Module):
+    def __init__(self, model):
+        super().__init__()
+        self.model, self.config = model, model.config
+    def has_teacher_model(self):
+        return False
+wrapper = Wrapper(network)
+arguments = {"lr": 3e-4, "weight_decay": 0.1}
+json.dump({"normal": get_normal_group_with_names(wrapper, arguments).get_param_names(),
+           "mup": get_mup_group_with_names(wrapper, arguments).get_param_names()}, open(sys.argv[3], "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_parameter_groups_are_those_of_the_reference(tmp_path):
+    """The hybrid model of the reference's own parameter-group test (attention, Mamba-2, RNN and GRU mixers, one MoE block with a
+    shared expert, muP initialisation; reference tests/training/params_group/training_config.yml): the reference's grouping
+    functions, run in a child process on its model, and this package's on its own model put the same parameter names, in
+    the same order, into the same groups, for the plain and for the muP method."""
+    import json
+
+    from lm_engine.enums import ParamsGroupMethod
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+    from lm_engine.optimization.params_group import get_param_groups_with_names
+
+    out = tmp_path / "groups.json"
+    subprocess.run([sys.executable, "-c", _GROUPS, REF, json.dumps(_HYBRID), str(out)], check=True, cwd=str(tmp_path),
+                   env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True)
+    theirs = json.loads(out.read_text())
+    with torch.device("meta"):
+        model = GPTBaseForCausalLM(GPTBaseConfig(**_HYBRID))
+    for key, method in (("normal", None), ("mup", ParamsGroupMethod.mup)):
+        mine = {group: [f"model.{name}" for name in names] for group, names in get_param_groups_with_names(model, method).items()}
+        assert mine == theirs[key], key
+    assert len(theirs["mup"]["mup"]) == 24 and len(theirs["normal"]["no_weight_decay"]) == 32
