@@ -237,3 +237,102 @@ def test_parameter_groups_are_those_of_the_reference(tmp_path):
         mine = {group: [f"model.{name}" for name in names] for group, names in get_param_groups_with_names(model, method).items()}
         assert mine == theirs[key], key
     assert len(theirs["mup"]["mup"]) == 24 and len(theirs["normal"]["no_weight_decay"]) == 32
+
+
+def _family_cases() -> dict:
+    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)
+    mamba2 = dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=128, num_heads=8, conv_kernel_size=4, num_groups=2, chunk_size=8)
+    latent = dict(sequence_mixer_type="multihead_latent_attention", num_attention_heads=4, query_compression_size=32,
+                  key_value_compression_size=32, head_dim=16)
+    convolution = dict(sequence_mixer_type="causal_convolution", in_channels=64, out_channels=64, kernel_size=3, num_groups=64,
+                       activation_function="silu")
+    mlp = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=False)
+
+    def config(first_mixer, position="rope", **extra):
+        made = dict(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type=position, normalization_function="rmsnorm",
+                    max_position_embeddings=64, tie_word_embeddings=False, sequence_mixer_blocks=[first_mixer, dict(attention)],
+                    mlp_blocks=[dict(mlp), dict(mlp)])
+        if position == "rope":
+            made["rope_dim"] = 16
+        made.update(extra)
+        return made
+
+    biased_and_moe = [dict(mlp_type="MLP", activation_function="gelu_pytorch_tanh", intermediate_size=128, add_bias=True),
+                      dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, shared_intermediate_size=32, num_experts=4,
+                           num_experts_per_tok=2, add_bias=False)]
+    # name -> (model family, config, tolerance of the logits); rnn / gru / stick-breaking are absent because the reference
+    # cannot evaluate them without its kernel packages
+    return {
+        "mamba2": ("gpt_base", config(mamba2), 1e-4),
+        "causal_convolution": ("gpt_base", config(convolution), 1e-6),
+        "latent_attention_nope": ("gpt_base", config(latent, "nope"), 1e-6),
+        "latent_attention_learned": ("gpt_base", config(latent, "learned_absolute"), 1e-6),
+        "mup_multipliers": ("gpt_base", config(attention, m_emb=12, m_width=9, m_residual=0.22, init_method="mup"), 1e-6),
+        "layernorm_bias_shared_expert": ("gpt_base", config(attention, "learned_absolute", normalization_function="layernorm",
+                                                            mlp_blocks=biased_and_moe), 1e-6),
+        "palm": ("palm", config(attention), 1e-6),
+        "ladder_residual": ("ladder_residual", config(attention), 1e-6),
+        "ladder_residual_mamba2": ("ladder_residual", config(mamba2), 1e-4),
+        "gpt_crosslayer": ("gpt_crosslayer", config(attention), 1e-6),
+        "gpt_crosslayer_shared": ("gpt_crosslayer", config(attention, sharing_pattern=[0, 0]), 1e-6),
+    }
+
+
+_FAMILIES = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm, disable_generation_cache
+from transformers import AutoModelForCausalLM
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+classes = {"gpt_base": rm.GPTBaseConfig, "palm": rm.PaLMConfig, "ladder_residual": rm.LadderResidualConfig, "gpt_crosslayer": rm.GPTCrossLayerConfig}
+for family in ("gpt_base", "palm", "ladder_residual"):  # classes without a constructor of their own
+    classes[family].__init__ = init
+cm.CommonConfig.__init__ = init  # reached through the constructor of the cross-layer config
+results = {}
+for name, (family, config, _) in json.loads(sys.argv[2]).items():
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(classes[family](**config))
+    model.eval()
+    ids = torch.randint(0, config["vocab_size"], (2, 16))
+    with disable_generation_cache(), torch.no_grad():
+        out = model(input_ids=ids, labels=ids, use_cache=False)
+    results[name] = {"sd": model.state_dict(), "ids": ids, "loss": out.loss, "logits": out.logits}
+torch.save(results, sys.argv[3])
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_every_family_the_reference_can_evaluate_on_cpu_gives_its_logits(tmp_path):
+    """Model families (gpt_base, palm, ladder_residual, gpt_crosslayer with and without shared keys / values) and mixers
+    (Mamba-2, causal convolution, multi-head latent attention, muP multipliers, LayerNorm + biases + an MoE block with a
+    shared expert): the reference's weights load key for key into this package's model of the same config, and the logits
+    and the loss are the reference's (bit-equal but for Mamba-2, whose chunked scan sums in another order)."""
+    import json
+
+    import lm_engine.hf_models as hm
+
+    cases = _family_cases()
+    out = tmp_path / "families.pt"
+    done = subprocess.run([sys.executable, "-c", _FAMILIES, REF, json.dumps(cases), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=900, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(out)
+    classes = {"gpt_base": (hm.GPTBaseConfig, hm.GPTBaseForCausalLM), "palm": (hm.PaLMConfig, hm.PaLMForCausalLM),
+               "ladder_residual": (hm.LadderResidualConfig, hm.LadderResidualForCausalLM),
+               "gpt_crosslayer": (hm.GPTCrossLayerConfig, hm.GPTCrossLayerForCausalLM)}
+    for name, (family, config, tolerance) in cases.items():
+        make_config, make_model = classes[family]
+        model = make_model(make_config(**config))
+        result = model.load_state_dict(theirs[name]["sd"], strict=True)
+        assert not result.missing_keys and not result.unexpected_keys, name
+        model.eval()
+        with torch.no_grad():
+            mine = model(input_ids=theirs[name]["ids"], labels=theirs[name]["ids"])
+        assert (mine.logits - theirs[name]["logits"]).abs().max().item() <= tolerance, name
+        assert abs(mine.loss.item() - theirs[name]["loss"].item()) <= 1e-5, name
