@@ -336,3 +336,49 @@ def test_every_family_the_reference_can_evaluate_on_cpu_gives_its_logits(tmp_pat
             mine = model(input_ids=theirs[name]["ids"], labels=theirs[name]["ids"])
         assert (mine.logits - theirs[name]["logits"]).abs().max().item() <= tolerance, name
         assert abs(mine.loss.item() - theirs[name]["loss"].item()) <= 1e-5, name
+
+
+_SCHEDULES = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+from lm_engine.enums import LRDecaySchedule
+from lm_engine.optimization.scheduler import _LR_SCHEDULER_CLASSES
+results = {}
+for name, case in json.loads(sys.argv[2]).items():
+    optimizer = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=case["lr"])
+    scheduler = _LR_SCHEDULER_CLASSES[LRDecaySchedule(case["style"])](optimizer, **case["arguments"])
+    results[name] = [scheduler._lr_lambda(step) for step in range(case["steps"])]
+json.dump(results, open(sys.argv[3], "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_learning_rate_schedules_follow_the_reference_step_by_step(tmp_path):
+    """Every decay style (constant, linear, cosine, exponential, power), with and without warm-up and constant phases, with an
+    explicit decay length and with the one implied by the number of training steps, evaluated past its end: the factor of
+    every step equals the one of the reference's scheduler classes (lm_engine/optimization/scheduler.py:56-196)."""
+    import json
+
+    from lm_engine.enums import LRDecaySchedule
+    from lm_engine.optimization.scheduler import PhasedSchedule
+
+    def arguments(warmup, constant, decay, total, floor, **extra):
+        return dict(num_warmup_steps=warmup, num_constant_steps=constant, num_decay_steps=decay, num_training_steps=total,
+                    lr_decay_factor=floor, **extra)
+
+    cases = {}
+    for style in ("linear", "cosine", "exponential"):
+        cases[f"{style}_phases"] = dict(style=style, lr=3e-4, steps=80, arguments=arguments(5, 7, 40, 60, 0.1))
+        cases[f"{style}_implied_length"] = dict(style=style, lr=3e-4, steps=80, arguments=arguments(0, 0, None, 60, 0.0))
+    cases["constant"] = dict(style="constant", lr=1e-3, steps=30, arguments=arguments(4, 0, 0, 20, 0.1))
+    cases["power"] = dict(style="power", lr=3e-4, steps=400, arguments=arguments(50, 0, None, 300, 0.1, a=4.6e-3, b=-0.51, c=16.0))
+    cases["power_below_the_peak"] = dict(style="power", lr=0.02, steps=60, arguments=arguments(10, 0, None, 50, 0.1, a=0.03, b=-0.51, c=1.0))
+    out = tmp_path / "schedules.json"
+    done = subprocess.run([sys.executable, "-c", _SCHEDULES, REF, json.dumps(cases), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    for name, case in cases.items():
+        schedule = PhasedSchedule(LRDecaySchedule(case["style"]), base_lr=case["lr"], **case["arguments"])
+        for step, expected in enumerate(theirs[name]):
+            assert abs(schedule(step) - expected) <= 1e-12 * max(1.0, abs(expected)), (name, step, schedule(step), expected)
