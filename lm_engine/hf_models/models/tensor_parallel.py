@@ -10,7 +10,7 @@ Layouts (tp = tensor-parallel size, r = rank):
     that the local activation splits the same way; the fused ``c_attn`` is sharded by whole key/value groups.
   * row-parallel linear: columns ``[r * in / tp, ...)``; the bias is replicated and added after the reduction.
   * embedding / LM head: vocabulary rows, the vocabulary padded to a multiple of 64.
-  * norms, router, ``wpe``, row-parallel biases and the multi-query ``kv_attn`` are replicated. Their gradients are
+  * norms, router, row-parallel biases and the multi-query ``kv_attn`` are replicated. Their gradients are
     partial sums whenever their input or their consumers are sharded; such parameters carry ``_tp_partial_grad`` and
     :func:`reduce_tensor_parallel_grads` sums them over the group before the optimizer step.
   * sequence parallelism: between the linears the activations hold ``tokens / tp`` rows.
@@ -271,8 +271,8 @@ class LMHead_TP(Embedding_TP):
 # attention
 class Attention_TP(Attention):
     """Heads are divided over the ranks; the attention itself is local. Grouped-query attention shards whole key/value
-    groups through the fused ``c_attn``; multi-query attention (one key/value head) keeps a column-parallel ``q_attn``
-    and a replicated ``kv_attn`` whose outputs form the local ``[q heads | k | v]`` row."""
+    groups through the fused ``c_attn``; multi-query attention (one key/value head) keeps a column-parallel ``c_attn.q_attn``
+    and a replicated ``c_attn.kv_attn`` whose outputs form the local ``[q heads | k | v]`` row."""
 
     def __init__(self, hidden_size: int, num_attention_heads: int, num_key_value_heads: int, attention_multiplier: float | None,
                  position_embedding_type: str, add_bias: bool, softmax_dropout: float, dropout: float, init_method: str,
@@ -303,9 +303,11 @@ class Attention_TP(Attention):
 
         std = initializer_range / math.sqrt(m_width) if init_method == "mup" else initializer_range
         if self.multi_query:
-            self.q_attn = ColumnParallelLinear(hidden_size, hidden_size, bias=add_bias, std=std, sequence_parallel=sequence_parallel)
-            self.kv_attn = ReplicatedLinear(hidden_size, 2 * self.head_dim, bias=add_bias, std=std, partial_grad="always")
-            first = [self.q_attn.weight, self.kv_attn.weight]
+            # parameter names as in the reference's tensor-parallel multi-query projection: `c_attn.q_attn`, `c_attn.kv_attn`
+            self.c_attn = nn.Module()
+            self.c_attn.q_attn = ColumnParallelLinear(hidden_size, hidden_size, bias=add_bias, std=std, sequence_parallel=sequence_parallel)
+            self.c_attn.kv_attn = ReplicatedLinear(hidden_size, 2 * self.head_dim, bias=add_bias, std=std, partial_grad="always")
+            first = [self.c_attn.q_attn.weight, self.c_attn.kv_attn.weight]
         else:
             self.c_attn = ColumnParallelLinear(hidden_size, hidden_size + 2 * num_key_value_heads * self.head_dim, bias=add_bias,
                                                std=std, sequence_parallel=sequence_parallel)
@@ -322,7 +324,7 @@ class Attention_TP(Attention):
     def forward(self, hidden_states: torch.Tensor, ctx, past_key_values=None) -> torch.Tensor:
         if self.multi_query:
             x = tp.column_parallel_input(hidden_states, self.sequence_parallel)
-            qkv = torch.cat([ops.linear(x, self.q_attn.weight, self.q_attn.bias), self.kv_attn(x)], dim=-1)
+            qkv = torch.cat([ops.linear(x, self.c_attn.q_attn.weight, self.c_attn.q_attn.bias), self.c_attn.kv_attn(x)], dim=-1)
         else:
             qkv = self.c_attn(hidden_states)
         out = self._forward_packed(qkv, ctx) if ctx.packed else self._forward_padded(qkv, ctx, past_key_values)
@@ -586,8 +588,10 @@ class BaseModelMixin_TP(PreTrainedModelMixin_TP, BaseModelMixin):
     def _setup_positional_encoding(self) -> None:
         if self.position_embedding_type == "learned_absolute":
             if self.is_first_stage:
-                self.wpe = ParameterizedEmbedding(self.config.max_position_embeddings, self.embed_dim, std=self.initializer_range)
-                mark_tp_partial_grad(self.wpe.weight, "sequence_parallel")
+                # rows divided over the ranks like the token table, which is also the layout of the reference's checkpoints
+                self.wpe = Embedding_TP(self.config.max_position_embeddings, self.embed_dim, std=self.initializer_range,
+                                        use_padding_free_transformer=self.use_padding_free_transformer,
+                                        sequence_parallel=self.sequence_parallel)
         else:
             super()._setup_positional_encoding()
 
@@ -597,11 +601,7 @@ class BaseModelMixin_TP(PreTrainedModelMixin_TP, BaseModelMixin):
     def embed(self, input_ids, inputs_embeds, position_ids, token_type_ids) -> torch.Tensor:
         x = self.wte(input_ids) if inputs_embeds is None else inputs_embeds
         if self.position_embedding_type == "learned_absolute":
-            pos = self.wpe(position_ids)
-            if self.sequence_parallel and tp.tp_world() > 1:
-                # this rank's tokens only; the gradient of the table is then this rank's share (summed later)
-                pos = pos.chunk(tp.tp_world(), dim=tp.token_dim(pos))[tp.tp_rank()]
-            x = x + pos
+            x = x + self.wpe(position_ids)  # already this rank's tokens under sequence parallelism
         if token_type_ids is not None:
             x = x + self.wte(token_type_ids)
         x = self.embedding_dropout(x)

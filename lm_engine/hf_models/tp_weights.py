@@ -38,8 +38,8 @@ def tensor_parallel_split_safetensor_slice(slice_, dim: int, start_end: tuple[in
 
 def _rule(config, name: str, tp_world: int) -> tuple[str, int, int]:
     """(kind, dim, parts) for a parameter of the unsharded model: kind in {"split", "vocab", "replicate", "mqa"}."""
-    if name.endswith(("wte.weight", "lm_head.weight")):
-        return "vocab", 0, 1
+    if name.endswith(("wte.weight", "lm_head.weight", "wpe.weight")):
+        return "vocab", 0, 1  # the position table is a padded, row-sharded embedding as well (as in the reference)
     match = re.search(r"\.h\.(\d+)\.(sequence_mixer|mlp_block)\.(\w+)\.(weight|bias)$", name)
     if match is None:
         return "replicate", 0, 1
@@ -67,6 +67,11 @@ def _rule(config, name: str, tp_world: int) -> tuple[str, int, int]:
 
 def _padded_vocab(vocab_size: int) -> int:
     return VOCAB_MULTIPLE * math.ceil(vocab_size / VOCAB_MULTIPLE)
+
+
+def _table_rows(config, name: str) -> int:
+    """Rows of an embedding table without its padding."""
+    return config.max_position_embeddings if name.endswith("wpe.weight") else config.vocab_size
 
 
 def _split_blocks(full: torch.Tensor, dim: int, parts: int, rank: int, world: int) -> torch.Tensor:
@@ -118,7 +123,7 @@ def shard_tensor(config, name: str, read, shape: tuple[int, ...], rank: int, wor
         q_rows = shape[0] - 2 * head_dim
         stride = q_rows // world
         suffix = name.rsplit(".", 1)[1]
-        base = name[: -len("c_attn." + suffix)]
+        base = name[: -len(suffix)]  # "...sequence_mixer.c_attn."
         return {base + "q_attn." + suffix: read((slice(rank * stride, (rank + 1) * stride),) + everything[1:]),
                 base + "kv_attn." + suffix: read((slice(q_rows, shape[0]),) + everything[1:])}
     block = shape[dim] // parts
@@ -170,7 +175,7 @@ def unshard_tensor_parallel_state_dicts(config, tensor_parallel_state_dicts: lis
             kv = [sd[key.replace(".q_attn.", ".kv_attn.")] for sd in tensor_parallel_state_dicts]
             if check_correctness:
                 assert all(torch.equal(kv[0], other) for other in kv[1:]), f"{name}: replicated kv_attn differs between ranks"
-            out[prefix + name.replace("q_attn." + suffix, "c_attn." + suffix)] = torch.cat(pieces + [kv[0]], dim=0)
+            out[prefix + name.replace("c_attn.q_attn." + suffix, "c_attn." + suffix)] = torch.cat(pieces + [kv[0]], dim=0)
             continue
         kind, dim, parts = _rule(config, name, world)
         if kind == "replicate":
@@ -178,7 +183,7 @@ def unshard_tensor_parallel_state_dicts(config, tensor_parallel_state_dicts: lis
                 assert all(torch.equal(pieces[0], other) for other in pieces[1:]), f"{name}: replicated tensor differs between ranks"
             out[key] = pieces[0]
         elif kind == "vocab":
-            out[key] = torch.cat(pieces, dim=0)[: config.vocab_size]
+            out[key] = torch.cat(pieces, dim=0)[: _table_rows(config, name)]
         else:
             blocks = [p.chunk(parts, dim=dim) for p in pieces]
             out[key] = torch.cat([torch.cat([blocks[r][b] for r in range(world)], dim=dim) for b in range(parts)], dim=dim)
@@ -198,13 +203,13 @@ def fix_unsharded_state_dict(config, state_dict: dict[str, torch.Tensor], tensor
         if ".q_attn." in name:
             suffix = name.rsplit(".", 1)[1]
             kv_key = key.replace(".q_attn.", ".kv_attn.")
-            out[key.replace("q_attn." + suffix, "c_attn." + suffix)] = torch.cat([state_dict[key], state_dict[kv_key]], dim=0)
+            out[key.replace("c_attn.q_attn." + suffix, "c_attn." + suffix)] = torch.cat([state_dict[key], state_dict[kv_key]], dim=0)
             del out[key], out[kv_key]
             continue
         kind, dim, parts = _rule(config, name, world)
         value = state_dict[key]
         if kind == "vocab":
-            out[key] = value[: config.vocab_size]
+            out[key] = value[: _table_rows(config, name)]
         elif kind == "split" and parts > 1:
             per_rank = value.chunk(world, dim=dim)
             out[key] = torch.cat([torch.cat([p.chunk(parts, dim=dim)[b] for p in per_rank], dim=dim) for b in range(parts)], dim=dim)

@@ -382,3 +382,91 @@ def test_learning_rate_schedules_follow_the_reference_step_by_step(tmp_path):
         schedule = PhasedSchedule(LRDecaySchedule(case["style"]), base_lr=case["lr"], **case["arguments"])
         for step, expected in enumerate(theirs[name]):
             assert abs(schedule(step) - expected) <= 1e-12 * max(1.0, abs(expected)), (name, step, schedule(step), expected)
+
+
+_TP_WEIGHTS = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+from lm_engine.hf_models.models.gpt_base_TP.weights import (fix_gpt_base_unsharded_state_dict, get_gpt_base_model_parallel_state_dict,
+                                                            unshard_gpt_base_tensor_parallel_state_dicts)
+from lm_engine.utils import ProcessGroupManager, SafeTensorsWeightsManager
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+work, world = sys.argv[3], int(sys.argv[4])
+config = rm.GPTBaseConfig(**json.loads(sys.argv[2]))
+shards = []
+for rank in range(world):
+    with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world), ProcessGroupManager.set_dummy_tensor_parallel_rank(rank):
+        shards.append(get_gpt_base_model_parallel_state_dict(config, SafeTensorsWeightsManager(work + "/model.safetensors"), 1, 0))
+mine = torch.load(work + "/shards.pt")
+with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world):
+    whole = unshard_gpt_base_tensor_parallel_state_dicts(config, mine["shards"])
+    fixed = fix_gpt_base_unsharded_state_dict(config, dict(mine["concatenated"]), world)
+torch.save({"shards": shards, "whole": whole, "fixed": fixed}, work + "/theirs.pt")
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+@pytest.mark.parametrize("key_value_heads", [1, 2, 4])
+def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path, key_value_heads):
+    """Multi-query, grouped-query and multi-head attention with biases, a gated MLP with biases, a gated MoE block, learned
+    positions and a vocabulary that needs padding, at tensor-parallel size 2: the per-rank state dicts cut by this package
+    and by the reference (from the same safetensors file) are equal key for key and bit for bit; each side's unsharding of
+    the other side's shards gives back the original weights; so does each side's repair of the rank-order concatenation
+    (the form a tensor-parallel checkpoint is read back in)."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+    from lm_engine.hf_models.tp_weights import _rule, fix_unsharded_state_dict, shard_state_dict, unshard_tensor_parallel_state_dicts
+
+    world = 2
+    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=key_value_heads, add_bias=True)
+    made = dict(vocab_size=250, hidden_size=64, num_layers=2, position_embedding_type="learned_absolute", max_position_embeddings=32,
+                normalization_function="layernorm", tie_word_embeddings=True, sequence_mixer_blocks=[attention, dict(attention)],
+                mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=True),
+                            dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                                 add_bias=False)])
+    torch.manual_seed(3)
+    model = GPTBaseForCausalLM(GPTBaseConfig(**made))
+    config = model.config
+    original = {k: v.detach().clone().contiguous() for k, v in model.state_dict().items() if k != "lm_head.weight"}
+    save_file(original, str(tmp_path / "model.safetensors"))
+    shards = [shard_state_dict(config, original, rank, world) for rank in range(world)]
+
+    def dimension(key: str) -> int | None:  # along which a rank-order concatenation joins the pieces of a local tensor
+        if ".kv_attn." in key:
+            return None
+        if ".q_attn." in key:
+            return 0
+        kind, dim, _ = _rule(config, key, world)
+        return None if kind == "replicate" else dim
+
+    concatenated = {key: shards[0][key] if dimension(key) is None else torch.cat([s[key] for s in shards], dim=dimension(key))
+                    for key in shards[0]}
+    torch.save({"shards": shards, "concatenated": concatenated}, tmp_path / "shards.pt")
+    done = subprocess.run([sys.executable, "-c", _TP_WEIGHTS, REF, json.dumps(made), str(tmp_path), str(world)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(tmp_path / "theirs.pt")
+
+    def same(a: dict, b: dict, skip=()) -> None:
+        assert set(a) == set(b), (sorted(set(a) - set(b)), sorted(set(b) - set(a)))
+        for key in a:
+            if key not in skip:
+                assert a[key].shape == b[key].shape and torch.equal(a[key], b[key]), key
+
+    for rank in range(world):
+        same(shards[rank], theirs["shards"][rank])
+    same(theirs["whole"], original)
+    same(unshard_tensor_parallel_state_dicts(config, theirs["shards"]), original)
+    same(fix_unsharded_state_dict(config, concatenated, world), original)
+    same(theirs["fixed"], original, skip=("transformer.wpe.weight",))  # the reference leaves the padding of the position table in
