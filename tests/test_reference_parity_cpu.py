@@ -470,3 +470,93 @@ def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path, key_value_he
     same(unshard_tensor_parallel_state_dicts(config, theirs["shards"]), original)
     same(fix_unsharded_state_dict(config, concatenated, world), original)
     same(theirs["fixed"], original, skip=("transformer.wpe.weight",))  # the reference leaves the padding of the position table in
+
+
+# the same scenario text runs against the reference (child process) and against this package (here): only the package that
+# `lm_engine` resolves to differs
+_DATA_SCENARIO = r"""
+import torch
+from lm_engine.data.base import BaseDataset, BlendedDatasets
+from lm_engine.data.sampler import BlendedDistributedSampler
+from lm_engine.data.utils import collate_fn
+from lm_engine.enums import DatasetSplit, LossMask, Mode
+
+class Tokenizer:
+    eos_token_id = 2
+    def __call__(self, text, add_special_tokens=False):
+        return {"input_ids": [3 + sum(map(ord, word)) % 97 for word in text.split()]}
+
+class Words(BaseDataset):
+    def __init__(self, name, count, mode, encoder_decoder=False, limits=(None, None), formats=("__input__", "__output__")):
+        super().__init__(class_args={}, split=DatasetSplit.train, mode=mode, tokenizer=Tokenizer(), is_encoder_decoder=encoder_decoder,
+                         data_name=name, input_format=formats[0], output_format=formats[1], max_input_tokens=limits[0],
+                         max_output_tokens=limits[1])
+        for i in range(count):
+            prompt = self.construct_input_from_format(" ".join(f"{name}{i}w{j}" for j in range(1 + (i * 5) % 7)))
+            answer = self.construct_output_from_format(" ".join(f"{name}{i}a{j}" for j in range(1 + (i * 3) % 5)))
+            self.examples.append(self.get_input_output_token_ids(prompt, answer))
+
+def scenario():
+    results = {}
+    # tokenisation: formats, trimming, end-of-sequence tokens, with and without outputs, decoder-only and encoder-decoder
+    for label, kwargs in {
+        "plain": dict(mode=Mode.training),
+        "formatted": dict(mode=Mode.training, formats=("question: __input__ answer:", "__output__ .")),
+        "trimmed": dict(mode=Mode.training, limits=(3, 3)),
+        "inference": dict(mode=Mode.inference, limits=(4, None)),
+        "encoder_decoder": dict(mode=Mode.training, encoder_decoder=True, limits=(4, 3)),
+    }.items():
+        results["examples_" + label] = Words("x", 9, **kwargs).examples
+    # sampling order of a blend, per rank and epoch
+    blend = BlendedDatasets([Words("a", 7, Mode.training), Words("b", 13, Mode.training), Words("c", 5, Mode.training)], DatasetSplit.train)
+    results["blend_length"] = len(blend)
+    results["blend_items"] = [blend[i] for i in (0, 6, 7, 19, 20, 24)]
+    for shuffle in (False, True):
+        for rank in range(4):
+            sampler = BlendedDistributedSampler(blend, data_sampling_ratios=[3, 1, 2], num_replicas=4, rank=rank, shuffle=shuffle, seed=11)
+            results[f"order_shuffle{int(shuffle)}_rank{rank}"] = [list(sampler), list(sampler)]
+    sampler = BlendedDistributedSampler(blend, data_sampling_ratios=[1, 1, 1], num_replicas=2, rank=1, shuffle=True, seed=5, drop_last=True)
+    results["order_drop_last"] = list(sampler)
+    # collation
+    batch = [dict(e) for e in Words("y", 5, Mode.training).examples]
+    copy = lambda: [dict(input=list(e["input"]), output=list(e["output"])) for e in batch]
+    def tensors(made):
+        return {k: (v.tolist() if isinstance(v, torch.Tensor) else v) for k, v in made.items()}
+    cpu = torch.device("cpu")
+    results["collate_padded_output_only"] = tensors(collate_fn(copy(), Mode.training, LossMask.output_only, 2, False, False, pad_to_multiple_of=4, device=cpu))
+    results["collate_packed_output_only"] = tensors(collate_fn(copy(), Mode.training, LossMask.output_only, 2, False, True, pad_to_multiple_of=8, device=cpu))
+    results["collate_packed_no_mask"] = tensors(collate_fn(copy(), Mode.training, LossMask.no_mask, 2, False, True, device=cpu))
+    results["collate_inference"] = tensors(collate_fn([dict(input=list(e["input"])) for e in batch], Mode.inference, LossMask.output_only, 2, False, False, device=cpu))
+    pairs = Words("z", 4, Mode.training, encoder_decoder=True).examples
+    results["collate_encoder_decoder"] = tensors(collate_fn([dict(input=list(e["input"]), output=list(e["output"])) for e in pairs], Mode.training,
+                                                            LossMask.output_only, 2, True, False, device=cpu))
+    return results
+"""
+
+_DATA_CHILD = r"""
+import json, sys
+sys.path.insert(0, sys.argv[1])
+exec(sys.argv[2])
+json.dump(scenario(), open(sys.argv[3], "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_finetuning_data_path_matches_the_reference(tmp_path):
+    """Example construction (formats, trimming, end-of-sequence handling, inference and encoder-decoder forms), the order in
+    which a blend of three datasets is sampled (with and without shuffling, four ranks, two epochs, drop_last) and the collated
+    batches (padded, padding-free with padding of the token count, no-mask labels, inference, encoder-decoder) are those
+    of the reference's classes, produced by the same scenario text run against either package."""
+    import json
+
+    out = tmp_path / "theirs.json"
+    done = subprocess.run([sys.executable, "-c", _DATA_CHILD, REF, _DATA_SCENARIO, str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    scope: dict = {}
+    exec(_DATA_SCENARIO, scope)
+    mine = json.loads(json.dumps(scope["scenario"]()))
+    assert set(mine) == set(theirs)
+    for key in theirs:
+        assert mine[key] == theirs[key], key
