@@ -560,3 +560,61 @@ def test_finetuning_data_path_matches_the_reference(tmp_path):
     assert set(mine) == set(theirs)
     for key in theirs:
         assert mine[key] == theirs[key], key
+
+
+_TRAINING = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+from transformers import AutoModelForCausalLM
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+config = json.loads(sys.argv[2])
+torch.manual_seed(0)
+model = AutoModelForCausalLM.from_config(rm.GPTBaseConfig(**config))
+model.train()
+ids = torch.randint(0, config["vocab_size"], (2, 16))
+weights = {k: v.detach().clone() for k, v in model.state_dict().items()}
+out = model(input_ids=ids, labels=ids, use_cache=False)
+out.loss.backward()
+torch.save({"sd": weights, "ids": ids, "loss": out.loss.detach(), "aux_loss": out.aux_loss.detach(),
+            "grads": {n: p.grad for n, p in model.named_parameters()}}, sys.argv[3])
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_training_loss_with_router_loss_and_all_gradients_match_the_reference(tmp_path):
+    """Training mode, an MoE block with a shared expert and a router auxiliary-loss coefficient: the total loss, the auxiliary
+    loss and the gradient of every parameter equal the reference's from the same weights and tokens."""
+    import json
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)
+    made = dict(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", normalization_function="rmsnorm",
+                tie_word_embeddings=False, router_aux_loss_coef=0.02, sequence_mixer_blocks=[attention, dict(attention)],
+                mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=False),
+                            dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, shared_intermediate_size=32,
+                                 num_experts=4, num_experts_per_tok=2, add_bias=False)])
+    out = tmp_path / "training.pt"
+    done = subprocess.run([sys.executable, "-c", _TRAINING, REF, json.dumps(made), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(out)
+    model = GPTBaseForCausalLM(GPTBaseConfig(**made))
+    model.load_state_dict(theirs["sd"], strict=True)
+    model.train()
+    mine = model(input_ids=theirs["ids"], labels=theirs["ids"])
+    assert abs(mine.loss.item() - theirs["loss"].item()) <= 1e-6
+    assert abs(float(mine.aux_loss.detach()) - theirs["aux_loss"].item()) <= 1e-6
+    mine.loss.backward()
+    for name, parameter in model.named_parameters():
+        expected = theirs["grads"][name]
+        assert expected is not None and parameter.grad is not None, name
+        assert (parameter.grad - expected).abs().max().item() <= 1e-5 * expected.abs().max().item() + 1e-9, name
