@@ -618,3 +618,82 @@ def test_training_loss_with_router_loss_and_all_gradients_match_the_reference(tm
         expected = theirs["grads"][name]
         assert expected is not None and parameter.grad is not None, name
         assert (parameter.grad - expected).abs().max().item() <= 1e-5 * expected.abs().max().item() + 1e-9, name
+
+
+_GREEDY = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm, disable_generation_cache
+from transformers import AutoModelForCausalLM
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+results = {}
+for name, case in json.loads(sys.argv[2]).items():
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(rm.GPTBaseConfig(**case["config"]))
+    model.eval()
+    ids = torch.randint(3, 256, (2, 7))
+    mask = torch.ones_like(ids)
+    mask[1, : case["padding"]] = 0
+    sequence, attention, scores = ids, mask, []
+    # the reference's own `generate` does not run against the installed transformers; greedy decoding by evaluating the whole
+    # prefix again for every token needs its forward pass only
+    with torch.no_grad(), disable_generation_cache():
+        for _ in range(case["new_tokens"]):
+            logits = model(input_ids=sequence, attention_mask=attention, use_cache=False).logits[:, -1]
+            scores.append(logits)
+            sequence = torch.cat([sequence, logits.argmax(-1, keepdim=True)], dim=1)
+            attention = torch.cat([attention, torch.ones_like(attention[:, :1])], dim=1)
+    results[name] = {"sd": model.state_dict(), "ids": ids, "mask": mask, "sequences": sequence, "scores": torch.stack(scores)}
+torch.save(results, sys.argv[3])
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_cached_generation_repeats_the_reference_s_greedy_decoding(tmp_path):
+    """``generate`` of this package (prefill + one token at a time from the KV / Mamba-2 caches) against greedy decoding
+    with the reference's forward pass over the whole prefix: the same tokens and the same scores, for a left-padded batch
+    through attention + MoE layers and for an unpadded batch through a Mamba-2 layer. (With left padding the reference's
+    Mamba-2 block does not reproduce its own unpadded result, so that combination has nothing to compare with.)"""
+    import json
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False)
+    mamba2 = dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=128, num_heads=8, conv_kernel_size=4, num_groups=2, chunk_size=8)
+    mlps = [dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=False),
+            dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, num_experts=4, num_experts_per_tok=2, add_bias=False)]
+
+    def config(first):
+        # end-of-sequence id outside the sampled range is not possible with 256 tokens: decoding is compared up to the first one
+        return dict(vocab_size=256, hidden_size=64, num_layers=2, position_embedding_type="rope", rope_dim=16, normalization_function="rmsnorm",
+                    tie_word_embeddings=False, bos_token_id=0, eos_token_id=1, pad_token_id=2, sequence_mixer_blocks=[first, dict(attention)],
+                    mlp_blocks=mlps)
+
+    cases = {"attention_left_padded": dict(config=config(attention), padding=3, new_tokens=9),
+             "mamba2": dict(config=config(mamba2), padding=0, new_tokens=9)}
+    out = tmp_path / "greedy.pt"
+    done = subprocess.run([sys.executable, "-c", _GREEDY, REF, json.dumps(cases), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(out)
+    for name, case in cases.items():
+        data = theirs[name]
+        model = GPTBaseForCausalLM(GPTBaseConfig(**case["config"]))
+        model.load_state_dict(data["sd"], strict=True)
+        model.eval()
+        made = model.generate(input_ids=data["ids"], attention_mask=data["mask"], max_new_tokens=case["new_tokens"], do_sample=False,
+                              return_dict_in_generate=True, output_scores=True)
+        prompt = data["ids"].shape[1]
+        for row in range(data["ids"].shape[0]):
+            expected = data["sequences"][row, prompt:].tolist()
+            upto = expected.index(1) + 1 if 1 in expected else len(expected)  # this package stops a row at its end-of-sequence token
+            assert made.sequences[row, prompt : prompt + upto].tolist() == expected[:upto], (name, row)
+            for step in range(min(upto, len(made.scores))):
+                assert (made.scores[step][row] - data["scores"][step][row]).abs().max().item() <= 1e-4, (name, row, step)
