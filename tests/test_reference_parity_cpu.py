@@ -697,3 +697,83 @@ def test_cached_generation_repeats_the_reference_s_greedy_decoding(tmp_path):
             assert made.sequences[row, prompt : prompt + upto].tolist() == expected[:upto], (name, row)
             for step in range(min(upto, len(made.scores))):
                 assert (made.scores[step][row] - data["scores"][step][row]).abs().max().item() <= 1e-4, (name, row, step)
+
+
+_SCHEMA = r"""
+import enum, json, typing
+import lm_engine.arguments as arguments
+from pydantic import BaseModel
+
+def fields_of(cls, seen):
+    out = {}
+    for name, field in cls.model_fields.items():
+        nested = None
+        for outer in [field.annotation, *typing.get_args(field.annotation)]:
+            for inner in [outer, *typing.get_args(outer)]:
+                if isinstance(inner, type) and issubclass(inner, BaseModel):
+                    nested = inner
+        default = field.default_factory() if field.default_factory is not None else field.default
+        if isinstance(default, enum.Enum):
+            default = default.value
+        if isinstance(default, BaseModel):
+            default = "<arguments>"
+        try:
+            json.dumps(default)
+        except TypeError:
+            default = repr(default)
+        out[name] = {"default": default, "required": field.is_required()}
+        if nested is not None and nested not in seen:
+            out[name]["fields"] = fields_of(nested, seen | {nested})
+    return out
+
+def schema():
+    return {name: fields_of(getattr(arguments, name), set())
+            for name in ("TrainingArgs", "InferenceArgs", "UnshardingArgs", "DistillationArgs")}
+"""
+
+_SCHEMA_CHILD = r"""
+import json, sys
+sys.path.insert(0, sys.argv[1])
+exec(sys.argv[2])
+json.dump(schema(), open(sys.argv[3], "w"))
+"""
+
+# keys this package adds to the reference's schema (all optional)
+_ADDED_KEYS = {"fp8_recipe", "expert_parallel_world_size", "fused_collectives", "expert_capacity_factor", "keep_parameters_gathered", "strict"}
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_argument_schema_accepts_every_key_of_the_reference_with_its_default(tmp_path):
+    """The four argument trees (training, inference, unsharding, distillation), walked recursively on both sides: every key
+    of the reference exists here, is required or optional alike and has the same default, so a YAML file written for the
+    reference means the same thing here; the only keys on top are the listed optional ones."""
+    import json
+
+    out = tmp_path / "schema.json"
+    done = subprocess.run([sys.executable, "-c", _SCHEMA_CHILD, REF, _SCHEMA, str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    scope: dict = {}
+    exec(_SCHEMA, scope)
+    mine = json.loads(json.dumps(scope["schema"]()))
+    problems, added = [], set()
+
+    def compare(a: dict, b: dict, path: str) -> None:
+        for key, entry in a.items():
+            if key not in b:
+                problems.append(f"missing: {path}{key}")
+                continue
+            if (entry["default"], entry["required"]) != (b[key]["default"], b[key]["required"]):
+                problems.append(f"default of {path}{key}: {entry['default']!r} there, {b[key]['default']!r} here")
+            if "fields" in entry:
+                if "fields" not in b[key]:
+                    problems.append(f"not a group here: {path}{key}")
+                else:
+                    compare(entry["fields"], b[key]["fields"], f"{path}{key}.")
+        added.update(key for key in b if key not in a)
+
+    for name in theirs:
+        compare(theirs[name], mine[name], name + ".")
+    assert not problems, problems
+    assert added <= _ADDED_KEYS, added - _ADDED_KEYS
