@@ -777,3 +777,45 @@ def test_argument_schema_accepts_every_key_of_the_reference_with_its_default(tmp
         compare(theirs[name], mine[name], name + ".")
     assert not problems, problems
     assert added <= _ADDED_KEYS, added - _ADDED_KEYS
+
+
+_MODEL_SCHEMA = r"""
+import importlib, inspect
+import lm_engine.hf_models.config as base
+
+def model_schema():
+    try:  # the reference keeps the block arguments in submodules of a package
+        modules = [importlib.import_module("lm_engine.hf_models.config.mlp"), importlib.import_module("lm_engine.hf_models.config.sequence_mixer")]
+    except ImportError:
+        modules = [base]
+    out = {}
+    for module in modules:
+        for name, cls in vars(module).items():
+            if name.startswith("_") and hasattr(cls, "model_fields"):
+                out[name] = {key: "<required>" if field.is_required() else repr(field.default_factory() if field.default_factory else field.default)
+                             for key, field in cls.model_fields.items()}
+    signature = inspect.signature(base.CommonConfig.__init__)
+    out["CommonConfig"] = {key: repr(parameter.default) for key, parameter in signature.parameters.items() if key not in ("self", "kwargs")}
+    return out
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_model_config_takes_the_reference_s_keys_and_defaults(tmp_path):
+    """Constructor arguments of the common model config and the argument classes of every sequence-mixer and MLP block type:
+    the same names with the same defaults on both sides."""
+    import json
+
+    out = tmp_path / "model_schema.json"
+    child = "import json, sys\nsys.path.insert(0, sys.argv[1])\nexec(sys.argv[2])\njson.dump(model_schema(), open(sys.argv[3], 'w'))\n"
+    done = subprocess.run([sys.executable, "-c", child, REF, _MODEL_SCHEMA, str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    scope: dict = {}
+    exec(_MODEL_SCHEMA, scope)
+    mine = scope["model_schema"]()
+    assert len(theirs) == 10 and len(theirs["CommonConfig"]) > 20  # nine block argument classes and the config itself
+    for name, fields in theirs.items():
+        assert name in mine, name
+        assert mine[name] == fields, (name, {k: (v, mine[name].get(k)) for k, v in fields.items() if mine[name].get(k) != v})
