@@ -83,7 +83,7 @@ def __getattr__(name: str):
         "BlendedDistributedSampler": ".sampler", "ResumableDataLoader": ".dataloader",
         "DispatchingDataLoader": ".dataloader", "AlpacaDataset": ".instruction_tuning", "DollyDataset": ".instruction_tuning",
         "SlimOrcaDataset": ".instruction_tuning", "DebugDataset": ".debug", "HuggingFaceDataset": ".huggingface",
-        "SST2Dataset": ".sst2",
+        "SST2Dataset": ".sst2", "get_ibm_dataloaders": ".ibm",
     }
     if name in lazy:
         return getattr(importlib.import_module(lazy[name], __name__), name)

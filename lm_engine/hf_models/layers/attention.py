@@ -49,6 +49,12 @@ def split_query_key_value_tensor_for_attention(qkv: torch.Tensor, num_heads: int
     return q.reshape(-1, *rest), k.reshape(-1, *rest), v.reshape(-1, *rest)
 
 
+def get_attention_head_type(num_attention_heads: int, num_key_value_heads: int) -> str:
+    """"mha" (a key/value head per query head), "mqa" (one key/value head) or "gqa" (anything between); the names the
+    tensor-parallel weight layout and the conversion tools go by."""
+    return {1: "mqa", num_attention_heads: "mha"}.get(num_key_value_heads, "gqa")  # one head of each kind counts as "mha"
+
+
 def repeat_key_value(x: torch.Tensor, num_heads: int, num_key_value_heads: int) -> torch.Tensor:
     """``[b, hkv, s, d] -> [b, hq, s, d]`` by repeating each key/value head for its query group."""
     g = num_heads // num_key_value_heads

@@ -35,6 +35,17 @@ def _std(initializer_range: float, init_method: str, m_width: float | None, dept
     return std
 
 
+def interleave_up_gate_tensor_for_mlp(up_weight: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor:
+    """The fused ``c_fc`` of a gated MLP: rows ``[up ; gate]``."""
+    return torch.cat((up_weight, gate_weight), dim=0)
+
+
+def split_up_gate_tensor_for_mlp(c_fc_weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of :func:`interleave_up_gate_tensor_for_mlp`."""
+    half = c_fc_weight.shape[0] // 2
+    return c_fc_weight[:half], c_fc_weight[half:]
+
+
 class MLP(nn.Module):
     def __init__(self, hidden_size: int, intermediate_size: int, activation_function: str, add_bias: bool,
                  dropout: float, init_method: str, initializer_range: float, m_width: float | None,

@@ -309,3 +309,34 @@ def export_to_huggingface(pretrained_model_name_or_path: str, save_path: str, mo
     hf_config.save_pretrained(save_path)
     if tokenizer is not None:
         tokenizer.save_pretrained(save_path, legacy_format=False)
+
+
+def _family_entry_points() -> None:
+    """``import_from_huggingface_<family>`` / ``export_to_huggingface_<family>`` for every supported architecture, the names
+    the reference exports (lm_engine/hf_models/model_conversion/__init__.py): the import reads the architecture from the
+    checkpoint and refuses another one than the name says, the export fixes the target architecture."""
+
+    def importer(family: str):
+        def import_one(pretrained_model_name_or_path: str, save_path: str) -> None:
+            hf_config, _, _ = download_repo(pretrained_model_name_or_path)
+            expected = "gpt_bigcode" if family == "bigcode" else family
+            if hf_config.model_type != expected:
+                raise ValueError(f"the checkpoint is a {hf_config.model_type} model, not {expected}")
+            import_from_huggingface(pretrained_model_name_or_path, save_path)
+
+        import_one.__name__ = import_one.__qualname__ = f"import_from_huggingface_{family}"
+        return import_one
+
+    def exporter(family: str):
+        def export_one(pretrained_model_name_or_path: str, save_path: str) -> None:
+            export_to_huggingface(pretrained_model_name_or_path, save_path, "gpt_bigcode" if family == "bigcode" else family)
+
+        export_one.__name__ = export_one.__qualname__ = f"export_to_huggingface_{family}"
+        return export_one
+
+    for family in ("bigcode",) + _LLAMA_LIKE:
+        globals()[f"import_from_huggingface_{family}"] = importer(family)
+        globals()[f"export_to_huggingface_{family}"] = exporter(family)
+
+
+_family_entry_points()

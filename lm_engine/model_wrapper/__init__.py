@@ -66,3 +66,14 @@ def get_model_container(args, mode: Mode) -> ModelContainer:
     with enable_kernels(args.kernel_args.kernels):
         wrappers = [cls(**kwargs, pipeline_stage_id=stage) for stage in get_pipeline_stage_ids_on_current_rank(num_stages)]
     return ModelContainer(wrappers)
+
+
+def __getattr__(name: str):
+    """The wrapper classes of the other tuning methods and the input broadcast, resolved on first use."""
+    import importlib
+
+    lazy = {"ModelWrapperForFinetuning": ".finetuning", "ModelWrapperForDistillation": ".distillation",
+            "broadcast_tensor_parallel_input": ".utils"}
+    if name in lazy:
+        return getattr(importlib.import_module(lazy[name], __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
