@@ -216,7 +216,22 @@ class ProcessGroupManager:
     @staticmethod
     def get_tensor_parallel_first_rank() -> int:
         """Global rank of the member with tp-rank 0 in this rank's tensor parallel group."""
+        if "tp_first_rank" in _State.dummy:
+            return _State.dummy["tp_first_rank"]
         return dist.get_process_group_ranks(ProcessGroupManager.get_tensor_parallel_group())[0]
+
+    @staticmethod
+    @contextmanager
+    def set_dummy_tensor_parallel_first_rank(rank: int):
+        previous = _State.dummy.get("tp_first_rank")
+        _State.dummy["tp_first_rank"] = rank
+        try:
+            yield
+        finally:
+            if previous is None:
+                _State.dummy.pop("tp_first_rank", None)
+            else:
+                _State.dummy["tp_first_rank"] = previous
 
     @staticmethod
     @contextmanager
@@ -316,6 +331,16 @@ class ProcessGroupManager:
     @staticmethod
     def get_sharding_world_size() -> int:
         return 1 if _State.mesh is None else _State.mesh["fsdp"].size()
+
+    @staticmethod
+    def get_data_parallel_replication_world_size() -> int:
+        """The reference's name for :meth:`get_replication_world_size`."""
+        return ProcessGroupManager.get_replication_world_size()
+
+    @staticmethod
+    def get_data_parallel_sharding_world_size() -> int:
+        """The reference's name for :meth:`get_sharding_world_size`."""
+        return ProcessGroupManager.get_sharding_world_size()
 
     @staticmethod
     def get_sharding_rank() -> int:

@@ -863,3 +863,57 @@ def test_public_names_of_the_reference_resolve_here(tmp_path):
         if gone:
             missing[name] = gone
     assert not missing, missing
+
+
+_MEMBERS = r"""
+import importlib, inspect, json, sys
+sys.path.insert(0, sys.argv[1])
+found = {}
+for module_name, classes in json.loads(sys.argv[2]).items():
+    module = importlib.import_module(module_name)
+    for class_name in classes:
+        cls = getattr(module, class_name)
+        names = []
+        for name, _ in inspect.getmembers(cls):
+            if name.startswith("_"):
+                continue
+            owner = next((base for base in cls.__mro__ if name in vars(base)), None)
+            if owner is not None and owner.__module__.startswith("lm_engine"):  # not what torch / transformers / pydantic bring along
+                names.append(name)
+        found[class_name] = names
+json.dump(found, open(sys.argv[3], "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_public_methods_of_the_reference_s_main_classes_exist_here(tmp_path):
+    """Process-group manager (every getter and every ``set_dummy_*`` context manager), communication helpers, step tracker,
+    experiment tracker, metrics dict, safetensors manager, containers, model wrappers, generation cache, datasets, sampler and
+    data loaders: every public method or attribute that the reference's class defines is there under the same name."""
+    import importlib
+    import json
+
+    classes = {"lm_engine.utils": ["ProcessGroupManager", "StepTracker", "ExperimentsTracker", "MetricsTrackingDict", "SafeTensorsWeightsManager",
+                                   "ProgressBar", "BaseArgs"],
+               "lm_engine.communication": ["Communication"],
+               "lm_engine.containers": ["ModelContainer", "OptimizerContainer", "LRSchedulerContainer", "BackwardHookOptimizerContainer"],
+               "lm_engine.model_wrapper": ["ModelWrapper", "ModelWrapperForPretraining", "ModelWrapperForFinetuning", "ModelWrapperForDistillation"],
+               "lm_engine.hf_models": ["GPTBaseForCausalLM", "GPTBaseModel"], "lm_engine.hf_models.cache": ["GenerationCache"],
+               "lm_engine.data": ["ResumableDataLoader", "DispatchingDataLoader", "BlendedDatasets", "BaseDataset", "BlendedDistributedSampler"]}
+    out = tmp_path / "members.json"
+    done = subprocess.run([sys.executable, "-c", _MEMBERS, REF, json.dumps(classes), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    assert len(theirs["ProcessGroupManager"]) > 25
+    # set-up steps of the reference's wrappers / model that happen inside the constructors here
+    internal = {"ModelWrapperForPretraining": {"reset_parameters"}, "ModelWrapperForDistillation": {"reset_parameters"}, "GPTBaseModel": {"mask_value"}}
+    missing = {}
+    for module_name, names in classes.items():
+        module = importlib.import_module(module_name)
+        for class_name in names:
+            cls = getattr(module, class_name)
+            gone = [name for name in theirs[class_name] if not hasattr(cls, name) and name not in internal.get(class_name, ())]
+            if gone:
+                missing[class_name] = gone
+    assert not missing, missing
