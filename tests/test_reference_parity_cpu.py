@@ -399,23 +399,23 @@ def init(self, *a, **k):
     if isinstance(rope, dict) and "factor" not in rope:
         self.__dict__["rope_parameters"] = None
 rm.GPTBaseConfig.__init__ = init
-work, world = sys.argv[3], int(sys.argv[4])
-config = rm.GPTBaseConfig(**json.loads(sys.argv[2]))
-shards = []
-for rank in range(world):
-    with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world), ProcessGroupManager.set_dummy_tensor_parallel_rank(rank):
-        shards.append(get_gpt_base_model_parallel_state_dict(config, SafeTensorsWeightsManager(work + "/model.safetensors"), 1, 0))
-mine = torch.load(work + "/shards.pt")
-with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world):
-    whole = unshard_gpt_base_tensor_parallel_state_dicts(config, mine["shards"])
-    fixed = fix_gpt_base_unsharded_state_dict(config, dict(mine["concatenated"]), world)
-torch.save({"shards": shards, "whole": whole, "fixed": fixed}, work + "/theirs.pt")
+world = int(sys.argv[3])
+for work, made in json.loads(sys.argv[2]).items():
+    config = rm.GPTBaseConfig(**made)
+    shards = []
+    for rank in range(world):
+        with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world), ProcessGroupManager.set_dummy_tensor_parallel_rank(rank):
+            shards.append(get_gpt_base_model_parallel_state_dict(config, SafeTensorsWeightsManager(work + "/model.safetensors"), 1, 0))
+    mine = torch.load(work + "/shards.pt")
+    with ProcessGroupManager.set_dummy_tensor_parallel_world_size(world):
+        whole = unshard_gpt_base_tensor_parallel_state_dicts(config, mine["shards"])
+        fixed = fix_gpt_base_unsharded_state_dict(config, dict(mine["concatenated"]), world)
+    torch.save({"shards": shards, "whole": whole, "fixed": fixed}, work + "/theirs.pt")
 """
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
-@pytest.mark.parametrize("key_value_heads", [1, 2, 4])
-def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path, key_value_heads):
+def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path):
     """Multi-query, grouped-query and multi-head attention with biases, a gated MLP with biases, a gated MoE block, learned
     positions and a vocabulary that needs padding, at tensor-parallel size 2: the per-rank state dicts cut by this package
     and by the reference (from the same safetensors file) are equal key for key and bit for bit; each side's unsharding of
@@ -429,34 +429,38 @@ def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path, key_value_he
     from lm_engine.hf_models.tp_weights import _rule, fix_unsharded_state_dict, shard_state_dict, unshard_tensor_parallel_state_dicts
 
     world = 2
-    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=key_value_heads, add_bias=True)
-    made = dict(vocab_size=250, hidden_size=64, num_layers=2, position_embedding_type="learned_absolute", max_position_embeddings=32,
-                normalization_function="layernorm", tie_word_embeddings=True, sequence_mixer_blocks=[attention, dict(attention)],
-                mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=True),
-                            dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, num_experts=4, num_experts_per_tok=2,
-                                 add_bias=False)])
-    torch.manual_seed(3)
-    model = GPTBaseForCausalLM(GPTBaseConfig(**made))
-    config = model.config
-    original = {k: v.detach().clone().contiguous() for k, v in model.state_dict().items() if k != "lm_head.weight"}
-    save_file(original, str(tmp_path / "model.safetensors"))
-    shards = [shard_state_dict(config, original, rank, world) for rank in range(world)]
+    cases = {}
+    for key_value_heads in (1, 2, 4):
+        attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=key_value_heads, add_bias=True)
+        made = dict(vocab_size=250, hidden_size=64, num_layers=2, position_embedding_type="learned_absolute", max_position_embeddings=32,
+                    normalization_function="layernorm", tie_word_embeddings=True, sequence_mixer_blocks=[attention, dict(attention)],
+                    mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=True),
+                                dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                                     add_bias=False)])
+        work = tmp_path / f"kv{key_value_heads}"
+        work.mkdir()
+        torch.manual_seed(3)
+        model = GPTBaseForCausalLM(GPTBaseConfig(**made))
+        config = model.config
+        original = {k: v.detach().clone().contiguous() for k, v in model.state_dict().items() if k != "lm_head.weight"}
+        save_file(original, str(work / "model.safetensors"))
+        shards = [shard_state_dict(config, original, rank, world) for rank in range(world)]
 
-    def dimension(key: str) -> int | None:  # along which a rank-order concatenation joins the pieces of a local tensor
-        if ".kv_attn." in key:
-            return None
-        if ".q_attn." in key:
-            return 0
-        kind, dim, _ = _rule(config, key, world)
-        return None if kind == "replicate" else dim
+        def dimension(key: str, config=config) -> int | None:  # along which a rank-order concatenation joins the pieces of a local tensor
+            if ".kv_attn." in key:
+                return None
+            if ".q_attn." in key:
+                return 0
+            kind, dim, _ = _rule(config, key, world)
+            return None if kind == "replicate" else dim
 
-    concatenated = {key: shards[0][key] if dimension(key) is None else torch.cat([s[key] for s in shards], dim=dimension(key))
-                    for key in shards[0]}
-    torch.save({"shards": shards, "concatenated": concatenated}, tmp_path / "shards.pt")
-    done = subprocess.run([sys.executable, "-c", _TP_WEIGHTS, REF, json.dumps(made), str(tmp_path), str(world)], cwd=str(tmp_path),
-                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+        concatenated = {key: shards[0][key] if dimension(key) is None else torch.cat([s[key] for s in shards], dim=dimension(key))
+                        for key in shards[0]}
+        torch.save({"shards": shards, "concatenated": concatenated}, work / "shards.pt")
+        cases[str(work)] = (made, config, original, shards, concatenated)
+    done = subprocess.run([sys.executable, "-c", _TP_WEIGHTS, REF, json.dumps({work: case[0] for work, case in cases.items()}), str(world)],
+                          cwd=str(tmp_path), env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
     assert done.returncode == 0, done.stderr[-3000:]
-    theirs = torch.load(tmp_path / "theirs.pt")
 
     def same(a: dict, b: dict, skip=()) -> None:
         assert set(a) == set(b), (sorted(set(a) - set(b)), sorted(set(b) - set(a)))
@@ -464,12 +468,14 @@ def test_tensor_parallel_weight_layout_is_the_reference_s(tmp_path, key_value_he
             if key not in skip:
                 assert a[key].shape == b[key].shape and torch.equal(a[key], b[key]), key
 
-    for rank in range(world):
-        same(shards[rank], theirs["shards"][rank])
-    same(theirs["whole"], original)
-    same(unshard_tensor_parallel_state_dicts(config, theirs["shards"]), original)
-    same(fix_unsharded_state_dict(config, concatenated, world), original)
-    same(theirs["fixed"], original, skip=("transformer.wpe.weight",))  # the reference leaves the padding of the position table in
+    for work, (_, config, original, shards, concatenated) in cases.items():
+        theirs = torch.load(os.path.join(work, "theirs.pt"))
+        for rank in range(world):
+            same(shards[rank], theirs["shards"][rank])
+        same(theirs["whole"], original)
+        same(unshard_tensor_parallel_state_dicts(config, theirs["shards"]), original)
+        same(fix_unsharded_state_dict(config, concatenated, world), original)
+        same(theirs["fixed"], original, skip=("transformer.wpe.weight",))  # the reference leaves the padding of the position table in
 
 
 # the same scenario text runs against the reference (child process) and against this package (here): only the package that
