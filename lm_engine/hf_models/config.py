@@ -10,6 +10,7 @@ accepted and ignored: the head layout follows from ``num_attention_heads`` / ``n
 from __future__ import annotations
 
 import copy
+import inspect
 import warnings
 from typing import Any
 
@@ -258,8 +259,20 @@ class CommonConfig(PretrainedConfig):
         return out
 
     def to_diff_dict(self) -> dict:
-        out = self.to_dict()
-        out.pop("transformers_version", None)
+        """What ``config.json`` holds: every key of this model family (also those at their defaults, so that the file reads
+        on its own) plus the generic transformers keys that differ from their defaults."""
+        typed = (self.sequence_mixer_blocks, self.mlp_blocks)
+        self.sequence_mixer_blocks, self.mlp_blocks = _as_plain(typed[0]), _as_plain(typed[1])
+        try:
+            out = super().to_diff_dict()
+        finally:
+            self.sequence_mixer_blocks, self.mlp_blocks = typed
+        full = self.to_dict()
+        for key in inspect.signature(CommonConfig.__init__).parameters:
+            if key in full:
+                out[key] = full[key]
+        for key in set(full) - set(PretrainedConfig().to_dict()):  # keys of a subclass (sharing pattern and the like)
+            out.setdefault(key, full[key])
         return out
 
     def __deepcopy__(self, memo):

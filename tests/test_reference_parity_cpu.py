@@ -923,3 +923,65 @@ def test_public_methods_of_the_reference_s_main_classes_exist_here(tmp_path):
             if gone:
                 missing[class_name] = gone
     assert not missing, missing
+
+
+_CONFIG_FILES = r"""
+import json, sys
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+from transformers import AutoConfig
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+rm.GPTBaseConfig(**json.loads(sys.argv[2])).save_pretrained(sys.argv[3] + "/theirs")
+views = {}
+for which in ("theirs", "mine"):
+    view = AutoConfig.from_pretrained(sys.argv[3] + "/" + which).to_dict()
+    view.pop("_name_or_path", None)
+    views[which] = json.loads(json.dumps(view, default=repr))
+json.dump(views, open(sys.argv[3] + "/views.json", "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_config_files_are_interchangeable_with_the_reference(tmp_path):
+    """A hybrid config (attention with a multiplier, Mamba-2, GRU, MoE with a shared expert, muP multipliers, YaRN scaling):
+    ``config.json`` written by this package has the keys and values of the one the reference writes, the reference reads
+    both into the same config, and this package reads the reference's file into the config it started from."""
+    import json
+
+    from transformers import AutoConfig
+
+    from lm_engine.hf_models import GPTBaseConfig
+
+    made = dict(vocab_size=256, hidden_size=64, num_layers=3, position_embedding_type="rope", rope_dim=16, normalization_function="rmsnorm",
+                tie_word_embeddings=False, m_emb=12.0, m_width=2.0, m_residual=0.3, init_method="mup", router_aux_loss_coef=0.02,
+                rope_scaling=dict(type="yarn", factor=4.0, original_max_position_embeddings=128),
+                sequence_mixer_blocks=[dict(sequence_mixer_type="softmax_attention", num_attention_heads=4, num_key_value_heads=2, add_bias=False,
+                                            attention_multiplier=0.3),
+                                       dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=128, num_heads=8, num_groups=2, chunk_size=8),
+                                       dict(sequence_mixer_type="gru", state_size=32, num_heads=4)],
+                mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=128, add_bias=False),
+                            dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=64, shared_intermediate_size=32, num_experts=4,
+                                 num_experts_per_tok=2, add_bias=False),
+                            dict(mlp_type="MLP", activation_function="gelu_pytorch_tanh", add_bias=True)])
+    config = GPTBaseConfig(**made)
+    config.save_pretrained(str(tmp_path / "mine"))
+    done = subprocess.run([sys.executable, "-c", _CONFIG_FILES, REF, json.dumps(made), str(tmp_path)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    mine = json.loads((tmp_path / "mine" / "config.json").read_text())
+    theirs = json.loads((tmp_path / "theirs" / "config.json").read_text())
+    assert mine == theirs, {key: (mine.get(key), theirs.get(key)) for key in set(mine) | set(theirs) if mine.get(key) != theirs.get(key)}
+    views = json.loads((tmp_path / "views.json").read_text())
+    assert views["mine"] == views["theirs"]
+    read_back = AutoConfig.from_pretrained(str(tmp_path / "theirs")).to_dict()
+    expected = config.to_dict()
+    for view in (read_back, expected):
+        view.pop("_name_or_path", None)
+    assert read_back == expected
