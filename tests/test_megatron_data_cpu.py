@@ -258,3 +258,28 @@ def test_indices_and_samples_match_reference(tmp_path):
         assert np.array_equal(ds.sample_index, ref[f"sample{n}"])
         assert np.array_equal(ds.shuffle_index, ref[f"shuffle{n}"])
         assert np.array_equal(np.stack([ds[i]["text"] for i in range(n)]), ref[f"text{n}"])
+
+
+def test_stand_alone_dataloader_tool(tmp_path):
+    """``lm_engine.cli.megatron_dataloader``: the loaders without the rest of the engine (library call and command line), weighted
+    blend of two stores, resumption by the number of consumed samples."""
+    import subprocess
+
+    from lm_engine.cli.megatron_dataloader import build_dataloaders
+
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    _write_store(a, 80, 3)
+    _write_store(b, 60, 4)
+    common = dict(data_path=[0.7, a, 0.3, b], split="90,10,0", sequence_length=16, micro_batch_size=4, num_training_steps=6,
+                  data_cache_path=str(tmp_path / "cache"), eval_during_training=True, eval_interval=3, num_workers=0)
+    train, validation, test = build_dataloaders(**common)
+    first, second = next(train)["text"], next(train)["text"]
+    assert first.shape == (4, 17) and len(validation) == 1 and test == []
+    resumed, _, _ = build_dataloaders(**common, consumed_samples=4)
+    assert torch.equal(next(resumed)["text"], second)
+
+    done = subprocess.run([sys.executable, "-m", "lm_engine.cli.megatron_dataloader", "--data-path", "0.7", a, "0.3", b, "--split", "90,10,0",
+                           "--sequence-length", "16", "--micro-batch-size", "4", "--num-training-steps", "6", "--cache", str(tmp_path / "cache"),
+                           "--show", "2"], cwd=ROOT, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert "batch 1: text (4, 17)" in done.stdout and f"first tokens {first[0, :8].tolist()}" in done.stdout
