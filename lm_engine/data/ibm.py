@@ -14,7 +14,8 @@ can report and restore its position so that a run resumes mid-epoch, also on a d
     CheckpointDataset       saves the whole stack's state every ``interval`` batches and reloads the latest one
 
 State dictionaries are per (loader worker) rank; :meth:`load_state_dict` takes the list of all saved ranks' states and
-picks / re-deals what belongs to this rank.
+picks / re-deals what belongs to this rank. From the same shard files and arguments every layer emits, token for token,
+what the reference's class of the same name emits, and saves the same position.
 """
 
 from __future__ import annotations
@@ -256,162 +257,177 @@ _handler_map = {"arrow": ArrowHandler, "hf_parquet": ParquetHandler}
 
 # ----------------------------------------------------------------------------------------------------------------------
 class StreamingDocDataset(_StatefulDataset):
-    """Streams the documents of ``datapath/<dataset>`` (shard files, possibly nested) that fall to this rank.
+    """Streams the documents of ``datapath`` (shard files, possibly nested) that fall to this rank.
 
-    The documents of all files form one numbered range; rank ``r`` of ``w`` owns the contiguous share
-    ``[r / w, (r + 1) / w)`` of it, so files may be split between ranks. Within an epoch the owned documents are
-    visited in the order of a full-period linear congruential generator (no shuffle array is kept); a document is
-    emitted as chunks of at most ``max_chunksize`` tokens, the first starting with ``bos`` (when set) and the last
-    ending with ``delimiter_token``. Document counts come from ``meta/*.csv`` (columns: path, documents, tokens) when
-    present, otherwise from the files themselves.
+    Partition: the shard files, in sorted order, are laid end to end by size (the ``size`` column of ``../meta/*counts*.csv``
+    when there is one, else the file sizes); rank ``r`` of ``w`` owns the stretch ``[r / w, (r + 1) / w]`` of that line, and
+    of every file it touches the documents whose numbers fall inside the matching fraction. Order: the owned file pieces
+    are shuffled once (seeded by ``seed + rank``) and read one after the other, so a file is opened once per epoch; within
+    a piece the documents come in the order of a full-period linear congruential generator, no index array is kept.
+    A document is emitted as chunks of at most ``max_chunksize`` tokens, the first starting with ``bos`` (when set) and the
+    last ending with ``delimiter_token``. The stream, and the saved position (``docset_index``, ``chunk_index``,
+    ``lcg_state``), are those of the reference's class of the same name (lm_engine/data/ibm.py:742-1086).
     """
 
     def __init__(self, datapath: str, rank: int, worldsize: int, filehandler: _ShardFileHandler, delimiter_token: Any,
                  bos_token: Any | None = None, strip_tokens: set | None = None, seed: int = 42, min_length: int = 1,
                  max_chunksize: int = 1024, verbose: bool = False) -> None:
         super().__init__(datapath, rank, worldsize)
+        assert max_chunksize > 0, "max_chunksize must be positive"
         self.filehandler = filehandler
         self.eos, self.bos = delimiter_token, bos_token
         self.drop = set(strip_tokens or ())
         self.seed, self.min_length, self.chunksize, self.verbose = seed, min_length, max_chunksize, verbose
-        self.docset: list[tuple[str, int, int]] = []  # (file, first doc, last doc) inclusive, owned by this rank
+        self.docset: list[tuple[str, int, int]] = []  # (file relative to datapath, first doc, last doc) inclusive
         self.dataset = ""
         self.docs_per_epoch = 0
-        # position
-        self.docset_index = 0  # documents of the current epoch already started
-        self.chunk_index = -1  # last chunk emitted of the current document (-1: none)
+        # position: the document of the epoch that is being read, its last chunk handed out, the generator state before it
+        self.docset_index = 0
+        self.chunk_index = -1
+        self.lcg_state = 0
+        # statistics
         self.epochs_seen = -1
         self.tokens_seen = 0
         self.docs_seen = 0
         self.percent_seen = 0.0
-        self.lcg_state = seed + rank
         self.state_params = ["dataset", "docset_index", "chunk_index", "epochs_seen", "tokens_seen", "docs_seen", "percent_seen", "lcg_state"]
 
     # -- discovery -------------------------------------------------------------------------------------------------------
-    def _document_counts(self, root: str, files: list[str]) -> dict[str, int]:
-        meta = os.path.join(os.path.dirname(root.rstrip("/")), "meta")
-        counts: dict[str, int] = {}
-        if os.path.isdir(meta):
-            for name in os.listdir(meta):
-                if not name.endswith(".csv"):
+    def _metadata(self, parent: str, dataset: str) -> tuple[dict[str, int], dict[str, int]]:
+        """``(sizes, documents)`` per file (relative to the dataset directory) from the first ``*counts*.csv`` under
+        ``parent/meta``; empty dicts when there is none. Rows are keyed by ``.../<dataset>/<file>``."""
+        folder = os.path.join(parent, "meta")
+        tables = [name for name in os.listdir(folder) if "counts" in name and "csv" in name] if os.path.isdir(folder) else []
+        sizes: dict[str, int] = {}
+        documents: dict[str, int] = {}
+        if not tables:
+            return sizes, documents
+        marker = f"/{dataset}/"
+        with open(os.path.join(folder, tables[0])) as handle:
+            for row in csv.DictReader(handle):
+                path = row["dataset/filename"]
+                at = path.rfind(marker)
+                if at < 0:
                     continue
-                with open(os.path.join(meta, name)) as handle:
-                    for row in csv.DictReader(handle):
-                        path = row.get("dataset/filename") or row.get("path") or ""
-                        for f in files:
-                            if path.endswith(os.path.relpath(f, os.path.dirname(root.rstrip("/")))) or path.endswith(os.path.basename(f)):
-                                counts[f] = int(row.get("documents") or row.get("docs") or 0)
-        for f in files:
-            if f not in counts or counts[f] <= 0:
-                counts[f] = self.filehandler.length(f)
-        return counts
+                key = path[at + len(marker):]
+                documents[key] = int(row["documents"])
+                if row.get("size") not in (None, ""):
+                    sizes[key] = int(row["size"])
+        return sizes, documents
 
     def setup(self) -> None:
         if self.is_setup:
             return
         super().setup()
         root = self.datapath
-        self.dataset = os.path.basename(root.rstrip("/")) if not self.dataset else self.dataset
-        files = sorted(os.path.join(folder, name) for folder, _, names in os.walk(root) for name in names
+        parent, dataset = os.path.split(root.rstrip("/"))
+        self.dataset = dataset
+        names = sorted(os.path.join(folder, name)[len(root.rstrip("/")) + 1:] for folder, _, files in os.walk(root) for name in files
                        if self.filehandler.is_legal(os.path.join(folder, name)))
-        assert files, f"no shard files of the expected type under {root}"
-        counts = self._document_counts(root, files)
-        total = sum(counts[f] for f in files)
-        first = (total * self.rank) // self.worldsize
-        last = (total * (self.rank + 1)) // self.worldsize  # exclusive
-        cursor = 0
-        for f in files:
-            lo, hi = max(first, cursor), min(last, cursor + counts[f])
-            if hi > lo:
-                self.docset.append((f, lo - cursor, hi - cursor - 1))
-            cursor += counts[f]
-        self.docs_per_epoch = sum(hi - lo + 1 for _, lo, hi in self.docset)
-        assert self.docs_per_epoch > 0, f"rank {self.rank} of {self.worldsize} owns no document of {root}"
-        if self.epochs_seen < 0 and self.docset_index == 0:
-            self.lcg_state = self.seed + self.rank  # fresh start: the stream depends on the final (worker-folded) rank
+        assert names, f"no shard files of the expected type under {root}"
+        sizes, documents = self._metadata(parent, dataset)
+        weights = [sizes[name] for name in names] if sizes else [os.path.getsize(os.path.join(root, name)) for name in names]
+        total = sum(weights)
+        shares = [weight / total for weight in weights]
+        lo, hi = self.rank / self.worldsize, (self.rank + 1) / self.worldsize
+        cursor, owned = 0, []
+        for name, share in zip(names, shares):
+            if cursor <= hi and cursor + share >= lo:
+                owned.append((name, min(max((lo - cursor) / share, 0), 1), min(max((hi - cursor) / share, 0), 1)))
+            cursor += share
+        self.docset = []
+        for name, first_fraction, last_fraction in owned:
+            count = documents[name] if documents else self.filehandler.length(os.path.join(root, name))
+            first, last = round(count * first_fraction), round(count * last_fraction) - 1
+            if last >= first:
+                self.docset.append((name, first, last))
+        self.docs_per_epoch = sum(last - first + 1 for _, first, last in self.docset)
+        # the order of the pieces and the generator both depend on the final (worker-folded) rank
+        random.Random(self.seed + self.rank).shuffle(self.docset)
+        self.lcg_state = self.seed + self.rank
 
     # -- order -----------------------------------------------------------------------------------------------------------
-    def _locate(self, index: int) -> tuple[str, int]:
-        for f, lo, hi in self.docset:
-            span = hi - lo + 1
+    def _piece_of(self, index: int) -> tuple[str, int, int]:
+        """``(file, documents in the piece, first document)`` of the piece that holds document ``index`` of the epoch."""
+        for name, first, last in self.docset:
+            span = last - first + 1
             if index < span:
-                return f, lo + index
+                return name, span, first
             index -= span
         raise IndexError(index)
 
-    def _next_random_document(self) -> int:
-        """Full-period LCG modulo the next power of two, skipping values outside the range: a permutation of
-        ``range(docs_per_epoch)`` per period, continued across epochs from the saved state."""
-        modulus = 1 << max(int(math.ceil(math.log2(max(self.docs_per_epoch, 2)))), 1)
+    def _draw(self, size: int) -> int:
+        """Next value below ``size`` of the generator ``x -> 5 x + c`` modulo the next power of two (``c`` odd, so the period
+        is full: ``size`` consecutive draws visit every document of a piece once), from the saved state."""
+        modulus = 2 ** math.ceil(math.log2(size))
+        increment = (self.rank + self.seed) * 2 + 1
+        state = self.lcg_state
         while True:
-            self.lcg_state = (5 * self.lcg_state + 2 * self.seed + 1) % modulus  # a = 1 mod 4, c odd: full period
-            if self.lcg_state < self.docs_per_epoch:
-                return self.lcg_state
-
-    def _chunks(self, doc) -> int:
-        length = len(doc) + (1 if self.bos is not None else 0) + 1
-        return max(math.ceil(length / self.chunksize), 1)
+            state = (5 * state + increment) % modulus
+            if state < size:
+                return state
 
     def _chunk(self, doc, j: int, n_chunks: int) -> list:
         """Chunk ``j`` of the delimited document ``[bos] doc eos``."""
-        offset = 1 if self.bos is not None else 0
-        start = j * self.chunksize
-        stop = min((j + 1) * self.chunksize, len(doc) + offset + 1)
-        out: list = []
-        if j == 0 and self.bos is not None:
-            out.append(self.bos)
-        body_lo, body_hi = max(start - offset, 0), min(stop - offset, len(doc))
-        if body_hi > body_lo:
-            out.extend(self.filehandler.slice(doc, body_lo, body_hi - body_lo))
+        start, pull = j * self.chunksize, self.chunksize
+        if self.bos is not None:
+            if j == 0:
+                pull -= 1
+            else:
+                start -= 1
+        out = self.filehandler.slice(doc, start, pull)
+        self.tokens_seen += len(out)
+        if self.bos is not None and j == 0:
+            out = [self.bos] + out
         if j == n_chunks - 1:
-            out.append(self.eos)
+            out = out + [self.eos]
         return out
+
+    def _read(self, index: int, files: dict, first_chunk: int, stop_chunk: int | None):
+        """Chunks ``[first_chunk, stop_chunk)`` (to the end of the document when ``stop_chunk`` is None) of document ``index``
+        of the epoch; the generator's return value is the state that the draw for this document left."""
+        name, span, first = self._piece_of(index)
+        drawn = self._draw(span)
+        path = os.path.join(self.datapath, name)
+        if files.get("path") != path:
+            files["path"], files["reader"] = path, self.filehandler.open(path)  # one open file at a time
+        doc = self.filehandler.get(files["reader"], first + drawn, self.drop)
+        if len(doc) == 0:
+            return drawn
+        length = len(doc) + (1 if self.bos is None else 2)
+        if length >= self.min_length:
+            n_chunks = math.ceil(length / self.chunksize)
+            for j in range(first_chunk, n_chunks if stop_chunk is None else stop_chunk):
+                self.chunk_index = j
+                if stop_chunk is None and j == n_chunks - 1:
+                    self.docs_seen += 1
+                    self.percent_seen = self.docs_seen * 100 / (self.docs_per_epoch + 1e-9)
+                yield self._chunk(doc, j, n_chunks)
+        return drawn
 
     def __iter__(self):
         self.setup()
-        reader, open_path = None, None
-        resume_doc = self.docset_index > 0 and self.chunk_index >= 0  # mid-document restart
+        # where the (possibly restored) position points: a pass visits every document once, starting there
+        start_doc, start_state, skipped = self.docset_index, self.lcg_state, self.chunk_index + 1
+        files: dict = {}
         while True:
-            if self.docset_index == 0 and not resume_doc:
-                self.epochs_seen += 1
-            while self.docset_index < self.docs_per_epoch or resume_doc:
-                if resume_doc:
-                    local, first_chunk = self._current_doc, self.chunk_index + 1
-                    resume_doc = False
-                else:
-                    local, first_chunk = self._next_random_document(), 0
-                    self._current_doc = local
-                    self.docset_index += 1
-                path, row = self._locate(local)
-                if path != open_path:
-                    reader, open_path = self.filehandler.open(path), path
-                doc = self.filehandler.get(reader, row, self.drop)
-                if len(doc) < self.min_length:
-                    continue
-                n_chunks = self._chunks(doc)
-                for j in range(first_chunk, n_chunks):
-                    chunk = self._chunk(doc, j, n_chunks)
-                    self.chunk_index = j
-                    self.tokens_seen += len(chunk)
-                    if j == n_chunks - 1:
-                        self.docs_seen += 1
-                        self.chunk_index = -1
-                        self.percent_seen = self.docs_seen * 100.0 / self.docs_per_epoch
-                    yield chunk
-            self.docset_index = 0
-
-    def state_dict(self) -> dict:
-        out = super().state_dict()
-        out[self.statename("_current_doc")] = getattr(self, "_current_doc", 0)
-        return out
+            for step in range(self.docs_per_epoch):
+                index = (start_doc + step) % self.docs_per_epoch
+                if index == 0:
+                    self.epochs_seen += 1
+                self.docset_index = index
+                self.lcg_state = yield from self._read(index, files, skipped if step == 0 else 0, None)
+            # the chunks of the first document that were handed out before the restart close the pass
+            self.docset_index, self.lcg_state = start_doc, start_state
+            yield from self._read(start_doc, files, 0, skipped)
 
     def load_state_dict(self, state_dicts: list[dict], sharded_input: bool = False) -> list[dict]:
         self.setup()
         assert self.load_worldsize == self.worldsize or sharded_input, (
             "StreamingDocDataset alone cannot change the number of ranks; wrap it in ScalableShardDataset")
+        name = self.dataset
         mine = super().load_state_dict(state_dicts, sharded_input)
-        if len(mine) == 1 and self.statename("_current_doc") in mine[0]:
-            self._current_doc = mine[0][self.statename("_current_doc")]
+        assert name == self.dataset, f"the saved position belongs to dataset {self.dataset}, not {name}"
         return mine
 
 
@@ -567,8 +583,11 @@ def _repath(dataset: _StatefulDataset, datapath: str, rank: int, worldsize: int,
 
 
 class BufferDataset(_WrapperDataset):
-    """Re-cuts the stream of variable-length chunks into lines of exactly ``seq_len`` tokens. ``pack_hard`` splits
-    chunks across lines; otherwise a chunk that does not fit starts a new line and the old one is padded."""
+    """Re-cuts the stream of variable-length chunks into lines of ``seq_len`` tokens without losing a token. Chunks are
+    pulled until the line would overflow. ``pack_hard``: the overflowing chunk is split across the line boundary; a token
+    that has to give way to the delimiter at the end of a line opens the next line. Otherwise the chunk that does not fit
+    opens the next line and the current one is closed with the delimiter and padded. A line that does not start with
+    ``bos_token`` gets one. Same lines as the reference's class (lm_engine/data/ibm.py:646-739)."""
 
     def __init__(self, dataset: _StatefulDataset, seq_len: int, pack_hard: bool, bos_token=None, eos_token=None, pad_token=None) -> None:
         super().__init__(dataset)
@@ -580,38 +599,43 @@ class BufferDataset(_WrapperDataset):
         self.buffer: list = []
         self.state_params = ["buffer"]
 
+    def _line(self, source) -> list:
+        held, pending = list(self.buffer), []
+        while len(held) + len(pending) < self.len:  # `pending`: the last chunk pulled, not yet part of the line
+            held = held + pending
+            pending = list(next(source))
+        if self.bos is not None and (not held or held[0] != self.bos):
+            held = [self.bos] + held
+        if len(held) < self.len and not self.pack_hard:
+            if self.eos is not None and held and held[-1] != self.eos:
+                held = held + [self.eos]
+            self.buffer = pending
+            return held if self.pad is None else held + [self.pad] * (self.len - len(held))
+        if len(held) < self.len:
+            held, pending = held + pending, []
+        line, rest = held[: self.len], held[self.len :]
+        if self.eos is not None and line[-1] != self.eos:
+            rest = [line[-1]] + rest
+            line[-1] = self.eos
+        self.buffer = rest + pending
+        return line
+
     def __iter__(self):
         self.setup()
         source = iter(self.dataset)
         while True:
-            if self.pack_hard:
-                while len(self.buffer) < self.len:
-                    self.buffer = self.buffer + list(next(source))
-                line, self.buffer = self.buffer[: self.len], self.buffer[self.len :]
-            else:
-                line = self.buffer
-                self.buffer = []
-                while True:
-                    chunk = list(next(source))[: self.len]
-                    if len(line) + len(chunk) > self.len:
-                        self.buffer = chunk
-                        break
-                    line = line + chunk
-                line = line + [self.pad] * (self.len - len(line))
-            if self.bos is not None and line[0] != self.bos:
-                line = [self.bos] + line[:-1]
-            if self.eos is not None and line[-1] != self.eos:
-                line = line[:-1] + [self.eos]
-            yield line
+            yield self._line(source)
 
 
 class PreloadBufferDataset(_WrapperDataset):
-    """Shuffle inside a window: keeps ``window_size`` lines, emits a random one and refills its place. After a restart
-    on fewer ranks the re-dealt windows are larger than ``window_size`` and drain back to it."""
+    """Shuffle inside a window of ``window_size`` lines: a random line of the window is emitted and its place refilled.
+    The window grows by one line per step until it is full (so the first lines come out almost in order, as in the
+    reference's class, lm_engine/data/ibm.py:570-643). After a restart on fewer ranks the re-dealt windows are larger than
+    ``window_size`` and drain back to it."""
 
     def __init__(self, dataset: _StatefulDataset, window_size: int) -> None:
         super().__init__(dataset)
-        assert window_size > 1
+        assert window_size > 1, "a window of one line does not shuffle"
         self.window_size = window_size
         self.g_state = None
         self.generator = torch.Generator().manual_seed(self.rank)
@@ -625,7 +649,7 @@ class PreloadBufferDataset(_WrapperDataset):
         if self.g_state is not None:
             self.generator.set_state(self.g_state)
         while True:
-            while len(self.buffer) < self.window_size:
+            if len(self.buffer) < self.window_size:
                 self.buffer.append(next(source))
             index = int(torch.randint(len(self.buffer), (1,), generator=self.generator))
             out = self.buffer[index]

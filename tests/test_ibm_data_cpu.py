@@ -143,3 +143,105 @@ def test_loader_factory_and_auto_checkpoint(tmp_path):
     # a new loader picks up the latest state and continues with the batch that followed it
     resumed = build_experimental_data_loader(cfg, None, rank=0, world_size=1)
     assert torch.equal(next(resumed), batches[6])
+
+
+# the same scenario text runs against the reference (child process) and against this package (here)
+_REFERENCE_SCENARIO = r"""
+import copy
+import os
+import torch
+from lm_engine.data.ibm import (ArrowHandler, BufferDataset, PreloadBufferDataset, PreprocessDataset, SamplingDataset, ScalableShardDataset,
+                                StreamingDocDataset, build_experimental_data_loader, train_config)
+from lm_engine.utils import ProcessGroupManager
+
+def plain(value):
+    if isinstance(value, torch.Tensor):
+        return value.tolist()
+    if isinstance(value, dict):
+        return {key: plain(item) for key, item in value.items()}
+    if isinstance(value, (list, tuple)):
+        return [plain(item) for item in value]
+    return value
+
+def take(iterator, n):
+    return [plain(next(iterator)) for _ in range(n)]
+
+def scenario(root):
+    out = {}
+    for rank in range(3):
+        d = StreamingDocDataset(os.path.join(root, "a"), rank, 3, ArrowHandler(), 0, bos_token=1, max_chunksize=16, seed=7)
+        d.setup()
+        out[f"stream_rank{rank}"] = take(iter(d), 60)
+    d = StreamingDocDataset(os.path.join(root, "b"), 0, 1, ArrowHandler(), 0, max_chunksize=1000, min_length=5, seed=3)
+    d.setup()
+    out["stream_long_chunks"] = take(iter(d), 50)
+    for rank in range(2):
+        d = ScalableShardDataset(StreamingDocDataset(os.path.join(root, "a"), rank, 2, ArrowHandler(), 0, max_chunksize=16, seed=5), 0, n_logical_shards=8)
+        d.setup()
+        out[f"scalable_rank{rank}"] = take(iter(d), 60)
+    d = SamplingDataset(root, StreamingDocDataset(root, 0, 1, ArrowHandler(), 0, max_chunksize=16, seed=9), 0, datasets=["a", "b"], weights=[3, 1])
+    d.setup()
+    out["sampling"] = take(iter(d), 80)
+    for hard in (True, False):
+        d = BufferDataset(StreamingDocDataset(os.path.join(root, "a"), 0, 1, ArrowHandler(), 0, max_chunksize=16, seed=7), 24, pack_hard=hard,
+                          bos_token=1, eos_token=0, pad_token=2)
+        d.setup()
+        out[f"buffer_hard{int(hard)}"] = take(iter(d), 30)
+    d = PreloadBufferDataset(StreamingDocDataset(os.path.join(root, "a"), 0, 1, ArrowHandler(), 0, max_chunksize=16, seed=7), 10)
+    d.setup()
+    out["preload"] = take(iter(d), 40)
+
+    # a position saved in the middle of a document, and what follows it
+    def reader():
+        made = BufferDataset(StreamingDocDataset(os.path.join(root, "a"), 0, 1, ArrowHandler(), 0, bos_token=1, max_chunksize=8, seed=11), 20, pack_hard=True)
+        made.setup()
+        return made
+    first = reader()
+    stream = iter(first)
+    out["before_saving"] = take(stream, 23)
+    out["saved_state"] = plain(first.state_dict())
+    out["after_saving"] = take(stream, 40)
+    second = reader()
+    second.load_state_dict([copy.deepcopy(out["saved_state"])])  # the reference extends a loaded buffer in place
+    out["after_loading"] = take(iter(second), 40)
+
+    # the whole stack as the training entry point builds it
+    cfg = train_config(dict(dataset_path=root, datasets="a,b", weights="2,1", drop_tokens="", bos_token=1, eos_token=0, file_type="arrow", col_name="tokens",
+                            logical_shards=8, seq_len=31, batch_size=3, num_workers=0, enable_checkpoint=False, checkpoint_model_weights_only=False))
+    for rank in range(2):
+        with ProcessGroupManager.set_dummy_data_parallel_rank(rank), ProcessGroupManager.set_dummy_data_parallel_world_size(2):
+            loader = build_experimental_data_loader(cfg, None)
+            out[f"loader_rank{rank}"] = take(loader, 12)
+    return out
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "lm_engine")),
+                    reason="reference is not installed under baseline/_ref")
+def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path):
+    """Token for token what the reference's classes of the same names produce from the same shard files: the document
+    streams of three ranks (with and without a start token, short and long chunks, a minimum length), logical shards on two
+    ranks, weighted sampling of two datasets, hard and soft packing into lines, the shuffle window, the position saved in the
+    middle of a document (the same state dict) and the stream after loading it, and the batches of the whole stack as the
+    training entry point builds it, on two data-parallel ranks."""
+    import json
+    import subprocess
+    import sys
+
+    reference = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    root = str(tmp_path / "data")
+    _write_dataset(root, "a", n_files=3, docs_per_file=17, first_id=100)
+    _write_dataset(root, "b", n_files=2, docs_per_file=11, first_id=500)
+    child = "import json, sys\nsys.path.insert(0, sys.argv[1])\nexec(sys.argv[2])\njson.dump(scenario(sys.argv[3]), open(sys.argv[4], 'w'))\n"
+    out = tmp_path / "theirs.json"
+    done = subprocess.run([sys.executable, "-c", child, reference, _REFERENCE_SCENARIO, root, str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    scope: dict = {}
+    exec(_REFERENCE_SCENARIO, scope)
+    mine = json.loads(json.dumps(scope["scenario"](root)))
+    assert set(mine) == set(theirs) and len(theirs) == 16
+    for key in theirs:
+        assert mine[key] == theirs[key], key
+    assert mine["after_loading"] == mine["after_saving"]
