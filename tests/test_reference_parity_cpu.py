@@ -985,3 +985,81 @@ def test_config_files_are_interchangeable_with_the_reference(tmp_path):
     for view in (read_back, expected):
         view.pop("_name_or_path", None)
     assert read_back == expected
+
+
+_FLOPS_SCENARIO = r"""
+import lm_engine.hf_models as hm
+from lm_engine.enums import GradientCheckpointingMethod
+from lm_engine.train_utils import get_model_tflops
+
+def scenario():
+    attention = dict(sequence_mixer_type="softmax_attention", num_attention_heads=8, num_key_value_heads=2, add_bias=False)
+    mqa = dict(sequence_mixer_type="softmax_attention", num_attention_heads=8, num_key_value_heads=1, add_bias=True)
+    mamba = dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=256, num_heads=8, num_groups=2, chunk_size=8)
+    gru = dict(sequence_mixer_type="gru", state_size=64, num_heads=4)
+    rnn = dict(sequence_mixer_type="rnn", state_size=64, num_heads=4)
+    latent = dict(sequence_mixer_type="multihead_latent_attention", num_attention_heads=8, query_compression_size=64, key_value_compression_size=32, head_dim=16)
+    conv = dict(sequence_mixer_type="causal_convolution", in_channels=128, out_channels=128, kernel_size=3, num_groups=128, activation_function="silu")
+    sb = dict(sequence_mixer_type="stickbreaking_attention", num_attention_heads=8, num_key_value_heads=2)
+    dense = dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=512, add_bias=False)
+    plain = dict(mlp_type="MLP", activation_function="gelu_pytorch_tanh", intermediate_size=512, add_bias=True)
+    moe = dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=128, num_experts=8, num_experts_per_tok=2, add_bias=False)
+    shared = dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=128, shared_intermediate_size=64, num_experts=8, num_experts_per_tok=2, add_bias=False)
+    out = {}
+    for name, mixers, mlps, extra in [
+        ("dense", [attention] * 2, [dense] * 2, {}),
+        ("mqa_plain", [mqa] * 2, [plain] * 2, dict(position_embedding_type="learned_absolute")),
+        ("moe", [attention] * 2, [moe, shared], {}),
+        ("hybrid", [mamba, gru, rnn, attention], [dense, moe, plain, dense], dict(num_layers=4)),
+        ("latent_conv", [latent, conv], [dense] * 2, dict(position_embedding_type="nope")),
+        ("stickbreaking", [sb] * 2, [dense] * 2, dict(position_embedding_type="nope")),
+        ("tied", [attention] * 2, [dense] * 2, dict(tie_word_embeddings=True)),
+    ]:
+        made = dict(vocab_size=1000, hidden_size=128, num_layers=2, position_embedding_type="rope", rope_dim=16, normalization_function="rmsnorm",
+                    tie_word_embeddings=False, sequence_mixer_blocks=[dict(m) for m in mixers], mlp_blocks=[dict(m) for m in mlps])
+        made.update(extra)
+        try:
+            config = hm.GPTBaseConfig(**made)
+            out[name] = [get_model_tflops(config, 16, 512, None, {}),
+                         get_model_tflops(config, 4, 2048, GradientCheckpointingMethod.block, {}),
+                         get_model_tflops(config, 4, 2048, GradientCheckpointingMethod.block, {"num_blocks": 1})]
+        except Exception as error:
+            out[name] = f"{type(error).__name__}: {error}"
+    return out
+"""
+
+_FLOPS_CHILD = r"""
+import json, sys
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+exec(sys.argv[2])
+json.dump(scenario(), open(sys.argv[3], "w"))
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_model_flop_count_is_the_reference_s(tmp_path):
+    """The FLOP model behind the logged TFLOP/s and MFU (lm_engine/train_utils.py:73-212): dense, multi-query with biases, MoE
+    with and without a shared expert, a Mamba-2 / GRU / RNN / attention hybrid, latent attention with a convolution mixer,
+    stick-breaking attention and tied embeddings, each without recomputation, with every block recomputed and with one block
+    recomputed, give the reference's numbers exactly."""
+    import json
+
+    out = tmp_path / "flops.json"
+    done = subprocess.run([sys.executable, "-c", _FLOPS_CHILD, REF, _FLOPS_SCENARIO, str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = json.loads(out.read_text())
+    scope: dict = {}
+    exec(_FLOPS_SCENARIO, scope)
+    mine = json.loads(json.dumps(scope["scenario"]()))
+    assert len(theirs) == 7 and all(isinstance(values, list) and min(values) > 0 for values in theirs.values()), theirs
+    assert mine == theirs
