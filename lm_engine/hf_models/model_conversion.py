@@ -99,6 +99,11 @@ def _import_config(hf) -> GPTBaseConfig:
         sequence_mixer_blocks=mixers, mlp_blocks=mlps, **extra)
 
 
+_ARCHITECTURES = {"llama": "LlamaForCausalLM", "granite": "GraniteForCausalLM", "granitemoe": "GraniteMoeForCausalLM",
+                  "granitemoeshared": "GraniteMoeSharedForCausalLM", "granitemoehybrid": "GraniteMoeHybridForCausalLM",
+                  "gpt_bigcode": "GPTBigCodeForCausalLM"}
+
+
 def _export_config(config: GPTBaseConfig, model_type: str):
     from transformers import CONFIG_MAPPING
 
@@ -113,7 +118,8 @@ def _export_config(config: GPTBaseConfig, model_type: str):
             activation_function=mlp.activation_function, resid_pdrop=attn.dropout, embd_pdrop=config.embedding_dropout,
             attn_pdrop=attn.softmax_dropout, layer_norm_epsilon=config.layer_norm_epsilon, initializer_range=config.initializer_range,
             scale_attn_weights=attn.attention_multiplier is None, use_cache=config.use_cache, multi_query=attn.num_key_value_heads == 1,
-            tie_word_embeddings=True, bos_token_id=config.bos_token_id, eos_token_id=config.eos_token_id, pad_token_id=config.pad_token_id)
+            tie_word_embeddings=True, bos_token_id=config.bos_token_id, eos_token_id=config.eos_token_id, pad_token_id=config.pad_token_id,
+            architectures=[_ARCHITECTURES["gpt_bigcode"]])
 
     assert config.normalization_function == "rmsnorm"
     attn_blocks = [b for b in config.sequence_mixer_blocks if b.sequence_mixer_type == "softmax_attention"]
@@ -149,7 +155,10 @@ def _export_config(config: GPTBaseConfig, model_type: str):
                               mamba_expand=mamba.intermediate_size // config.hidden_size, mamba_d_conv=mamba.conv_kernel_size,
                               mamba_chunk_size=mamba.chunk_size, mamba_conv_bias=mamba.use_conv_bias, mamba_proj_bias=mamba.add_bias,
                               mamba_d_head=mamba.intermediate_size // mamba.num_heads)
-    return CONFIG_MAPPING[model_type](**kwargs)
+            # carried along as in the reference's export of this family
+            kwargs.update(normalization_function=config.normalization_function, init_method=config.init_method)
+    # serving stacks choose the model class by this key
+    return CONFIG_MAPPING[model_type](architectures=[_ARCHITECTURES[model_type]], **kwargs)
 
 
 # ----------------------------------------------------------------------------------------------------------------------

@@ -73,4 +73,8 @@ def test_import_export_round_trip(name, tmp_path):
     reloaded = AutoModelForCausalLM.from_pretrained(back_dir).eval().float()
     with torch.no_grad():
         torch.testing.assert_close(reloaded(input_ids=ids).logits, expected, atol=2e-5, rtol=1e-4)
-    assert os.path.isfile(os.path.join(back_dir, "config.json"))
+    import json
+
+    with open(os.path.join(back_dir, "config.json")) as handle:
+        written = json.load(handle)
+    assert written["architectures"] == [type(hf_model).__name__]  # serving stacks pick the model class by this key
