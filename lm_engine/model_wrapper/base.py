@@ -190,5 +190,9 @@ class ModelWrapper(nn.Module):
                 state_dict = self.model.state_dict()
         else:
             state_dict = {k[len("model."):] if k.startswith("model.") else k: v for k, v in state_dict.items()}
+        model = getattr(self, "model", None)
+        if model is not None and not getattr(self.config, "architectures", None):
+            # what transformers' own save_pretrained records; the unsharded weights are those of the single-device class
+            self.config.architectures = [type(model).__name__.removesuffix("_TP")]
         self.config.save_pretrained(save_path)
         SafeTensorsWeightsManager.save_state_dict(state_dict, save_path)
