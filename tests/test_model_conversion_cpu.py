@@ -78,3 +78,77 @@ def test_import_export_round_trip(name, tmp_path):
     with open(os.path.join(back_dir, "config.json")) as handle:
         written = json.load(handle)
     assert written["architectures"] == [type(hf_model).__name__]  # serving stacks pick the model class by this key
+
+
+_REFERENCE_CONVERTERS = r"""
+import json, sys
+sys.path.insert(0, sys.argv[1])
+import transformers
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm, export_to_huggingface, import_from_huggingface
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+# the reference reads `rope_theta` / `rope_scaling` off the transformers configs, which the installed transformers keeps under
+# `rope_parameters`
+for name in ("LlamaConfig", "GraniteConfig", "GraniteMoeConfig", "GraniteMoeSharedConfig"):
+    cls = getattr(transformers, name)
+    cls.rope_theta = property(lambda self: (self.__dict__.get("rope_parameters") or {}).get("rope_theta", 10000))
+    cls.rope_scaling = property(lambda self: None)
+for root, model_type in json.loads(sys.argv[2]).items():
+    import_from_huggingface(root + "/hf", root + "/theirs")
+    export_to_huggingface(root + "/theirs", root + "/theirs_back", model_type=model_type)
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "lm_engine")),
+                    reason="reference is not installed under baseline/_ref")
+def test_converted_checkpoints_equal_the_reference_s_converters(tmp_path):
+    """llama (with and without biases), granite, granitemoe, granitemoeshared and granitemoehybrid: the directory this package's
+    import writes holds the tensors and the config of the one the reference's import writes from the same Hugging Face
+    checkpoint, and so does the export back (bit-equal tensors, equal ``config.json``). The reference's gpt_bigcode
+    converter does not run against the installed transformers."""
+    import json
+    import subprocess
+    import sys
+
+    from safetensors.torch import load_file
+
+    reference = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    jobs = {}
+    for name in ("llama", "llama_bias", "granite", "granitemoe", "granitemoeshared", "granitemoehybrid"):
+        root = str(tmp_path / name)
+        torch.manual_seed(0)
+        hf_config = _hf_config(name)
+        AutoModelForCausalLM.from_config(hf_config).float().save_pretrained(root + "/hf", safe_serialization=True)
+        import_from_huggingface(root + "/hf", root + "/mine")
+        export_to_huggingface(root + "/mine", root + "/mine_back", hf_config.model_type)
+        jobs[root] = hf_config.model_type
+    done = subprocess.run([sys.executable, "-c", _REFERENCE_CONVERTERS, reference, json.dumps(jobs)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=900, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+
+    def tensors(folder: str) -> dict:
+        out = {}
+        for name in os.listdir(folder):
+            if name.endswith(".safetensors"):
+                out.update(load_file(os.path.join(folder, name)))
+        return out
+
+    def config(folder: str) -> dict:
+        with open(os.path.join(folder, "config.json")) as handle:
+            made = json.load(handle)
+        made.pop("rope_parameters", None)  # rewritten by the child's patch of the reference's config class
+        return made
+
+    for root in jobs:
+        for mine, theirs in ((root + "/mine", root + "/theirs"), (root + "/mine_back", root + "/theirs_back")):
+            a, b = tensors(mine), tensors(theirs)
+            assert set(a) == set(b), (mine, sorted(set(a) ^ set(b)))
+            for key in a:
+                assert a[key].shape == b[key].shape and torch.equal(a[key], b[key]), (mine, key)
+            assert config(mine) == config(theirs), mine
