@@ -16,7 +16,13 @@ class BaseInstructionDataset(BaseDataset):
         self.examples = self.prepare_examples()
 
     def construct_input_from_format(self, instruction: str, input: str | None = None) -> str:
-        text = instruction if not input else f"{instruction}\n\n{input}"
+        """The prompt of the reference (lm_engine/data/instruction_tuning/base.py:43-48): the instruction, a blank line, an
+        ``input:`` line when there is one, and ``output:``. The reference refuses an ``input_format`` for these datasets;
+        here one wraps the whole prompt."""
+        text = instruction + "\n\n"
+        if input:
+            text += f"input: {input}\n"
+        text += "output:"
         return super().construct_input_from_format(text)
 
     def load_raw(self):
@@ -32,7 +38,7 @@ class BaseInstructionDataset(BaseDataset):
         for raw in self.load_raw():
             instruction, context, answer = self.fields(raw)
             text_in = self.construct_input_from_format(instruction, context)
-            text_out = self.construct_output_from_format(answer) if self.mode == Mode.training else None
+            text_out = self.construct_output_from_format(answer.strip()) if self.mode == Mode.training else None
             examples.append(self.get_input_output_token_ids(text_in, text_out))
         return examples
 
@@ -55,12 +61,8 @@ class SlimOrcaDataset(BaseInstructionDataset):
     hub_name = "Open-Orca/SlimOrca-Dedup"
 
     def fields(self, raw):
-        system = human = answer = ""
-        for turn in raw["conversations"]:
-            if turn["from"] == "system":
-                system = turn["value"]
-            elif turn["from"] == "human":
-                human = turn["value"]
-            elif turn["from"] == "gpt":
-                answer = turn["value"]
-        return (system if system else human), (human if system else None), answer
+        turns = raw["conversations"]
+        if len(turns) == 3:  # system prompt (possibly empty), question, answer: the layout of the corpus
+            return turns[0]["value"], turns[1]["value"], turns[2]["value"]
+        said = {turn["from"]: turn["value"] for turn in turns}
+        return said.get("system", ""), said.get("human"), said.get("gpt", "")

@@ -16,5 +16,7 @@ class SST2Dataset(BaseDataset):
         data = load_dataset("glue", "sst2")[self._SPLIT_NAME[self.split]]
         for raw in data:
             text_in = self.construct_input_from_format(raw["sentence"].strip())
-            text_out = self.construct_output_from_format(str(raw["label"])) if self.mode == Mode.training else None
+            # the label as a word, as in the reference (lm_engine/data/sst2.py:53-57)
+            text_out = (self.construct_output_from_format("positive" if raw["label"] == 1 else "negative")
+                        if self.mode == Mode.training else None)
             self.examples.append(self.get_input_output_token_ids(text_in, text_out))

@@ -533,6 +533,30 @@ def scenario():
     results["collate_packed_output_only"] = tensors(collate_fn(copy(), Mode.training, LossMask.output_only, 2, False, True, pad_to_multiple_of=8, device=cpu))
     results["collate_packed_no_mask"] = tensors(collate_fn(copy(), Mode.training, LossMask.no_mask, 2, False, True, device=cpu))
     results["collate_inference"] = tensors(collate_fn([dict(input=list(e["input"])) for e in batch], Mode.inference, LossMask.output_only, 2, False, False, device=cpu))
+    # instruction-tuning corpora and SST-2 over a stand-in for `datasets.load_dataset`
+    import datasets
+    from lm_engine.data import AlpacaDataset, DollyDataset, SlimOrcaDataset, SST2Dataset
+    corpora = {
+        "tatsu-lab/alpaca": {"train": [dict(instruction="w1 w2", input="w3", output=" w4 w5 "), dict(instruction="w6", input="", output="w7")]},
+        "databricks/databricks-dolly-15k": {"train": [dict(instruction="w1 w2", context="w3 w8", response="w4\n"), dict(instruction="w6", context="", response="w7")]},
+        "Open-Orca/SlimOrca-Dedup": {"train": [dict(conversations=[dict(**{"from": "system"}, value="w9"), dict(**{"from": "human"}, value="w1 w2"), dict(**{"from": "gpt"}, value=" w4 ")]),
+                                                dict(conversations=[dict(**{"from": "system"}, value=""), dict(**{"from": "human"}, value="w6"), dict(**{"from": "gpt"}, value="w7")])]},
+        "sst2": {split: [dict(sentence=" w1 w2 ", label=1), dict(sentence="w3", label=0)] for split in ("train", "validation", "test")},
+    }
+    corpora["glue"] = corpora["sst2"]
+    real, datasets.load_dataset = datasets.load_dataset, lambda name, *args, **kwargs: corpora[name]
+    import sys
+    for module in list(sys.modules.values()):  # modules that imported the function by name
+        if getattr(module, "__name__", "").startswith("lm_engine.data") and hasattr(module, "load_dataset"):
+            module.load_dataset = datasets.load_dataset
+    try:
+        for cls in (AlpacaDataset, DollyDataset, SlimOrcaDataset, SST2Dataset):
+            for mode in (Mode.training, Mode.inference) if cls is SST2Dataset else (Mode.training,):
+                made = cls(class_args={}, split=DatasetSplit.train, mode=mode, tokenizer=Tokenizer(), is_encoder_decoder=False, data_name="x",
+                           input_format="__input__", output_format="__output__", max_input_tokens=None, max_output_tokens=None)
+                results[f"{cls.__name__}_{mode.value}"] = made.examples
+    finally:
+        datasets.load_dataset = real
     pairs = Words("z", 4, Mode.training, encoder_decoder=True).examples
     results["collate_encoder_decoder"] = tensors(collate_fn([dict(input=list(e["input"]), output=list(e["output"])) for e in pairs], Mode.training,
                                                             LossMask.output_only, 2, True, False, device=cpu))
