@@ -557,6 +557,11 @@ def scenario():
                 results[f"{cls.__name__}_{mode.value}"] = made.examples
     finally:
         datasets.load_dataset = real
+    from lm_engine.data import DebugDataset
+    for label, class_args, mode in (("static", dict(num_examples=3, token_id=7), Mode.training), ("indexed", dict(num_examples=3, static_examples=False), Mode.training)):
+        made = DebugDataset(class_args=class_args, split=DatasetSplit.train, mode=mode, tokenizer=Tokenizer(), is_encoder_decoder=False, data_name="d",
+                            input_format="__input__", output_format="__output__", max_input_tokens=6, max_output_tokens=4)
+        results["debug_" + label] = [len(made)] + [made[i] for i in range(len(made))]
     pairs = Words("z", 4, Mode.training, encoder_decoder=True).examples
     results["collate_encoder_decoder"] = tensors(collate_fn([dict(input=list(e["input"]), output=list(e["output"])) for e in pairs], Mode.training,
                                                             LossMask.output_only, 2, True, False, device=cpu))
