@@ -283,3 +283,38 @@ def test_stand_alone_dataloader_tool(tmp_path):
                            "--show", "2"], cwd=ROOT, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     assert "batch 1: text (4, 17)" in done.stdout and f"first tokens {first[0, :8].tolist()}" in done.stdout
+
+
+_CONVERT = r"""
+import sys
+sys.path.insert(0, sys.argv[1])
+from lm_engine.data.megatron.preprocess_data import convert_file
+class Tokenizer:
+    vocab_size = 1000
+    eos_token_id = 1
+    def encode(self, text):
+        return [2 + sum(map(ord, word)) % 900 for word in text.split()]
+convert_file(Tokenizer(), sys.argv[2], sys.argv[3], workers=1, chunk_size=4)
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_converted_store_is_byte_identical_to_the_reference_s(tmp_path):
+    """An arrow file of token lists converted to a ``.bin/.idx`` store by this package and by the reference: the same bytes in
+    both files (the reference's converter reaches only its arrow branch: its jsonl branch opens the wrong name)."""
+    import subprocess
+
+    import pyarrow as pa
+
+    schema = pa.schema([pa.field("tokens", pa.uint32())])
+    source = str(tmp_path / "in.arrow")
+    with pa.ipc.new_file(source, schema) as writer:
+        for i in range(20):
+            writer.write(pa.record_batch([pa.array([(i * 7 + j) % 900 + 2 for j in range(3 + i % 6)], type=pa.uint32())], schema))
+    for which, package in (("theirs", REF), ("mine", ROOT)):
+        done = subprocess.run([sys.executable, "-c", _CONVERT, package, source, str(tmp_path / which)], cwd=str(tmp_path),
+                              env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+    for suffix in ("_text.bin", "_text.idx"):
+        mine, theirs = (tmp_path / f"mine{suffix}").read_bytes(), (tmp_path / f"theirs{suffix}").read_bytes()
+        assert len(mine) > 100 and mine == theirs, suffix
