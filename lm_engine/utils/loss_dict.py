@@ -2,11 +2,11 @@ from __future__ import annotations
 
 
 class MetricsTrackingDict:
-    """Small numeric dict supporting ``+`` with a dict/tracker (key-wise) or scalar and ``/`` by a scalar
+    """Small numeric dict supporting ``+`` and ``/`` with a dict/tracker (key-wise) or a scalar; prints one ``key = value`` line per entry
     (parity: lm_engine/utils/loss_dict.py:8-59)."""
 
-    def __init__(self, values: dict | None = None) -> None:
-        self.data = dict(values or {})
+    def __init__(self, data: dict | None = None) -> None:
+        self.data = dict(data or {})
 
     def __getitem__(self, key):
         return self.data[key]
@@ -52,6 +52,12 @@ class MetricsTrackingDict:
     __iadd__ = __add__
 
     def __truediv__(self, other):
+        if isinstance(other, MetricsTrackingDict):
+            other = other.data
+        if isinstance(other, dict):  # key-wise; a key that is only in the divisor starts from zero
+            for key, value in other.items():
+                self.data[key] = self.data.get(key, 0) / value
+            return self
         for key in self.data:
             self.data[key] = self.data[key] / other
         return self
@@ -59,4 +65,4 @@ class MetricsTrackingDict:
     __itruediv__ = __truediv__
 
     def __repr__(self) -> str:
-        return f"MetricsTrackingDict({self.data})"
+        return "\n".join(f"{key} = {value}" for key, value in self.data.items())
