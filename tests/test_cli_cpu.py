@@ -138,3 +138,44 @@ def test_conversion_tools_round_trip_and_pt_to_safetensors(tmp_path, capsys):
             saved.update(load_file(os.path.join(st_dir, name)))
     for key, value in model.state_dict().items():
         assert torch.equal(saved[key], value), key
+
+
+def test_whole_corpus_conversion_in_jobs_and_merge_by_size(tmp_path, capsys):
+    """``convert-tree`` divides the files of every subset among jobs (together they convert each file once, a repeated job
+    skips what is there); ``merge-tree`` joins the stores of a subset, in groups when a size limit is given, and records the
+    grouping; the merged stores hold every document of the sources in order."""
+    import os
+
+    import pyarrow as pa
+
+    from lm_engine.cli import preprocess_data
+    from lm_engine.data.megatron.indexed_dataset import MMapIndexedDataset
+
+    class Tokenizer:
+        vocab_size, eos_token_id = 1000, 1
+
+    raw, staged, merged = (str(tmp_path / name) for name in ("raw", "staged", "merged"))
+    schema = pa.schema([pa.field("tokens", pa.uint32())])
+    documents = {}
+    for subset, files in (("a", 5), ("b", 2)):
+        os.makedirs(os.path.join(raw, subset))
+        for f in range(files):
+            with pa.ipc.new_file(os.path.join(raw, subset, f"part{f}.arrow"), schema) as writer:
+                for d in range(3):
+                    tokens = [10 * f + d + 2] * (4 + d)
+                    writer.write(pa.record_batch([pa.array(tokens, type=pa.uint32())], schema))
+                    documents.setdefault(subset, []).append(tokens + [1])
+    counts = [len(preprocess_data.convert_tree(Tokenizer(), raw, staged, ["a", "b"], jobs=3, job_index=job)) for job in range(3)]
+    assert sum(counts) == 7 and max(counts) <= 4
+    assert preprocess_data.convert_tree(Tokenizer(), raw, staged, ["a", "b"], jobs=1, job_index=0) == []  # all there already
+    made = preprocess_data.merge_tree(staged, merged, ["a", "b"])
+    assert sorted(made) == ["a", "b"] and len(made["a"]) == 5
+    for subset in ("a", "b"):
+        store = MMapIndexedDataset(os.path.join(merged, subset))
+        assert [store[i].tolist() for i in range(len(store))] == documents[subset]
+    grouped = preprocess_data.merge_tree(staged, str(tmp_path / "grouped"), ["a"], max_file_size=50 / 1024**3, output_suffix="v1")
+    assert len(grouped) >= 2 and sum(len(group) for group in grouped.values()) == 5
+    with open(tmp_path / "grouped" / "files-v1.json") as handle:
+        assert json.load(handle) == grouped
+    out = _run(preprocess_data, ["merge-tree", "--input-path", staged, "--output-path", str(tmp_path / "again"), "--data-subsets", "b"], capsys)
+    assert "b: 2 stores" in out
