@@ -1,7 +1,7 @@
 # Developer entry points. Everything runs from the repository root with the interpreter on PATH.
 PYTHON ?= python
 
-.PHONY: build test test-gpu bench bench-reference microbench clean
+.PHONY: build test test-gpu bench bench-reference microbench style clean
 
 build:            ## cross-compile csrc/ for sm_100a into csrc/_build/ (works without a GPU)
 	$(PYTHON) -c "import __graft_entry__ as g; g.build()"
@@ -22,6 +22,9 @@ microbench: build ## kernel micro-benchmarks
 	$(PYTHON) -m lm_engine.ops.microbench gemm
 	$(PYTHON) -m lm_engine.ops.microbench mxfp8
 	$(PYTHON) -m lm_engine.ops.microbench attention
+
+style:            ## the pre-commit hooks over the whole tree
+	pre-commit run --all-files
 
 clean:
 	rm -rf csrc/_build
