@@ -233,7 +233,13 @@ class ParquetHandler(_ShardFileHandler):
     def open(self, path: str):
         import pyarrow.parquet as pq
 
-        return pq.read_pandas(path, columns=[self.col_name], partitioning=None)[self.col_name]
+        names = pq.read_metadata(path).schema.names
+        column = self.col_name
+        if column not in names:  # the usual names of the text column in hub datasets
+            found = [name for name in ("text", "content", "contents") if name in names]
+            assert len(found) == 1, f"{path}: no column {self.col_name!r} and {len(found)} of text / content / contents"
+            column = found[0]
+        return pq.read_pandas(path, columns=[column], partitioning=None)[column]
 
     def length(self, path: str) -> int:
         import pyarrow.parquet as pq
@@ -241,7 +247,8 @@ class ParquetHandler(_ShardFileHandler):
         return pq.read_metadata(path).num_rows
 
     def get(self, reader, index: int, drop_tokens: set):
-        doc = self.tokenizer(str(reader[index]))["input_ids"]
+        # whole documents are tokenised before they are cut: a bound on the text keeps a pathological one affordable
+        doc = self.tokenizer(str(reader[index])[:128_000])["input_ids"]
         if len(doc) > 0 and doc[0] in drop_tokens:
             doc = doc[1:]
         if len(doc) > 0 and doc[-1] in drop_tokens:
@@ -679,18 +686,19 @@ class PreprocessDataset(_WrapperDataset):
 
 
 class CheckpointDataset(_WrapperDataset):
-    """Saves the state of the whole stack to ``<save_path>/checkpoints/step-<n>_ckp/`` every ``interval`` batches of
-    ``steps_per_batch`` items, and loads the latest one under ``load_path`` at the first iteration."""
+    """Saves the state of the whole stack to ``<save_path>/step-<n>/loader_state_<rank>.pth`` every ``interval`` batches of
+    ``steps_per_batch`` items (the reference's layout, lm_engine/data/ibm.py:440-567), and at the first iteration loads the
+    newest such directory: one in the save directory wins over one under ``load_path``. Directories written by earlier
+    versions of this class (``checkpoints/step-<n>_ckp``) are still found."""
 
     def __init__(self, dataset: _StatefulDataset, load_path: str, interval: int, steps_per_batch: int = 1, save_path: str = "") -> None:
         super().__init__(dataset)
         self.interval = interval
         self.spb = max(int(steps_per_batch), 1)
         self.load_path = load_path
-        self.path = os.path.join(save_path or load_path, "checkpoints")
+        self.path = save_path or load_path
         self.step = 0
         self.ministep = 0
-        self.state_params = ["step", "ministep"]
 
     def setup(self) -> None:
         if not self.is_setup:
@@ -706,39 +714,41 @@ class CheckpointDataset(_WrapperDataset):
                 self.ministep = 0
                 self.step += 1
                 if self.step % self.interval == 0:
-                    self.save_to_path(os.path.join(self.path, f"step-{self.step}_ckp"))
+                    self.save_to_path(os.path.join(self.path, f"step-{self.step}"))
+
+    @staticmethod
+    def _holds_loader_states(path: str) -> bool:
+        return os.path.isdir(path) and any("loader" in name for name in os.listdir(path))
 
     def _latest(self, path: str) -> str | None:
-        """A directory of loader states, or the newest ``step-<n>_ckp`` below ``path`` / ``path/checkpoints``."""
+        """``path`` itself when it holds loader states, else the ``step-<n>`` directory with the largest ``n`` below ``path``
+        (or below ``path/checkpoints``) if that one holds loader states."""
         if not path or not os.path.isdir(path):
             return None
-        if any(name.startswith("loader_state_") for name in os.listdir(path)):
+        if self._holds_loader_states(path):
             return path
         for root in (path, os.path.join(path, "checkpoints")):
-            latest = _get_latest(root, lambda p: os.path.isdir(p) and os.path.basename(p).startswith("step-") and p.endswith("_ckp")
-                                 ) if os.path.isdir(root) else None
-            if latest is not None and any(name.startswith("loader_state_") for name in os.listdir(latest)):
+            latest = _get_latest(root, lambda p: os.path.basename(p).startswith("step-"))
+            if latest is not None and self._holds_loader_states(latest):
                 return latest
         return None
 
     def load_from_path(self, path: str) -> None:
-        latest = self._latest(path)
+        latest = self._latest(self.path) or self._latest(path)
         if latest is None:
-            log_rank_0(logging.INFO, f"no dataloader checkpoint under {path}: starting from the beginning")
+            log_rank_0(logging.INFO, f"no dataloader checkpoint under {self.path} or {path}: starting from the beginning")
             return
         started = time.time()
         self.dataset.load_from_path(latest)
-        state_file = os.path.join(latest, f"checkpointer_{self.rank}.pth")
-        if os.path.isfile(state_file):
-            own = torch.load(state_file, weights_only=False)
-            self.step, self.ministep = own["step"], own["ministep"]
-        else:
-            self.step = int(os.path.basename(latest).split("-")[1].split("_")[0])
+        name = os.path.basename(latest.rstrip("/"))
+        if name.startswith("step-"):
+            self.step = int(name.split("-")[1].split("_")[0])
         log_rank_0(logging.INFO, f"dataloader state loaded from {latest} in {time.time() - started:.1f} s (step {self.step})")
 
     def save_to_path(self, path: str) -> None:
+        started = time.time()
         self.dataset.save_to_path(path)
-        torch.save({"step": self.step, "ministep": self.ministep}, os.path.join(path, f"checkpointer_{self.rank}.pth"))
+        log_rank_0(logging.INFO, f"dataloader state saved to {path} in {time.time() - started:.1f} s")
 
 
 # ----------------------------------------------------------------------------------------------------------------------

@@ -138,8 +138,8 @@ def test_loader_factory_and_auto_checkpoint(tmp_path):
     loader = build_experimental_data_loader(cfg, None, rank=0, world_size=1)
     batches = _take(loader, 8)
     assert all(b.shape == (4, 17) and b.dtype == torch.int64 for b in batches)
-    saved = sorted(os.listdir(tmp_path / "ckpt" / "checkpoints"))
-    assert saved == ["step-3_ckp", "step-6_ckp"]
+    saved = sorted(os.listdir(tmp_path / "ckpt"))
+    assert saved == ["step-3", "step-6"] and os.listdir(tmp_path / "ckpt" / "step-6") == ["loader_state_0.pth"]
     # a new loader picks up the latest state and continues with the batch that followed it
     resumed = build_experimental_data_loader(cfg, None, rank=0, world_size=1)
     assert torch.equal(next(resumed), batches[6])
@@ -205,6 +205,22 @@ def scenario(root):
     second.load_state_dict([copy.deepcopy(out["saved_state"])])  # the reference extends a loaded buffer in place
     out["after_loading"] = take(iter(second), 40)
 
+    # automatic saving: directory names, files, and the stream of a second instance that finds them
+    import tempfile
+    from lm_engine.data.ibm import CheckpointDataset
+    folder = tempfile.mkdtemp()
+    def saver():
+        made = CheckpointDataset(BufferDataset(StreamingDocDataset(os.path.join(root, "b"), 0, 1, ArrowHandler(), 0, max_chunksize=8, seed=2), 12, pack_hard=True),
+                                 folder, 5, steps_per_batch=2)
+        made.setup()
+        return made
+    first = saver()
+    out["autosave_stream"] = take(iter(first), 27)
+    out["autosave_tree"] = sorted((name, sorted(os.listdir(os.path.join(folder, name)))) for name in os.listdir(folder))
+    second = saver()
+    out["autosave_resumed_step"] = second.step
+    out["autosave_resumed_stream"] = take(iter(second), 7)
+
     # the whole stack as the training entry point builds it
     cfg = train_config(dict(dataset_path=root, datasets="a,b", weights="2,1", drop_tokens="", bos_token=1, eos_token=0, file_type="arrow", col_name="tokens",
                             logical_shards=8, seq_len=31, batch_size=3, num_workers=0, enable_checkpoint=False, checkpoint_model_weights_only=False))
@@ -241,7 +257,8 @@ def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path
     scope: dict = {}
     exec(_REFERENCE_SCENARIO, scope)
     mine = json.loads(json.dumps(scope["scenario"](root)))
-    assert set(mine) == set(theirs) and len(theirs) == 16
+    assert set(mine) == set(theirs) and len(theirs) == 20
     for key in theirs:
         assert mine[key] == theirs[key], key
     assert mine["after_loading"] == mine["after_saving"]
+    assert mine["autosave_resumed_step"] == 10 and mine["autosave_resumed_stream"] == mine["autosave_stream"][20:27]
