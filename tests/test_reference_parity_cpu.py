@@ -866,6 +866,12 @@ for name in modules:
     # what the module (or, for a package, one of its submodules) defines itself: names it merely imports from elsewhere are not its interface
     found[name] = sorted(key for key, value in vars(module).items() if not key.startswith("_") and not isinstance(value, type(sys))
                          and str(getattr(value, "__module__", "")).startswith(name))
+import enum
+import lm_engine.enums as enums
+from lm_engine.optimization.optimizer import _OPTIMIZER_CLASSES
+found["<enums>"] = {name: {member.name: member.value for member in cls} for name, cls in vars(enums).items()
+                    if isinstance(cls, type) and issubclass(cls, enum.Enum) and cls is not enum.Enum}
+found["<optimizers>"] = sorted(_OPTIMIZER_CLASSES)
 json.dump(found, open(sys.argv[3], "w"))
 """
 
@@ -888,6 +894,18 @@ def test_public_names_of_the_reference_resolve_here(tmp_path):
                           env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
     assert done.returncode == 0, done.stderr[-3000:]
     theirs = json.loads(out.read_text())
+    # every member of every enum (kernel names, modes, schedules, ...) with its value, and every optimizer name of the YAML files
+    import lm_engine.enums as enums
+    from lm_engine.optimization.optimizer import build_optimizer  # noqa: F401  (the module defines the table below)
+    import lm_engine.optimization.optimizer as optimizer_module
+
+    their_enums, their_optimizers = theirs.pop("<enums>"), theirs.pop("<optimizers>")
+    assert len(their_enums) >= 10
+    for name, members in their_enums.items():
+        mine = {member.name: member.value for member in getattr(enums, name)}
+        assert all(mine.get(key) == value for key, value in members.items()), (name, members, mine)
+    known = {key for table in vars(optimizer_module).values() if isinstance(table, dict) for key in table if isinstance(key, str)}
+    assert set(their_optimizers) <= known, set(their_optimizers) - known
     assert sum(len(names) for names in theirs.values()) > 150
     # helpers of the reference's own wrapping of torch FSDP / its data broadcast that have no counterpart in this design
     internal = {"lm_engine.data.megatron": {"get_source_and_broadcast_group"}, "lm_engine.kernels": {"is_cute_kernels_available"}}
