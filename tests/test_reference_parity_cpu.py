@@ -1110,3 +1110,59 @@ def test_model_flop_count_is_the_reference_s(tmp_path):
     mine = json.loads(json.dumps(scope["scenario"]()))
     assert len(theirs) == 7 and all(isinstance(values, list) and min(values) > 0 for values in theirs.values()), theirs
     assert mine == theirs
+
+
+_INITIAL_WEIGHTS = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+import lm_engine.hf_models as rm
+from lm_engine.hf_models import config as cm
+from transformers import AutoModelForCausalLM
+orig = cm.CommonConfig.__init__
+def init(self, *a, **k):
+    orig(self, *a, **k)
+    rope = self.__dict__.get("rope_parameters")
+    if isinstance(rope, dict) and "factor" not in rope:
+        self.__dict__["rope_parameters"] = None
+rm.GPTBaseConfig.__init__ = init
+made = {}
+for name, config in json.loads(sys.argv[2]).items():
+    torch.manual_seed(1234)
+    made[name] = dict(AutoModelForCausalLM.from_config(rm.GPTBaseConfig(**config)).state_dict())
+torch.save(made, sys.argv[3])
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lm_engine")), reason="reference is not installed under baseline/_ref")
+def test_the_same_seed_gives_the_reference_s_initial_weights(tmp_path):
+    """Initialisation (standard deviations by parameter kind, depth scaling of the output projections, muP division by the
+    width multiplier, Mamba-2's ``A_log`` / ``dt_bias`` / ``D``, biases and norms) and the order in which the parameters draw
+    from the generator: a model built here after ``torch.manual_seed(s)`` starts from exactly the weights of the
+    reference's model built after the same call, for plain and for muP initialisation."""
+    import json
+
+    from lm_engine.hf_models import GPTBaseConfig, GPTBaseForCausalLM
+
+    base = dict(
+        vocab_size=512, hidden_size=256, num_layers=3, position_embedding_type="learned_absolute", max_position_embeddings=128,
+        normalization_function="layernorm", tie_word_embeddings=False, initializer_range=0.02,
+        sequence_mixer_blocks=[dict(sequence_mixer_type="softmax_attention", num_attention_heads=8, num_key_value_heads=2, add_bias=True),
+                               dict(sequence_mixer_type="mamba2", state_size=16, intermediate_size=512, num_heads=8, num_groups=2, chunk_size=8),
+                               dict(sequence_mixer_type="multihead_latent_attention", num_attention_heads=8, query_compression_size=64,
+                                    key_value_compression_size=64, head_dim=32)],
+        mlp_blocks=[dict(mlp_type="MLP", activation_function="swiglu", intermediate_size=512, add_bias=True),
+                    dict(mlp_type="MoE", activation_function="swiglu", intermediate_size=256, shared_intermediate_size=128, num_experts=4,
+                         num_experts_per_tok=2, add_bias=False),
+                    dict(mlp_type="MLP", activation_function="gelu_pytorch_tanh", intermediate_size=512, add_bias=False)])
+    cases = {"normal": base, "mup": dict(base, init_method="mup", m_width=4.0, m_emb=2.0, m_residual=0.5)}
+    out = tmp_path / "initial.pt"
+    done = subprocess.run([sys.executable, "-c", _INITIAL_WEIGHTS, REF, json.dumps(cases), str(out)], cwd=str(tmp_path),
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(out)
+    for name, config in cases.items():
+        torch.manual_seed(1234)
+        mine = GPTBaseForCausalLM(GPTBaseConfig(**config)).state_dict()
+        assert set(mine) == set(theirs[name]) and len(mine) > 50
+        for key, value in theirs[name].items():
+            assert torch.equal(mine[key], value), (name, key)
