@@ -114,9 +114,15 @@ class _StatefulDataset(data.IterableDataset):
         return {self.statename(name): deepcopy(getattr(self, name)) for name in self.state_params + self.reshard_params}
 
     def _reshard(self, lists: list[list]) -> list:
-        """Concatenate the saved ranks' lists and take this rank's share."""
-        flat = [item for part in lists for item in part]
-        return _shard_partition(flat, self.rank, self.worldsize)
+        """This rank's share of the saved ranks' lists. ``lists`` are those of the saved ranks that this rank overlaps
+        (``_shard_inclusive`` of all of them), all of one length: positions are counted over the lists of ALL saved ranks
+        and shifted by what lies left of the first list given."""
+        length = len(lists[0])
+        assert all(len(part) == length for part in lists), "the saved ranks hold lists of different lengths"
+        skipped = math.floor(self.load_worldsize * self.rank / self.worldsize) * length  # items of the saved ranks not given
+        total = self.load_worldsize * length
+        first, last = int(total * self.rank / self.worldsize) - skipped, int(total * (self.rank + 1) / self.worldsize) - skipped
+        return [lists[i // length][i % length] for i in range(first, last)]
 
     def load_state_dict(self, state_dicts: list[dict], sharded_input: bool = False) -> list[dict]:
         """``state_dicts``: the states of all saved ranks (or, with ``sharded_input``, already only those this rank
@@ -125,14 +131,11 @@ class _StatefulDataset(data.IterableDataset):
         self.load_worldsize = len(state_dicts) if not sharded_input else self.load_worldsize
         mine = state_dicts if sharded_input else _shard_inclusive(state_dicts, self.rank, self.worldsize)
         if self.load_worldsize == self.worldsize and len(mine) == 1:
-            for name in self.state_params:
+            for name in self.state_params + self.reshard_params:
                 setattr(self, name, mine[0][self.statename(name)])
-        for name in self.reshard_params:
-            if self.load_worldsize == self.worldsize and len(mine) == 1:
-                setattr(self, name, mine[0][self.statename(name)])
-            else:
-                all_lists = [sd[self.statename(name)] for sd in state_dicts]
-                setattr(self, name, self._reshard(all_lists))
+        else:
+            for name in self.reshard_params:
+                setattr(self, name, self._reshard([sd[self.statename(name)] for sd in mine]))
         return mine
 
     def load_from_path(self, path: str) -> None:
@@ -480,21 +483,11 @@ class ScalableShardDataset(_WrapperDataset):
 
     def __iter__(self):
         self.setup()
-        if self.logical_shard_states is not None:  # restored positions, one per owned stream
-            for reader, state in zip(self.data, self.logical_shard_states):
-                reader.load_worldsize = reader.worldsize
-                reader.load_state_dict([state], sharded_input=True)
-            self.logical_shard_states = None
-        if self.g_state is not None:
-            self.generator.set_state(self.g_state)
         iterators = [iter(d) for d in self.data]
         while True:
             if self.current_reader is not None:
                 index = self.current_reader
             else:
-                if sum(self.n_docs_remaining) == 0:
-                    self.n_docs_remaining = [d.docs_per_epoch for d in self.data]
-                    self.generator.manual_seed(self.rank)
                 weights = torch.tensor(self.n_docs_remaining, dtype=torch.float)
                 index = int(torch.multinomial(weights, 1, generator=self.generator))
                 self.current_reader = index
@@ -502,6 +495,11 @@ class ScalableShardDataset(_WrapperDataset):
             if chunk[-1] == self.delimiter:  # document finished: choose afresh next time
                 self.n_docs_remaining[index] -= 1
                 self.current_reader = None
+                if sum(self.n_docs_remaining) == 0:
+                    # the pass is over: refilled before the chunk leaves, so that a saved state never holds an exhausted
+                    # count (re-dealt to another number of ranks it would starve its streams)
+                    self.n_docs_remaining = [d.docs_per_epoch for d in self.data]
+                    self.generator.manual_seed(self.rank)
             yield chunk
 
     def state_dict(self) -> dict:
@@ -514,7 +512,15 @@ class ScalableShardDataset(_WrapperDataset):
 
     def load_state_dict(self, state_dicts: list[dict], sharded_input: bool = False) -> list[dict]:
         self.setup()
-        return _StatefulDataset.load_state_dict(self, state_dicts, sharded_input)
+        mine = _StatefulDataset.load_state_dict(self, state_dicts, sharded_input)
+        if self.g_state is not None:
+            self.generator.set_state(self.g_state)
+        # the positions of the owned streams, applied at once: a state saved right after loading must hold them
+        for reader, state in zip(self.data, self.logical_shard_states or []):
+            reader.load_worldsize = reader.worldsize
+            reader.load_state_dict([state], sharded_input=True)
+        self.logical_shard_states = None
+        return mine
 
 
 class SamplingDataset(_WrapperDataset):

@@ -221,6 +221,27 @@ def scenario(root):
     out["autosave_resumed_step"] = second.step
     out["autosave_resumed_stream"] = take(iter(second), 7)
 
+    # four ranks save, two and eight ranks load: the streams of the logical shards move with their positions
+    def stack(rank, world):
+        made = StreamingDocDataset(os.path.join(root, "a"), rank, world, ArrowHandler(), 0, max_chunksize=16, seed=5)
+        made = PreloadBufferDataset(BufferDataset(ScalableShardDataset(made, 0, n_logical_shards=8), 20, pack_hard=True), 6)
+        made.setup()
+        return made
+    states = []
+    for rank in range(4):
+        saved = stack(rank, 4)
+        stream = iter(saved)
+        out[f"rescale_before_rank{rank}"] = take(stream, 15)
+        states.append(saved.state_dict())
+    for world in (2, 8):
+        for rank in range(world):
+            loaded = stack(rank, world)
+            loaded.load_state_dict(copy.deepcopy(states))
+            logical = loaded.dataset.dataset
+            out[f"rescale_to{world}_rank{rank}"] = [plain(logical.n_docs_remaining),
+                                                     [[r.rank, r.docset_index, r.chunk_index, r.lcg_state] for r in logical.data],
+                                                     take(iter(loaded), 25 if world == 2 else 6)]
+
     # the whole stack as the training entry point builds it
     cfg = train_config(dict(dataset_path=root, datasets="a,b", weights="2,1", drop_tokens="", bos_token=1, eos_token=0, file_type="arrow", col_name="tokens",
                             logical_shards=8, seq_len=31, batch_size=3, num_workers=0, enable_checkpoint=False, checkpoint_model_weights_only=False))
@@ -238,8 +259,9 @@ def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path
     """Token for token what the reference's classes of the same names produce from the same shard files: the document
     streams of three ranks (with and without a start token, short and long chunks, a minimum length), logical shards on two
     ranks, weighted sampling of two datasets, hard and soft packing into lines, the shuffle window, the position saved in the
-    middle of a document (the same state dict) and the stream after loading it, and the batches of the whole stack as the
-    training entry point builds it, on two data-parallel ranks."""
+    middle of a document (the same state dict) and the stream after loading it, automatic saving, the states of four ranks loaded
+    by two and by eight ranks (counts and positions of the logical shards, the lines that follow), and the batches of the whole
+    stack as the training entry point builds it, on two data-parallel ranks."""
     import json
     import subprocess
     import sys
@@ -257,7 +279,7 @@ def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path
     scope: dict = {}
     exec(_REFERENCE_SCENARIO, scope)
     mine = json.loads(json.dumps(scope["scenario"](root)))
-    assert set(mine) == set(theirs) and len(theirs) == 20
+    assert set(mine) == set(theirs) and len(theirs) == 34
     for key in theirs:
         assert mine[key] == theirs[key], key
     assert mine["after_loading"] == mine["after_saving"]
