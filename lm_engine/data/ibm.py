@@ -569,20 +569,25 @@ class SamplingDataset(_WrapperDataset):
             yield chunk
 
     def state_dict(self) -> dict:
+        """The states of the sub-dataset stacks as a list under ``sample_iterator_states`` (the reference's layout,
+        lm_engine/data/ibm.py:1351-1356), beside this layer's own counters."""
         self.setup()
-        out = {}
-        for name, child in zip(self.datasets, self.data):
-            out.update({f"{name}.{k}": v for k, v in child.state_dict().items()})
+        out = {self.statename("sample_iterator_states"): [child.state_dict() for child in self.data]}
         out.update(_StatefulDataset.state_dict(self))
         return out
 
     def load_state_dict(self, state_dicts: list[dict], sharded_input: bool = False) -> list[dict]:
         self.setup()
         mine = _StatefulDataset.load_state_dict(self, state_dicts, sharded_input)
-        for name, child in zip(self.datasets, self.data):
-            prefix = name + "."
+        key = self.statename("sample_iterator_states")
+        for index, (name, child) in enumerate(zip(self.datasets, self.data)):
             child.load_worldsize = self.load_worldsize
-            child.load_state_dict([{k[len(prefix):]: v for k, v in sd.items() if k.startswith(prefix)} for sd in mine], sharded_input=True)
+            if all(key in sd for sd in mine):
+                parts = [sd[key][index] for sd in mine]
+            else:  # states written before the list layout: the sub-dataset's keys carry its name as a prefix
+                prefix = name + "."
+                parts = [{k[len(prefix):]: v for k, v in sd.items() if k.startswith(prefix)} for sd in mine]
+            child.load_state_dict(parts, sharded_input=True)
         return mine
 
 

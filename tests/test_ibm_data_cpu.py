@@ -150,6 +150,7 @@ _REFERENCE_SCENARIO = r"""
 import copy
 import os
 import torch
+import tempfile
 from lm_engine.data.ibm import (ArrowHandler, BufferDataset, PreloadBufferDataset, PreprocessDataset, SamplingDataset, ScalableShardDataset,
                                 StreamingDocDataset, build_experimental_data_loader, train_config)
 from lm_engine.utils import ProcessGroupManager
@@ -250,6 +251,40 @@ def scenario(root):
             loader = build_experimental_data_loader(cfg, None)
             out[f"loader_rank{rank}"] = take(loader, 12)
     return out
+
+
+def job_scenario(root):
+    out = {}
+    folder = tempfile.mkdtemp()
+    def cfg():
+        return train_config(dict(dataset_path=root, datasets="a,b", weights="2,1", drop_tokens="", bos_token=1, eos_token=0, file_type="arrow", col_name="tokens",
+                                 logical_shards=8, seq_len=31, batch_size=2, num_workers=1, enable_checkpoint=True, checkpoint_model_weights_only=False,
+                                 checkpoint_folder=folder, checkpoint_interval=4, gradient_accumulation_steps=1))
+    loaders = []
+    for rank in range(4):
+        with ProcessGroupManager.set_dummy_data_parallel_rank(rank), ProcessGroupManager.set_dummy_data_parallel_world_size(4):
+            loaders.append(build_experimental_data_loader(cfg(), None))
+    firsts = [[] for _ in loaders]
+    for step in range(6):  # all ranks advance together, as the ranks of a job do
+        for rank, loader in enumerate(loaders):
+            firsts[rank].append(next(loader).tolist())
+    for rank in range(4):
+        out[f"first_rank{rank}"] = firsts[rank]
+    del loaders
+    out["tree"] = sorted((name, sorted(os.listdir(os.path.join(folder, name)))) for name in os.listdir(folder))
+    resumed = []
+    for rank in range(2):
+        with ProcessGroupManager.set_dummy_data_parallel_rank(rank), ProcessGroupManager.set_dummy_data_parallel_world_size(2):
+            resumed.append(build_experimental_data_loader(cfg(), None))
+    lines = [[] for _ in resumed]
+    for step in range(5):
+        for rank, loader in enumerate(resumed):
+            lines[rank].append(next(loader).tolist())
+    for rank in range(2):
+        out[f"resumed_rank{rank}"] = lines[rank]
+    out["tree_after"] = sorted((name, sorted(os.listdir(os.path.join(folder, name)))) for name in os.listdir(folder))
+    out["folder"] = folder
+    return out
 """
 
 
@@ -270,7 +305,8 @@ def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path
     root = str(tmp_path / "data")
     _write_dataset(root, "a", n_files=3, docs_per_file=17, first_id=100)
     _write_dataset(root, "b", n_files=2, docs_per_file=11, first_id=500)
-    child = "import json, sys\nsys.path.insert(0, sys.argv[1])\nexec(sys.argv[2])\njson.dump(scenario(sys.argv[3]), open(sys.argv[4], 'w'))\n"
+    child = ("import json, sys\nsys.path.insert(0, sys.argv[1])\nexec(sys.argv[2])\n"
+             "json.dump(dict(scenario(sys.argv[3]), job=job_scenario(sys.argv[3])), open(sys.argv[4], 'w'))\n")
     out = tmp_path / "theirs.json"
     done = subprocess.run([sys.executable, "-c", child, reference, _REFERENCE_SCENARIO, root, str(out)], cwd=str(tmp_path),
                           env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600, capture_output=True, text=True)
@@ -279,8 +315,34 @@ def test_streams_saved_positions_and_the_full_stack_equal_the_reference(tmp_path
     scope: dict = {}
     exec(_REFERENCE_SCENARIO, scope)
     mine = json.loads(json.dumps(scope["scenario"](root)))
+    their_job = theirs.pop("job")
     assert set(mine) == set(theirs) and len(theirs) == 34
     for key in theirs:
         assert mine[key] == theirs[key], key
     assert mine["after_loading"] == mine["after_saving"]
     assert mine["autosave_resumed_step"] == 10 and mine["autosave_resumed_stream"] == mine["autosave_stream"][20:27]
+
+    # the whole stack with automatic saving as a job runs it: four ranks (one loader worker each) advance together and save,
+    # two ranks find the states and go on. Same batches and same files on both sides; and the files the reference wrote
+    # are read here (two ranks again) to the batches the reference itself resumed with.
+    my_job = json.loads(json.dumps(scope["job_scenario"](root)))
+    their_folder = their_job.pop("folder")
+    my_job.pop("folder")
+    assert my_job == their_job and [name for name, _ in their_job["tree"]] == ["step-4"]
+    import shutil
+
+    from lm_engine.data.ibm import build_experimental_data_loader, train_config
+
+    for name in os.listdir(their_folder):  # back to what the two resuming ranks found: the states of the four ranks
+        if name != "step-4":
+            shutil.rmtree(os.path.join(their_folder, name))
+    cfg = train_config(dict(dataset_path=root, datasets="a,b", weights="2,1", drop_tokens="", bos_token=1, eos_token=0, file_type="arrow",
+                            col_name="tokens", logical_shards=8, seq_len=31, batch_size=2, num_workers=1, enable_checkpoint=True,
+                            checkpoint_model_weights_only=False, checkpoint_folder=their_folder, checkpoint_interval=4,
+                            gradient_accumulation_steps=1))
+    loaders = [build_experimental_data_loader(cfg, None, rank=rank, world_size=2) for rank in range(2)]
+    lines = [[], []]
+    for _ in range(5):
+        for rank, loader in enumerate(loaders):
+            lines[rank].append(next(loader).tolist())
+    assert lines[0] == their_job["resumed_rank0"] and lines[1] == their_job["resumed_rank1"]
